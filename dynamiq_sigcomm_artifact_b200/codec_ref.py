@@ -1,0 +1,176 @@
+"""CPU oracle of the `rht` codec family: a NumPy restatement of what the CUDA kernels compute.
+
+Follows the reference's strongest test idea - a scalar restatement of the codec fed the
+same random numbers as the kernel (cuda_kernels/tests/test_scaling_quantization_functional.py:122-259)
+- but for the rotation codec that this framework's `dynamiQ_aee_{b}bit` methods use:
+
+    block of 1024 values
+      -> Rademacher diagonal (1024 sign bits from Philox, shared by all ranks)
+      -> Walsh-Hadamard H_1024 / 32 (orthonormal; H_1024 = H_32 (x) H_32)
+      -> per-block fp32 scale  absmax / R,  R = 2^(b-1) - 1
+      -> stochastic rounding  floor(y * R/absmax + u),  u a 16-bit Philox uniform
+      -> b-bit codes, b in 2..8, packed without padding (8 codes of 5 bits in 5 bytes)
+
+A hop adds the locally rotated block to the decoded incoming block in fp32 and encodes
+the sum again (the reference rounds the sum to bf16 first,
+cuda_kernels/src/srrcomp/eden_utils/csrc/cuda_hierarchical_mee.cu:567-568).
+
+All arithmetic is float32 with one rounding per operation and no fused multiply-add, in the
+order the kernel uses, so that the kernel's bytes can be compared with ``==``.
+
+Layouts (shared with ``csrc/common/rht_codec.cuh``)
+* A warp owns a block; after the rotation lane ``l`` holds, in register ``k``, the
+  coefficient with index ``RHO[l, k] = (l & 3) + 4 k + 128 (l >> 2)``.
+* The 32 codes of a lane form a little-endian bit stream of ``b`` 32-bit words; word ``j`` of
+  lane ``l`` is stored at word ``j * 32 + l`` of the block's ``128 b`` code bytes, so each of
+  the ``b`` warp-wide stores is one contiguous 128-byte line.
+* A shard's message is ``[codes: nb * 128 b bytes][scales: nb * 4 bytes]``.
+"""
+from __future__ import annotations
+
+from typing import Tuple
+
+import numpy as np
+
+from .utils import philox
+
+BLOCK = 1024
+_L = np.arange(32).reshape(32, 1)
+_K = np.arange(32).reshape(1, 32)
+RHO = ((_L & 3) + 4 * _K + 128 * (_L >> 2)).astype(np.int64)  # [lane, reg] -> coefficient index
+FWD_STAGES = (0, 1, 7, 8, 9, 2, 3, 4, 5, 6)  # bit of the element index handled by each butterfly stage
+INV_STAGES = (2, 3, 4, 5, 6, 0, 1, 7, 8, 9)
+F32 = np.float32
+
+
+def qmax(bits: int) -> int:
+    if not 2 <= bits <= 8:
+        raise ValueError("bits must be in 2..8")
+    return (1 << (bits - 1)) - 1
+
+
+def payload_bytes(nblocks: int, bits: int) -> int:
+    """Bytes of one message: packed codes then one fp32 scale per block."""
+    return nblocks * (128 * bits + 4)
+
+
+def wire_bits_per_element(bits: int) -> float:
+    return (128 * bits + 4) * 8 / BLOCK
+
+
+def to_blocks(x: np.ndarray) -> np.ndarray:
+    """Flat fp32 vector -> [nblocks, 1024], zero padded; non-finite inputs become 0."""
+    x = np.asarray(x, dtype=F32).reshape(-1)
+    nb = (x.size + BLOCK - 1) // BLOCK
+    out = np.zeros(nb * BLOCK, dtype=F32)
+    out[: x.size] = np.where(np.isfinite(x), x, F32(0))
+    return out.reshape(nb, BLOCK)
+
+
+def _butterflies(v: np.ndarray, stages) -> np.ndarray:
+    v = v.astype(F32, copy=True)
+    idx = np.arange(BLOCK)
+    for bit in stages:
+        lo = idx[(idx >> bit) & 1 == 0]
+        hi = lo | (1 << bit)
+        a, b = v[:, lo], v[:, hi]
+        v[:, lo], v[:, hi] = a + b, a - b
+    return v
+
+
+def rotate_fwd(x: np.ndarray, signs: np.ndarray) -> np.ndarray:
+    """y = H_1024 (s * x) / 32 for every row of x [nb, 1024]."""
+    return _butterflies(x * signs[None, :], FWD_STAGES) * F32(1.0 / 32.0)
+
+
+def rotate_inv(y: np.ndarray, signs: np.ndarray, post_scale: float = 1.0) -> np.ndarray:
+    """x = s * H_1024 y / 32 * post_scale (post_scale = 1/world for the mean)."""
+    v = _butterflies(y, INV_STAGES)
+    return (v * F32(post_scale / 32.0)) * signs[None, :]
+
+
+def quantize(y: np.ndarray, bits: int, block_idx: np.ndarray, tag: int, step: int, seed: int
+             ) -> Tuple[np.ndarray, np.ndarray]:
+    """Rotated blocks [nb, 1024] -> (codes uint8 [nb, 32 lanes, 32 regs], scale f32 [nb])."""
+    R = qmax(bits)
+    y = y.astype(F32, copy=False)
+    absmax = np.max(np.abs(y), axis=1)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        ok = (absmax > 0) & np.isfinite(absmax)
+        scale = np.where(ok, absmax / F32(R), F32(0)).astype(F32)
+        inv = np.where(ok, F32(R) / absmax, F32(0)).astype(F32)
+    r16 = philox.block_uniforms16(block_idx, tag, step, seed)  # [nb, 32, 32]
+    u = (r16.astype(F32) + F32(0.5)) * F32(1.0 / 65536.0)
+    q = (y[:, RHO] * inv[:, None, None]).astype(F32)
+    t = (q + u).astype(F32)
+    code = np.clip(np.floor(t), -R, R).astype(np.int32) + R
+    return code.astype(np.uint8), scale
+
+
+def dequantize(codes: np.ndarray, scale: np.ndarray, bits: int) -> np.ndarray:
+    """(codes [nb,32,32], scale [nb]) -> rotated blocks [nb, 1024] in coefficient order."""
+    R = qmax(bits)
+    vals = (codes.astype(np.int32) - R).astype(F32) * scale[:, None, None].astype(F32)
+    y = np.empty((codes.shape[0], BLOCK), dtype=F32)
+    y[:, RHO.reshape(-1)] = vals.reshape(codes.shape[0], BLOCK)
+    return y
+
+
+def pack(codes: np.ndarray, bits: int) -> np.ndarray:
+    """codes [nb, 32 lanes, 32 regs] -> uint32 words [nb, bits, 32 lanes]."""
+    nb = codes.shape[0]
+    acc = np.zeros((nb, 32, bits), dtype=np.uint64)
+    for k in range(32):
+        off = k * bits
+        w, sh = off >> 5, off & 31
+        val = codes[:, :, k].astype(np.uint64) << np.uint64(sh)
+        acc[:, :, w] |= val & np.uint64(0xFFFFFFFF)
+        if sh + bits > 32:
+            acc[:, :, w + 1] |= val >> np.uint64(32)
+    return acc.astype(np.uint32).transpose(0, 2, 1).copy()
+
+
+def unpack(words: np.ndarray, bits: int) -> np.ndarray:
+    """uint32 words [nb, bits, 32] -> codes uint8 [nb, 32, 32]."""
+    nb = words.shape[0]
+    w64 = words.transpose(0, 2, 1).astype(np.uint64)  # [nb, lane, word]
+    codes = np.empty((nb, 32, 32), dtype=np.uint8)
+    mask = np.uint64((1 << bits) - 1)
+    for k in range(32):
+        off = k * bits
+        w, sh = off >> 5, off & 31
+        val = w64[:, :, w] >> np.uint64(sh)
+        if sh + bits > 32:
+            val = val | (w64[:, :, w + 1] << np.uint64(32 - sh))
+        codes[:, :, k] = (val & mask).astype(np.uint8)
+    return codes
+
+
+def to_message(words: np.ndarray, scale: np.ndarray) -> np.ndarray:
+    """Serialise one shard's blocks into the wire layout (uint8)."""
+    return np.concatenate([words.reshape(-1).view(np.uint8), scale.astype(F32).view(np.uint8)])
+
+
+def from_message(msg: np.ndarray, nblocks: int, bits: int) -> Tuple[np.ndarray, np.ndarray]:
+    ncode = nblocks * 128 * bits
+    words = msg[:ncode].view(np.uint32).reshape(nblocks, bits, 32)
+    scale = msg[ncode: ncode + 4 * nblocks].view(F32)
+    return words, scale
+
+
+def encode_blocks(y: np.ndarray, bits: int, block_idx, tag: int, step: int, seed: int) -> np.ndarray:
+    codes, scale = quantize(y, bits, np.asarray(block_idx), tag, step, seed)
+    return to_message(pack(codes, bits), scale)
+
+
+def decode_blocks(msg: np.ndarray, nblocks: int, bits: int) -> np.ndarray:
+    words, scale = from_message(msg, nblocks, bits)
+    return dequantize(unpack(words, bits), scale, bits)
+
+
+def nmse(estimate: np.ndarray, exact: np.ndarray) -> float:
+    """||estimate - exact||^2 / ||exact||^2 in float64 (the reference's vNMSE,
+    simulations_llm/new_comm_hooks/comm_hooks.py:22-50)."""
+    e = np.asarray(estimate, dtype=np.float64) - np.asarray(exact, dtype=np.float64)
+    d = float(np.sum(np.asarray(exact, dtype=np.float64) ** 2))
+    return float(np.sum(e * e)) / d if d > 0 else 0.0

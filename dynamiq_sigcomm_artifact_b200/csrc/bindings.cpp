@@ -1,0 +1,62 @@
+// Operator registration: every native entry point is a torch.ops.dq.* operator, loaded from
+// the in-tree shared library by dynamiq_sigcomm_artifact_b200/ops/__init__.py.
+// Reference counterpart: the pybind modules eden_utils
+// (cuda_kernels/src/srrcomp/eden_utils/eden_utils.cpp:417-433) and ring_allreduce_native
+// (rdma_comm_compress/ring_allreduce_ext/ring_allreduce_bindings.cpp:7-156).
+#include <torch/extension.h>
+#include <torch/library.h>
+
+namespace dq {
+at::Tensor topology();
+std::tuple<int64_t, at::Tensor> symm_alloc(int64_t device, int64_t bytes);
+int64_t symm_open(int64_t device, at::Tensor handle);
+void symm_close(int64_t ptr);
+void symm_free(int64_t ptr);
+at::Tensor wrap_ptr(int64_t ptr, int64_t bytes, int64_t device);
+
+void fused_allreduce(at::Tensor bucket, at::Tensor steps, std::vector<int64_t> mail_ptrs,
+                     std::vector<int64_t> flag_ptrs, int64_t mailbox_bytes, int64_t flag_words, int64_t nslots,
+                     int64_t status_ptr, int64_t tail_ws_ptr, int64_t rank, int64_t world, int64_t bits, int64_t ctas,
+                     int64_t threads, int64_t blocks_per_shard, int64_t slot_stride, int64_t scales_off,
+                     int64_t flag_base, int64_t epoch, int64_t seed, int64_t step, int64_t bucket_id,
+                     double post_scale, int64_t timeout_ns, bool no_transmit);
+void fused_allreduce_local(std::vector<at::Tensor> buckets, at::Tensor steps, std::vector<at::Tensor> mailboxes,
+                           std::vector<at::Tensor> flags, at::Tensor status, at::Tensor tail_ws, int64_t nslots,
+                           int64_t bits, int64_t ctas, int64_t threads, int64_t blocks_per_shard, int64_t slot_stride,
+                           int64_t scales_off, int64_t flag_base, int64_t epoch, int64_t seed, int64_t step,
+                           int64_t bucket_id, double post_scale, int64_t timeout_ns, bool no_transmit);
+std::tuple<at::Tensor, at::Tensor, at::Tensor> norm_fwd(at::Tensor x, at::Tensor w, c10::optional<at::Tensor> b,
+                                                        double eps, bool rms);
+std::tuple<at::Tensor, at::Tensor, at::Tensor> norm_bwd(at::Tensor dy, at::Tensor x, at::Tensor w, at::Tensor mean,
+                                                        at::Tensor rstd, bool rms);
+at::Tensor rope(at::Tensor x, at::Tensor cos, at::Tensor sin, bool backward);
+void adamw_step(at::Tensor table, at::Tensor numel, at::Tensor chunk_start, int64_t total_chunks, bool param_bf16,
+                bool grad_bf16, double lr, double beta1, double beta2, double eps, double weight_decay, int64_t step,
+                double grad_scale);
+}  // namespace dq
+
+TORCH_LIBRARY(dq, m) {
+  m.def("norm_fwd(Tensor x, Tensor w, Tensor? b, float eps, bool rms) -> (Tensor, Tensor, Tensor)", &dq::norm_fwd);
+  m.def("norm_bwd(Tensor dy, Tensor x, Tensor w, Tensor mean, Tensor rstd, bool rms) -> (Tensor, Tensor, Tensor)", &dq::norm_bwd);
+  m.def("rope(Tensor x, Tensor cos, Tensor sin, bool backward) -> Tensor", &dq::rope);
+  m.def("adamw_step(Tensor table, Tensor numel, Tensor chunk_start, int total_chunks, bool param_bf16, bool grad_bf16, "
+        "float lr, float beta1, float beta2, float eps, float weight_decay, int step, float grad_scale) -> ()", &dq::adamw_step);
+  m.def("topology() -> Tensor", &dq::topology);
+  m.def("symm_alloc(int device, int bytes) -> (int, Tensor)", &dq::symm_alloc);
+  m.def("symm_open(int device, Tensor handle) -> int", &dq::symm_open);
+  m.def("symm_close(int ptr) -> ()", &dq::symm_close);
+  m.def("symm_free(int ptr) -> ()", &dq::symm_free);
+  m.def("wrap_ptr(int ptr, int bytes, int device) -> Tensor", &dq::wrap_ptr);
+  m.def(
+      "fused_allreduce(Tensor(a!) bucket, Tensor steps, int[] mail_ptrs, int[] flag_ptrs, int mailbox_bytes, "
+      "int flag_words, int nslots, int status_ptr, int tail_ws_ptr, int rank, int world, int bits, int ctas, "
+      "int threads, int blocks_per_shard, int slot_stride, int scales_off, int flag_base, int epoch, int seed, "
+      "int step, int bucket_id, float post_scale, int timeout_ns, bool no_transmit) -> ()",
+      &dq::fused_allreduce);
+  m.def(
+      "fused_allreduce_local(Tensor[] buckets, Tensor steps, Tensor[] mailboxes, Tensor[] flags, Tensor status, "
+      "Tensor tail_ws, int nslots, int bits, int ctas, int threads, int blocks_per_shard, int slot_stride, "
+      "int scales_off, int flag_base, int epoch, int seed, int step, int bucket_id, float post_scale, "
+      "int timeout_ns, bool no_transmit) -> ()",
+      &dq::fused_allreduce_local);
+}

@@ -1,0 +1,258 @@
+// Warp-level building blocks of the rotation codec: one warp owns one block of 1024 values,
+// 32 per lane.  CPU oracle with the same arithmetic order: codec_ref.py.
+//
+// Replaces the reference's per-superchunk CTAs (one 256-thread CTA per 512 bytes, scalar
+// 2-byte loads, a serial thread-0 max between two block barriers;
+// cuda_kernels/src/srrcomp/eden_utils/csrc/cuda_hierarchical_mee.cu:203-270,526-604) and its
+// separate Hadamard passes (csrc/cuda_hadamard.cu:66-274).
+//
+// Register layouts of a lane
+//   load layout        reg t = 4 j + k   holds element     e = 128 j + 4 lane + k
+//   coefficient layout reg k             holds coefficient e = (lane & 3) + 4 k + 128 (lane >> 2)
+// The Hadamard transform runs five butterfly stages in registers, swaps the five lane bits
+// with the five register bits through a swizzled 4 KiB shared-memory tile, and runs five more.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "philox.cuh"
+
+namespace dq {
+
+constexpr int kBlock = 1024;
+constexpr unsigned kFullMask = 0xFFFFFFFFu;
+
+__device__ __forceinline__ void butterflies32(float (&v)[32]) {
+#pragma unroll
+  for (int m = 0; m < 5; ++m) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if ((i & (1 << m)) == 0) {
+        float a = v[i], b = v[i | (1 << m)];
+        v[i] = a + b;
+        v[i | (1 << m)] = a - b;
+      }
+    }
+  }
+}
+
+// load layout -> coefficient layout through the warp's 1024-float tile
+__device__ __forceinline__ void transpose_to_coeff(float (&v)[32], float* tile, int lane) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float4 q = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    *reinterpret_cast<float4*>(tile + j * 128 + ((lane ^ j) << 2)) = q;
+  }
+  __syncwarp();
+  const int J = lane >> 2, K = lane & 3;
+#pragma unroll
+  for (int t = 0; t < 32; ++t) v[t] = tile[J * 128 + ((t ^ J) << 2) + K];
+  __syncwarp();
+}
+
+// coefficient layout -> load layout
+__device__ __forceinline__ void transpose_to_load(float (&v)[32], float* tile, int lane) {
+  const int J = lane >> 2, K = lane & 3;
+#pragma unroll
+  for (int t = 0; t < 32; ++t) tile[J * 128 + ((t ^ J) << 2) + K] = v[t];
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float4 q = *reinterpret_cast<const float4*>(tile + j * 128 + ((lane ^ j) << 2));
+    v[4 * j] = q.x;
+    v[4 * j + 1] = q.y;
+    v[4 * j + 2] = q.z;
+    v[4 * j + 3] = q.w;
+  }
+  __syncwarp();
+}
+
+// bit t of the result = sign bit of the element a lane holds in register t of the load layout
+__device__ __forceinline__ uint32_t lane_sign_mask(const uint32_t* sign_words, int lane) {
+  uint32_t m = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    uint32_t w = sign_words[4 * j + (lane >> 3)];
+    m |= ((w >> ((lane & 7) * 4)) & 0xFu) << (4 * j);
+  }
+  return m;
+}
+
+__device__ __forceinline__ float flip(float x, uint32_t bit) {
+  return __uint_as_float(__float_as_uint(x) ^ (bit << 31));
+}
+
+__device__ __forceinline__ float sanitize(float x) { return (fabsf(x) <= 3.402823466e38f) ? x : 0.0f; }
+
+template <typename T>
+struct Elem;
+template <>
+struct Elem<float> {
+  static __device__ __forceinline__ void load4(const float* p, float (&o)[4]) {
+    float4 q = *reinterpret_cast<const float4*>(p);
+    o[0] = q.x, o[1] = q.y, o[2] = q.z, o[3] = q.w;
+  }
+  static __device__ __forceinline__ void store4(float* p, const float (&o)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]);
+  }
+  static __device__ __forceinline__ float to_float(float x) { return x; }
+  static __device__ __forceinline__ float from_float(float x) { return x; }
+};
+template <>
+struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&o)[4]) {
+    uint2 q = *reinterpret_cast<const uint2*>(p);
+    o[0] = __uint_as_float(q.x << 16), o[1] = __uint_as_float(q.x & 0xFFFF0000u);
+    o[2] = __uint_as_float(q.y << 16), o[3] = __uint_as_float(q.y & 0xFFFF0000u);
+  }
+  static __device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&o)[4]) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(o[0], o[1]);
+    __nv_bfloat162 b = __floats2bfloat162_rn(o[2], o[3]);
+    uint2 q;
+    q.x = *reinterpret_cast<uint32_t*>(&a);
+    q.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = q;
+  }
+  static __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+  static __device__ __forceinline__ __nv_bfloat16 from_float(float x) { return __float2bfloat16_rn(x); }
+};
+
+// 1024 elements starting at `base` in the load layout; elements >= valid read as 0.
+template <typename T>
+__device__ __forceinline__ void load_block(const T* base, int valid, bool vec_ok, int lane, float (&v)[32]) {
+  if (valid == kBlock && vec_ok) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float o[4];
+      Elem<T>::load4(base + j * 128 + lane * 4, o);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) v[4 * j + k] = o[k];
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        int e = j * 128 + lane * 4 + k;
+        v[4 * j + k] = e < valid ? Elem<T>::to_float(base[e]) : 0.0f;
+      }
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store_block(T* base, int valid, bool vec_ok, int lane, const float (&v)[32]) {
+  if (valid == kBlock && vec_ok) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float o[4] = {v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]};
+      Elem<T>::store4(base + j * 128 + lane * 4, o);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        int e = j * 128 + lane * 4 + k;
+        if (e < valid) base[e] = Elem<T>::from_float(v[4 * j + k]);
+      }
+    }
+  }
+}
+
+// raw gradients (load layout) -> rotated coefficients (coefficient layout): y = H (s * x) / 32
+__device__ __forceinline__ void rotate_forward(float (&v)[32], uint32_t sign_mask, float* tile, int lane) {
+#pragma unroll
+  for (int t = 0; t < 32; ++t) v[t] = flip(sanitize(v[t]), (sign_mask >> t) & 1u);
+  butterflies32(v);
+  transpose_to_coeff(v, tile, lane);
+  butterflies32(v);
+#pragma unroll
+  for (int t = 0; t < 32; ++t) v[t] = __fmul_rn(v[t], 0.03125f);
+}
+
+// rotated coefficients -> gradients in the load layout: x = s * (H y) * c, c = post_scale / 32
+__device__ __forceinline__ void rotate_inverse(float (&v)[32], uint32_t sign_mask, float c, float* tile, int lane) {
+  butterflies32(v);
+  transpose_to_load(v, tile, lane);
+  butterflies32(v);
+#pragma unroll
+  for (int t = 0; t < 32; ++t) v[t] = flip(__fmul_rn(v[t], c), (sign_mask >> t) & 1u);
+}
+
+template <int B>
+__device__ __forceinline__ void pack_codes(const uint32_t (&c)[32], uint32_t (&w)[B]) {
+#pragma unroll
+  for (int j = 0; j < B; ++j) w[j] = 0;
+#pragma unroll
+  for (int k = 0; k < 32; ++k) {
+    constexpr int dummy = 0;
+    (void)dummy;
+    const int off = k * B, wi = off >> 5, sh = off & 31;
+    w[wi] |= c[k] << sh;
+    if (sh + B > 32) w[wi + 1] |= c[k] >> (32 - sh);
+  }
+}
+
+template <int B>
+__device__ __forceinline__ uint32_t unpack_code(const uint32_t (&w)[B], int k) {
+  const int off = k * B, wi = off >> 5, sh = off & 31;
+  uint32_t x = w[wi] >> sh;
+  if (sh + B > 32) x |= w[wi + 1] << (32 - sh);
+  return x & ((1u << B) - 1u);
+}
+
+__device__ __forceinline__ float warp_absmax(const float (&y)[32]) {
+  float m = 0.0f;
+#pragma unroll
+  for (int k = 0; k < 32; ++k) m = fmaxf(m, fabsf(y[k]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(kFullMask, m, o));
+  return m;
+}
+
+// Stochastic b-bit quantisation of a block in the coefficient layout.  Returns the block scale.
+template <int B>
+__device__ __forceinline__ float quantize_block(const float (&y)[32], uint32_t (&w)[B], uint32_t block_idx,
+                                                uint32_t tag, uint32_t step, uint32_t k0, uint32_t k1, int lane) {
+  constexpr int R = (1 << (B - 1)) - 1;
+  const float m = warp_absmax(y);
+  const bool ok = (m > 0.0f) && (m <= 3.402823466e38f);
+  const float scale = ok ? __fdiv_rn(m, static_cast<float>(R)) : 0.0f;
+  const float inv = ok ? __fdiv_rn(static_cast<float>(R), m) : 0.0f;
+  uint32_t c[32];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    U4 r = philox4x32(block_idx, static_cast<uint32_t>(lane * 4 + q), tag, step, k0, k1);
+    const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int m8 = 0; m8 < 8; ++m8) {
+      const uint32_t r16 = (m8 & 1) ? (rw[m8 >> 1] >> 16) : (rw[m8 >> 1] & 0xFFFFu);
+      const float u = __fmul_rn(__fadd_rn(static_cast<float>(r16), 0.5f), 1.0f / 65536.0f);
+      const float t = __fadd_rn(__fmul_rn(y[8 * q + m8], inv), u);
+      int code = static_cast<int>(floorf(t));
+      code = max(-R, min(R, code)) + R;
+      c[8 * q + m8] = static_cast<uint32_t>(code);
+    }
+  }
+  pack_codes<B>(c, w);
+  return scale;
+}
+
+template <int B>
+__device__ __forceinline__ void dequantize_block(const uint32_t (&w)[B], float scale, float (&y)[32]) {
+  constexpr int R = (1 << (B - 1)) - 1;
+#pragma unroll
+  for (int k = 0; k < 32; ++k)
+    y[k] = __fmul_rn(static_cast<float>(static_cast<int>(unpack_code<B>(w, k)) - R), scale);
+}
+
+template <int B>
+__device__ __forceinline__ void dequantize_add_block(const uint32_t (&w)[B], float scale, float (&y)[32]) {
+  constexpr int R = (1 << (B - 1)) - 1;
+#pragma unroll
+  for (int k = 0; k < 32; ++k)
+    y[k] = __fadd_rn(y[k], __fmul_rn(static_cast<float>(static_cast<int>(unpack_code<B>(w, k)) - R), scale));
+}
+
+}  // namespace dq

@@ -1,0 +1,40 @@
+// Parameters of the persistent compressed all-reduce kernel (one struct per rank).
+#pragma once
+#include <cstdint>
+
+namespace dq {
+
+constexpr int kMaxWorld = 8;
+constexpr int kMaxSteps = 32;
+constexpr int kStepInts = 8;
+
+// local operand / result of a step: keep in sync with parallel/schedules.py
+enum : int { kLocalRaw = 0, kLocalWs = 1 };
+enum : int { kOutSend = 0, kOutStore = 1, kOutFinal = 2, kOutDecode = 3 };
+
+// error codes left in status[0]; status[1] = (step << 16) | cta, status[2] = slot
+enum : uint32_t { kOk = 0, kErrWaitTimeout = 1, kErrBadProgram = 2 };
+
+struct ARParams {
+  void* bucket;        // this rank's gradient bucket: input, scratch for partial sums, and output
+  float* tail_ws;      // 1024 floats: stands in for a partial last block when it holds partial sums
+  long long n;         // elements in the bucket
+  int nblocks;         // ceil(n / 1024)
+  int blocks_per_shard;
+  int world, rank;
+  int nsteps;
+  uint8_t* mail[kMaxWorld];    // every rank's mailbox (peer mapped); mail[rank] is local
+  uint32_t* flags[kMaxWorld];  // every rank's flag array
+  unsigned long long slot_stride;  // bytes between consecutive slots of a mailbox
+  unsigned long long scales_off;   // byte offset of the scales inside a slot
+  uint32_t flag_base;              // first flag word of this collective's slot set
+  uint32_t epoch;                  // value a flag must reach
+  uint32_t seed_lo, seed_hi, step, bucket_id;
+  float finish_scale;              // post_scale / 32 applied by the inverse rotation
+  unsigned long long timeout_ns;   // budget of each wait on a flag
+  uint32_t* status;                // 4 words, local
+  int no_transmit;                 // debug: run the maths, skip remote payload stores
+  int steps[kMaxSteps][kStepInts];
+};
+
+}  // namespace dq

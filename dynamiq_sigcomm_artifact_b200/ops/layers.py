@@ -1,0 +1,179 @@
+"""Autograd wrappers of the model-side kernels (csrc/kernels/model_ops.cu).
+
+The reference uses Hugging Face's LayerNorm / RMSNorm / rotary modules and
+``torch.optim.AdamW`` (testbed_evaluation/train_llm_causal.py:490-497,614).  These classes have
+the same maths; on CUDA tensors they call the native kernels, on CPU tensors (tests without a
+GPU) they fall back to the equivalent PyTorch expression.
+"""
+from __future__ import annotations
+
+from typing import Iterable, List
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import require
+
+
+class _NormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b, eps: float, rms: bool):
+        ops = require()
+        xc = x.contiguous()
+        y, mean, rstd = ops.norm_fwd(xc, w, b, eps, rms)
+        ctx.save_for_backward(xc, w, mean, rstd)
+        ctx.rms = rms
+        ctx.has_bias = b is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        ops = require()
+        x, w, mean, rstd = ctx.saved_tensors
+        dx, dw, db = ops.norm_bwd(dy.contiguous(), x, w, mean, rstd, ctx.rms)
+        return dx, dw, (db if ctx.has_bias else None), None, None
+
+
+class LayerNorm(nn.Module):
+    """LayerNorm over the last dimension with fp32 parameters and statistics."""
+
+    def __init__(self, hidden: int, eps: float = 1e-5):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(hidden))
+        self.bias = nn.Parameter(torch.zeros(hidden))
+        self.eps = eps
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.is_cuda:
+            return _NormFn.apply(x, self.weight.float(), self.bias.float(), self.eps, False)
+        return F.layer_norm(x.float(), (x.shape[-1],), self.weight.float(), self.bias.float(), self.eps).to(x.dtype)
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, hidden: int, eps: float = 1e-5):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(hidden))
+        self.eps = eps
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.is_cuda:
+            return _NormFn.apply(x, self.weight.float(), None, self.eps, True)
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps) * self.weight.float()).to(x.dtype)
+
+
+class _RopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        ctx.save_for_backward(cos, sin)
+        return require().rope(x.contiguous(), cos, sin, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin = ctx.saved_tensors
+        return require().rope(dy.contiguous(), cos, sin, True), None, None
+
+
+def rope_tables(seq_len: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin [S, D/2] in fp32 for the rotate-half convention."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float64) / head_dim))
+    ang = torch.outer(torch.arange(seq_len, dtype=torch.float64), inv)
+    return ang.cos().float().to(device).contiguous(), ang.sin().float().to(device).contiguous()
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x: [B, S, heads, D]; rotate-half: (x1 cos - x2 sin, x2 cos + x1 sin)."""
+    if x.is_cuda:
+        return _RopeFn.apply(x, cos, sin)
+    S, D = x.shape[1], x.shape[3]
+    c, s = cos[:S].view(1, S, 1, D // 2), sin[:S].view(1, S, 1, D // 2)
+    x1, x2 = x.float()[..., : D // 2], x.float()[..., D // 2:]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).to(x.dtype)
+
+
+class FusedAdamW(torch.optim.Optimizer):
+    """AdamW with one kernel launch per step for all parameters of a dtype pair (fp32 state)."""
+
+    CHUNK = 4096
+
+    def __init__(self, params: Iterable, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 0.01):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+        self._tables = {}
+        self._step = 0
+
+    def _table(self, gi: int, group) -> list:
+        """Per (param dtype, grad dtype) metadata; rebuilt when a gradient buffer moves."""
+        ps: List[torch.Tensor] = [p for p in group["params"] if p.grad is not None]
+        key = tuple((p.data_ptr(), p.grad.data_ptr()) for p in ps)
+        cached = self._tables.get(gi)
+        if cached is not None and cached[0] == key:
+            return cached[1]
+        buckets = {}
+        for p in ps:
+            st = self.state[p]
+            if "exp_avg" not in st:
+                st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.contiguous_format)
+                st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.contiguous_format)
+            if not (p.is_contiguous() and p.grad.is_contiguous()):
+                raise ValueError("FusedAdamW needs contiguous parameters and gradients")
+            buckets.setdefault((p.dtype, p.grad.dtype), []).append(p)
+        out = []
+        for (pd, gd), plist in buckets.items():
+            dev = plist[0].device
+            rows, numel, starts, c = [], [], [], 0
+            for p in plist:
+                st = self.state[p]
+                rows.append([p.data_ptr(), p.grad.data_ptr(), st["exp_avg"].data_ptr(), st["exp_avg_sq"].data_ptr()])
+                numel.append(p.numel())
+                starts.append(c)
+                c += (p.numel() + self.CHUNK - 1) // self.CHUNK
+            out.append((torch.tensor(rows, dtype=torch.int64, device=dev),
+                        torch.tensor(numel, dtype=torch.int64, device=dev),
+                        torch.tensor(starts, dtype=torch.int32, device=dev), c,
+                        pd == torch.bfloat16, gd == torch.bfloat16, plist))
+        self._tables[gi] = (key, out)
+        return out
+
+    @torch.no_grad()
+    def step(self, closure=None, grad_scale: float = 1.0):
+        loss = closure() if closure is not None else None
+        self._step += 1
+        for gi, group in enumerate(self.param_groups):
+            b1, b2 = group["betas"]
+            params = [p for p in group["params"] if p.grad is not None]
+            if not params:
+                continue
+            if params[0].is_cuda:
+                ops = require()
+                for table, numel, starts, chunks, pbf, gbf, _ in self._table(gi, group):
+                    ops.adamw_step(table, numel, starts, chunks, pbf, gbf, group["lr"], b1, b2, group["eps"],
+                                   group["weight_decay"], self._step, grad_scale)
+            else:
+                for p in params:
+                    st = self.state[p]
+                    if "exp_avg" not in st:
+                        st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+                        st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+                    g = p.grad.float() * grad_scale
+                    st["exp_avg"].mul_(b1).add_(g, alpha=1 - b1)
+                    st["exp_avg_sq"].mul_(b2).addcmul_(g, g, value=1 - b2)
+                    bc1, bc2 = 1 - b1 ** self._step, 1 - b2 ** self._step
+                    pf = p.float()
+                    pf.mul_(1 - group["lr"] * group["weight_decay"])
+                    pf.addcdiv_(st["exp_avg"], (st["exp_avg_sq"] / bc2).sqrt_().add_(group["eps"]),
+                                value=-group["lr"] / bc1)
+                    p.copy_(pf)
+        return loss
+
+    def state_dict(self):
+        d = super().state_dict()
+        d["fused_step"] = self._step
+        return d
+
+    def load_state_dict(self, d):
+        d = dict(d)
+        self._step = d.pop("fused_step", 0)
+        super().load_state_dict(d)
+        self._tables.clear()

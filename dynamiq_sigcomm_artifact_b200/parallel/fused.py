@@ -1,0 +1,261 @@
+"""Host side of the fused compressed all-reduce: buffer layout, plans and launches.
+
+``FusedAllreduce`` is the multi-GPU engine used by the DDP hooks: it owns one symmetric
+buffer per rank (mailbox slots, flags, status word, tail scratch), builds the step program of
+the chosen topology once, and launches ``torch.ops.dq.fused_allreduce`` - one cooperative
+kernel per bucket - on the caller's stream.  ``LocalCluster`` runs all ranks of a collective
+in one launch on one GPU (each rank's mailbox is an ordinary tensor); the standalone codec
+operators and the single-GPU tests are built on it.
+
+Reference counterparts: the ring / butterfly callbacks and their per-tag send/recv buffers
+(testbed_evaluation/new_comm_hooks/utils.py:78-226), ``RingRdmaExchange``
+(ring_rdma.py:257-383) and the compressor objects' kernel calls
+(utils_aggregation.py:369-569).
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import ops as _ops
+from . import schedules as sch
+from .symm import SymmetricBuffer
+
+BLOCK = 1024
+
+
+class CollectiveTimeout(RuntimeError):
+    """A device-side wait ran out of budget; the kernel returned instead of hanging."""
+
+
+def _align(x: int, a: int) -> int:
+    return (x + a - 1) // a * a
+
+
+@dataclasses.dataclass(frozen=True)
+class Layout:
+    """Geometry of one collective's slots for (numel, world, bits)."""
+
+    numel: int
+    world: int
+    bits: int
+
+    @property
+    def nblocks(self) -> int:
+        return (self.numel + BLOCK - 1) // BLOCK
+
+    @property
+    def blocks_per_shard(self) -> int:
+        return sch.shard_blocks(self.nblocks, self.world)
+
+    @property
+    def scales_off(self) -> int:
+        return _align(self.blocks_per_shard * 128 * self.bits, 16)
+
+    @property
+    def slot_stride(self) -> int:
+        return _align(self.scales_off + 4 * self.blocks_per_shard, 256)
+
+
+def program_tensor(rank: int, world: int, topology: str) -> torch.Tensor:
+    prog = sch.build_program(rank, world, topology)
+    return torch.tensor([s.as_ints() for s in prog], dtype=torch.int32)
+
+
+STATUS_MESSAGES = {1: "timed out waiting for a peer's flag", 2: "malformed step program"}
+
+
+def decode_status(words: Sequence[int]) -> Optional[str]:
+    code = int(words[0])
+    if code == 0:
+        return None
+    step, cta = (int(words[1]) >> 16) & 0xFFFF, int(words[1]) & 0xFFFF
+    return f"{STATUS_MESSAGES.get(code, f'error {code}')} (program step {step}, CTA {cta}, slot {int(words[2])})"
+
+
+class FusedAllreduce:
+    """Compressed all-reduce (mean) over NVLink for the ranks of a process group."""
+
+    def __init__(self, group=None, max_numel: int = 32 << 20, ctas: int = 64, threads: int = 256,
+                 timeout_ms: int = 2000, validate: bool = True):
+        self.ops = _ops.require()
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.ctas, self.threads = int(ctas), int(threads)
+        self.timeout_ns = int(timeout_ms) * 1_000_000
+        self.validate = validate
+        self.device = torch.cuda.current_device()
+        self.epoch = 0
+        self._programs: Dict[str, torch.Tensor] = {}
+        self.buf: Optional[SymmetricBuffer] = None
+        self.max_numel = 0
+        self._alloc(max_numel)
+
+    # -- buffers ---------------------------------------------------------------------------
+    def _alloc(self, max_numel: int) -> None:
+        if self.buf is not None:
+            self.buf.close()
+        self.max_numel = int(max_numel)
+        self.nslots = sch.n_slots(self.world, "ring")  # same count for every topology
+        worst = Layout(self.max_numel, self.world, 8)
+        self.set_bytes = _align(self.nslots * worst.slot_stride, 4096)
+        self.flag_words_per_set = self.nslots * self.ctas
+        self.off_flags = 2 * self.set_bytes
+        self.off_status = self.off_flags + _align(2 * self.flag_words_per_set * 4, 4096)
+        self.off_tail = self.off_status + 256
+        total = self.off_tail + BLOCK * 4
+        self.buf = SymmetricBuffer(total, group=self.group, device=self.device, validate=self.validate)
+        self._status_view = self.buf.local()[self.off_status: self.off_status + 16].view(torch.int32)
+
+    def ensure_capacity(self, numel: int) -> None:
+        """Grow the symmetric buffers (collective call: every rank must see the same sizes)."""
+        if numel > self.max_numel:
+            self._alloc(max(numel, int(self.max_numel * 1.5)))
+
+    def program(self, topology: str) -> torch.Tensor:
+        if topology not in self._programs:
+            self._programs[topology] = program_tensor(self.rank, self.world, topology)
+        return self._programs[topology]
+
+    # -- the collective --------------------------------------------------------------------
+    def allreduce_(self, bucket: torch.Tensor, bits: int, topology: str = "ring", seed: int = 0, step: int = 0,
+                   bucket_id: int = 0, no_transmit: bool = False) -> torch.Tensor:
+        """In-place mean all-reduce of a flat fp32/bf16 CUDA tensor on the current stream."""
+        if self.world == 1:
+            return bucket
+        self.ensure_capacity(bucket.numel())
+        lay = Layout(bucket.numel(), self.world, bits)
+        self.epoch += 1
+        parity = self.epoch & 1
+        mail = [p + parity * self.set_bytes for p in self.buf.ptrs]
+        flags = [p + self.off_flags for p in self.buf.ptrs]
+        self.ops.fused_allreduce(
+            bucket, self.program(topology), mail, flags, self.set_bytes, 2 * self.flag_words_per_set, self.nslots,
+            self.buf.local_ptr + self.off_status, self.buf.local_ptr + self.off_tail, self.rank, self.world, bits,
+            self.ctas, self.threads, lay.blocks_per_shard, lay.slot_stride, lay.scales_off,
+            parity * self.flag_words_per_set, self.epoch, seed, step, bucket_id, 1.0 / self.world, self.timeout_ns,
+            no_transmit)
+        return bucket
+
+    def check(self) -> None:
+        """Raise :class:`CollectiveTimeout` if any kernel so far gave up on a wait (synchronises)."""
+        words = self._status_view.cpu().tolist()
+        msg = decode_status(words)
+        if msg is not None:
+            self._status_view.zero_()
+            raise CollectiveTimeout(f"rank {self.rank}: {msg}")
+
+    def state_dict(self) -> dict:
+        return {"epoch": self.epoch}
+
+    def close(self) -> None:
+        if self.buf is not None:
+            self.buf.close()
+            self.buf = None
+
+
+class LocalCluster:
+    """All ranks of a collective on one GPU, one cooperative launch (blockIdx.y = rank)."""
+
+    def __init__(self, world: int, max_numel: int, ctas: int = 8, threads: int = 256, device="cuda",
+                 timeout_ms: int = 1000):
+        self.ops = _ops.require()
+        self.world, self.ctas, self.threads = world, ctas, threads
+        self.device = torch.device(device)
+        self.timeout_ns = timeout_ms * 1_000_000
+        self.nslots = sch.n_slots(world, "ring")
+        worst = Layout(max_numel, world, 8)
+        self.max_numel = max_numel
+        self.mailbox_bytes = self.nslots * worst.slot_stride
+        self.mail = [torch.zeros(self.mailbox_bytes, dtype=torch.uint8, device=self.device) for _ in range(world)]
+        self.flags = [torch.zeros(self.nslots * ctas, dtype=torch.int32, device=self.device) for _ in range(world)]
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.tail_ws = torch.zeros(world, BLOCK, dtype=torch.float32, device=self.device)
+        self.epoch = 0
+
+    def run(self, buckets: List[torch.Tensor], programs: torch.Tensor, bits: int, seed: int = 0, step: int = 0,
+            bucket_id: int = 0, post_scale: Optional[float] = None, no_transmit: bool = False,
+            preset_flags: bool = False) -> None:
+        lay = Layout(buckets[0].numel(), self.world, bits)
+        assert buckets[0].numel() <= self.max_numel
+        self.epoch += 1
+        if preset_flags:
+            for f in self.flags:
+                f.fill_(self.epoch)
+        self.ops.fused_allreduce_local(
+            buckets, programs, self.mail, self.flags, self.status, self.tail_ws, self.nslots, bits, self.ctas,
+            self.threads, lay.blocks_per_shard, lay.slot_stride, lay.scales_off, 0, self.epoch, seed, step, bucket_id,
+            (1.0 / self.world) if post_scale is None else post_scale, self.timeout_ns, no_transmit)
+
+    def allreduce_(self, buckets: List[torch.Tensor], bits: int, topology: str = "ring", **kw) -> List[torch.Tensor]:
+        progs = torch.stack([program_tensor(r, self.world, topology) for r in range(self.world)])
+        self.run(buckets, progs, bits, **kw)
+        return buckets
+
+    def check(self) -> None:
+        msg = decode_status(self.status.cpu().tolist())
+        if msg is not None:
+            self.status.zero_()
+            raise CollectiveTimeout(msg)
+
+    def slot(self, rank: int, slot: int, lay: Layout, nblocks: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(code words [nblocks, bits, 32] int32, scales [nblocks] fp32) of one received message."""
+        base = slot * lay.slot_stride
+        codes = self.mail[rank][base: base + nblocks * 128 * lay.bits].view(torch.int32).view(nblocks, lay.bits, 32)
+        scales = self.mail[rank][base + lay.scales_off: base + lay.scales_off + 4 * nblocks].view(torch.float32)
+        return codes, scales
+
+
+class RhtCodec:
+    """Standalone rotation-codec operators on one GPU (compress / decompress / hop).
+
+    The equivalents of ``eden_utils.scaling_compress / scaling_decompress / scaling_dec_comp``
+    (cuda_kernels/src/srrcomp/eden_utils/eden_utils.cpp:133-219) for the `rht` family; each is
+    a one-step program of the fused kernel.  Messages are (code words int32 [nb, bits, 32],
+    scales fp32 [nb]).
+    """
+
+    def __init__(self, bits: int, max_numel: int, seed: int = 0, ctas: int = 32, threads: int = 256, device="cuda"):
+        self.bits, self.seed = bits, seed
+        self.cluster = LocalCluster(1, max_numel, ctas=ctas, threads=threads, device=device)
+
+    def _prog(self, step: sch.Step) -> torch.Tensor:
+        return torch.tensor([[step.as_ints()]], dtype=torch.int32)
+
+    def _put(self, slot: int, msg, lay: Layout) -> None:
+        codes, scales = msg
+        c, s = self.cluster.slot(0, slot, lay, codes.shape[0])
+        c.copy_(codes)
+        s.copy_(scales)
+
+    def compress(self, x: torch.Tensor, step: int = 0, bucket_id: int = 0, tag: int = sch.TAG_ENCODE):
+        lay = Layout(x.numel(), 1, self.bits)
+        work = x.detach().clone().reshape(-1)
+        self.cluster.run([work], self._prog(sch.Step(shard=0, out=sch.OUT_SEND, dst=0, send_slot=0, tag=tag)),
+                         self.bits, seed=self.seed, step=step, bucket_id=bucket_id)
+        c, s = self.cluster.slot(0, 0, lay, lay.nblocks)
+        return c.clone(), s.clone()
+
+    def decompress(self, msg, numel: int, step: int = 0, bucket_id: int = 0, post_scale: float = 1.0,
+                   dtype=torch.float32) -> torch.Tensor:
+        lay = Layout(numel, 1, self.bits)
+        self._put(0, msg, lay)
+        out = torch.empty(numel, dtype=dtype, device=self.cluster.device)
+        self.cluster.run([out], self._prog(sch.Step(shard=0, recv_slot=0, nrecv=1, out=sch.OUT_DECODE)), self.bits,
+                         seed=self.seed, step=step, bucket_id=bucket_id, post_scale=post_scale, preset_flags=True)
+        return out
+
+    def dec_comp(self, msg, x_local: torch.Tensor, step: int = 0, bucket_id: int = 0, tag: int = sch.TAG_ENCODE + 1):
+        """decode(msg) + rotate(x_local), re-encoded: one ring hop."""
+        lay = Layout(x_local.numel(), 1, self.bits)
+        self._put(0, msg, lay)
+        work = x_local.detach().clone().reshape(-1)
+        self.cluster.run([work], self._prog(sch.Step(shard=0, recv_slot=0, nrecv=1, out=sch.OUT_SEND, dst=0,
+                                                     send_slot=1, tag=tag)),
+                         self.bits, seed=self.seed, step=step, bucket_id=bucket_id, preset_flags=True)
+        c, s = self.cluster.slot(0, 1, lay, lay.nblocks)
+        return c.clone(), s.clone()

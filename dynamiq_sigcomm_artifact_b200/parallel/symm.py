@@ -1,0 +1,123 @@
+"""Peer-mapped ("symmetric") device buffers for one NVSwitch box.
+
+Every rank allocates the same-sized buffer through the native launcher
+(csrc/launcher/symm.cpp), publishes its IPC handle with ``all_gather_object`` and maps all
+the others; kernels then address any rank's buffer by pointer.  This replaces the
+reference's transport bring-up: RankMeta all-gather, topology validation and the
+sender/receiver constructors of ``RingRdmaManager``
+(testbed_evaluation/new_comm_hooks/ring_rdma.py:386-494) and ``ButterflyRdmaManager``
+(butterfly_rdma.py:115-285).
+"""
+from __future__ import annotations
+
+import dataclasses
+import socket
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import ops as _ops
+
+
+@dataclasses.dataclass
+class RankMeta:
+    """What each rank publishes about itself (cf. RankMeta in ring_rdma.py:80-100)."""
+
+    rank: int
+    host: str
+    device: int
+    device_name: str
+    handle: bytes
+
+
+class TopologyError(RuntimeError):
+    pass
+
+
+def p2p_matrix() -> torch.Tensor:
+    """[ndev, ndev, 3] int32: (peer access, performance rank, native atomics)."""
+    return _ops.require().topology()
+
+
+def nvlink_summary(device: int) -> dict:
+    """NVLink state of one GPU through NVML (read-only); empty when NVML is unavailable."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(device)
+        active = 0
+        for link in range(18):
+            try:
+                if pynvml.nvmlDeviceGetNvLinkState(h, link):
+                    active += 1
+            except pynvml.NVMLError:
+                break
+        return {"device": device, "name": pynvml.nvmlDeviceGetName(h), "nvlink_active_links": active}
+    except Exception:  # NVML missing or refused: the P2P matrix is still checked
+        return {}
+
+
+class SymmetricBuffer:
+    """One allocation per rank of a group, all of them mapped into this process."""
+
+    def __init__(self, nbytes: int, group=None, device: Optional[int] = None, validate: bool = True):
+        self.ops = _ops.require()
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = torch.cuda.current_device() if device is None else device
+        self.nbytes = int(nbytes)
+        self.local_ptr, handle = self.ops.symm_alloc(self.device, self.nbytes)
+        meta = RankMeta(self.rank, socket.gethostname(), self.device, torch.cuda.get_device_name(self.device),
+                        bytes(handle.numpy().tobytes()))
+        metas: List[Optional[RankMeta]] = [None] * self.world
+        if self.world > 1:
+            dist.all_gather_object(metas, meta, group=group)
+        else:
+            metas = [meta]
+        self.metas = metas
+        if validate:
+            self._validate()
+        self.ptrs: List[int] = []
+        for r, m in enumerate(metas):
+            if r == self.rank:
+                self.ptrs.append(self.local_ptr)
+            else:
+                h = torch.frombuffer(bytearray(m.handle), dtype=torch.uint8).clone()
+                self.ptrs.append(self.ops.symm_open(self.device, h))
+        if self.world > 1:
+            dist.barrier(group=group)
+        self._closed = False
+
+    def _validate(self) -> None:
+        hosts = {m.host for m in self.metas}
+        if len(hosts) != 1:
+            raise TopologyError(f"symmetric buffers need all ranks on one host, got {sorted(hosts)}")
+        devs = [m.device for m in self.metas]
+        if len(set(devs)) != len(devs):
+            raise TopologyError(f"two ranks share a GPU: {devs}")
+        mat = p2p_matrix()
+        for m in self.metas:
+            if m.device != self.device and not int(mat[self.device, m.device, 0]):
+                raise TopologyError(f"GPU {self.device} cannot access GPU {m.device} peer-to-peer")
+
+    def local(self) -> torch.Tensor:
+        """This rank's buffer as a uint8 tensor (no ownership)."""
+        return self.ops.wrap_ptr(self.local_ptr, self.nbytes, self.device)
+
+    def close(self) -> None:
+        if self._closed:
+            return
+        self._closed = True
+        torch.cuda.synchronize(self.device)
+        if self.world > 1 and dist.is_initialized():
+            try:
+                dist.barrier(group=self.group)
+            except Exception:
+                pass
+        for r, p in enumerate(self.ptrs):
+            if r != self.rank:
+                self.ops.symm_close(p)
+        self.ops.symm_free(self.local_ptr)
