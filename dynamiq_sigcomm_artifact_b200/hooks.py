@@ -1,0 +1,250 @@
+"""DDP communication hooks with the reference's contract.
+
+Contract (testbed_evaluation/new_comm_hooks/comm_hooks.py:681-900, smoke_test_new_comm_hooks.py:303-326):
+``hook(state, bucket) -> Future[Tensor]`` where ``state`` is a *list holding one dict*, the
+future's value is the bucket's flat tensor holding the **mean** gradient, the caller advances
+``state["batch_idx"]`` before each backward, and the first steps (``batch_idx`` 0 and 1 in
+the reference) are served by the library all-reduce while DDP settles its buckets.
+
+What differs: the custom path is one fused kernel per bucket launched on a side stream
+(so bucket k's collective overlaps the backward of bucket k+1) instead of Python-driven
+ring steps executed synchronously in the reducer callback (comm_hooks.py:892-900); buckets
+can therefore stay at DDP's 25 MB instead of one 4000 MiB bucket (train_llm_causal.py:216,416).
+On CPU tensors (gloo) the same programs run through ``parallel/cpu_backend.py``.
+"""
+import time
+from typing import Callable, Dict, List, Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from .config import DynamiqConfig, MethodSpec, parse_method
+
+
+class HookState(dict):
+    """The mutable dict the hooks read; ``[state]`` is what ``register_comm_hook`` receives.
+
+    Keys kept from the reference: ``batch_idx``, ``params`` (scratch), ``args``.  New keys:
+    ``spec``, ``config``, ``engine``, ``stats``.
+    """
+
+    def __init__(self, config: DynamiqConfig, group=None):
+        super().__init__()
+        self["config"] = config
+        self["spec"] = config.spec()
+        self["batch_idx"] = 0
+        self["params"] = {}
+        self["args"] = config
+        self["group"] = group
+        self["engine"] = None
+        self["comm_stream"] = None
+        self["auto_step"] = True
+        self["stats"] = {"buckets": {}, "collectives": 0, "wire_bytes": 0, "err_sq": 0.0, "ref_sq": 0.0}
+        self["bit_policy"] = None
+        self["_seen_first"] = False
+
+    # -- step accounting -------------------------------------------------------------------
+    def begin_step(self, batch_idx: Optional[int] = None) -> None:
+        """Call before each backward (the reference's ``state["batch_idx"] += 1``)."""
+        self["auto_step"] = False
+        self["batch_idx"] = self["batch_idx"] + 1 if batch_idx is None else int(batch_idx)
+
+    def _auto_advance(self, bucket_index: int) -> None:
+        if self["auto_step"] and bucket_index == 0:
+            if self["_seen_first"]:
+                self["batch_idx"] += 1
+            self["_seen_first"] = True
+
+    # -- persistence (hook state is never saved by the reference; see checkpoint.py) ---------
+    def state_dict(self) -> dict:
+        d = {"batch_idx": self["batch_idx"], "method": self["config"].method, "seed": self["config"].seed,
+             "stats": {k: v for k, v in self["stats"].items() if k != "buckets"}}
+        if self["bit_policy"] is not None:
+            d["bit_policy"] = self["bit_policy"].state_dict()
+        for k in ("bitrate_u",):
+            if k in self["params"]:
+                d[k] = self["params"][k]
+        return d
+
+    def load_state_dict(self, d: dict) -> None:
+        self["batch_idx"] = int(d["batch_idx"])
+        self["auto_step"] = False
+        if "bit_policy" in d and self["bit_policy"] is not None:
+            self["bit_policy"].load_state_dict(d["bit_policy"])
+        for k in ("bitrate_u",):
+            if k in d:
+                self["params"][k] = d[k]
+
+    def close(self) -> None:
+        if self["engine"] is not None:
+            self["engine"].close()
+            self["engine"] = None
+
+
+def _unwrap(state) -> HookState:
+    return state[0] if isinstance(state, (list, tuple)) else state
+
+
+def _world(state: HookState) -> int:
+    return dist.get_world_size(state["group"]) if dist.is_initialized() else 1
+
+
+def _library_mean(state: HookState, buf: torch.Tensor, wire_dtype: Optional[torch.dtype] = None
+                  ) -> torch.futures.Future:
+    """Mean through the library all-reduce, optionally casting the wire to `wire_dtype`."""
+    world = _world(state)
+    if world == 1:
+        fut = torch.futures.Future()
+        fut.set_result(buf)
+        return fut
+    if wire_dtype is None or wire_dtype == buf.dtype:
+        buf.div_(world)
+        return dist.all_reduce(buf, group=state["group"], async_op=True).get_future().then(lambda f: f.value()[0])
+    wire = buf.to(wire_dtype).div_(world)
+    fut = dist.all_reduce(wire, group=state["group"], async_op=True).get_future()
+
+    def back(f):
+        buf.copy_(f.value()[0])
+        return buf
+
+    return fut.then(back)
+
+
+def _done(buf: torch.Tensor) -> torch.futures.Future:
+    fut = torch.futures.Future()
+    fut.set_result(buf)
+    return fut
+
+
+def _engine(state: HookState):
+    """The NVLink engine, created on first use (a collective call: every rank gets here together)."""
+    if state["engine"] is None:
+        from .parallel.fused import FusedAllreduce
+
+        cfg: DynamiqConfig = state["config"]
+        state["engine"] = FusedAllreduce(group=state["group"], max_numel=cfg.max_bucket_mb * (1 << 20) // 4,
+                                         ctas=cfg.comm_ctas, threads=cfg.comm_threads,
+                                         timeout_ms=cfg.wait_timeout_ms, validate=cfg.validate_topology)
+        state["comm_stream"] = torch.cuda.Stream(priority=-1)
+    return state["engine"]
+
+
+def _bucket_bits(state: HookState, index: int, buf: torch.Tensor) -> int:
+    policy = state["bit_policy"]
+    return policy.bits_for(index, buf) if policy is not None else state["spec"].bits
+
+
+def _rht_allreduce(state: HookState, bucket) -> torch.futures.Future:
+    spec: MethodSpec = state["spec"]
+    cfg: DynamiqConfig = state["config"]
+    buf = bucket.buffer()
+    index, step = bucket.index(), int(state["batch_idx"])
+    world = _world(state)
+    if world == 1 or buf.numel() == 0:
+        return _done(buf)
+    bits = _bucket_bits(state, index, buf)
+    st = state["stats"]
+    st["collectives"] += 1
+    st["buckets"][index] = {"numel": buf.numel(), "bits": bits}
+    exact = None
+    if cfg.measure_comm_error:
+        exact = buf.detach().clone().float()
+        dist.all_reduce(exact, group=state["group"])
+        exact.div_(world)
+    if buf.is_cuda:
+        eng = _engine(state)
+        eng.ensure_capacity(buf.numel())
+        if cfg.overlap:
+            stream = state["comm_stream"]
+            stream.wait_stream(torch.cuda.current_stream())
+            fut = torch.futures.Future(devices=[buf.device])
+            with torch.cuda.stream(stream):
+                eng.allreduce_(buf, bits, spec.topology, cfg.seed, step, index, no_transmit=spec.compute_only)
+                buf.record_stream(stream)
+                if exact is not None:
+                    _account_error(state, buf, exact)
+                fut.set_result(buf)
+            return fut
+        eng.allreduce_(buf, bits, spec.topology, cfg.seed, step, index, no_transmit=spec.compute_only)
+    else:
+        from .parallel.cpu_backend import allreduce_gloo
+
+        out = allreduce_gloo(buf.detach().float().numpy(), bits, spec.topology, cfg.seed, step, index,
+                             group=state["group"])
+        buf.copy_(torch.from_numpy(out).to(buf.dtype))
+    if exact is not None:
+        _account_error(state, buf, exact)
+    return _done(buf)
+
+
+def _account_error(state: HookState, got: torch.Tensor, exact: torch.Tensor) -> None:
+    """vNMSE bookkeeping (simulations_llm/new_comm_hooks/comm_hooks.py:1167-1198)."""
+    st = state["stats"]
+    st["err_sq"] += float((got.float() - exact).pow(2).sum())
+    st["ref_sq"] += float(exact.pow(2).sum())
+
+
+def dynamiq_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
+    """`dynamiQ_*` methods: rotation codec (`rht`) or the reference's superchunk codec."""
+    state = _unwrap(state)
+    state._auto_advance(bucket.index())
+    if state["batch_idx"] < state["config"].warmup_steps:
+        return _library_mean(state, bucket.buffer())
+    if state["spec"].family == "superchunk":
+        from .parallel.superchunk import superchunk_allreduce
+
+        return superchunk_allreduce(state, bucket)
+    return _rht_allreduce(state, bucket)
+
+
+def _cast_hook(dtype: Optional[torch.dtype]) -> Callable:
+    def hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
+        state = _unwrap(state)
+        state._auto_advance(bucket.index())
+        return _library_mean(state, bucket.buffer(), dtype)
+
+    return hook
+
+
+bf16_hook = _cast_hook(torch.bfloat16)
+fp16_hook = _cast_hook(torch.float16)
+fp32_hook = _cast_hook(None)
+
+
+def select_comm_hook(method: str, topology: Optional[str] = None) -> Callable:
+    """Hook function for an ``aggregation_method`` string (train_llm_causal.py:294-314)."""
+    spec = parse_method(method, topology)
+    if spec.hook in ("dynamiq", "dynamiq_bitrate"):
+        return dynamiq_hook
+    if spec.hook == "bf16":
+        return bf16_hook
+    if spec.hook == "fp16":
+        return fp16_hook
+    if spec.hook == "fp32":
+        return fp32_hook
+    from .parallel import baselines
+
+    return {"mxfp8": baselines.mxfp8_hook, "fpx": baselines.fpx_hook, "thc": baselines.thc_hook,
+            "omnireduce": baselines.omnireduce_hook}[spec.hook]
+
+
+def build_comm_state(config: DynamiqConfig, group=None) -> List[HookState]:
+    """``[state]`` as the reference's ``build_comm_state`` returns it (train_llm_causal.py:242-286)."""
+    state = HookState(config, group)
+    spec = state["spec"]
+    if spec.hook in ("dynamiq", "dynamiq_bitrate") and spec.family == "rht" and spec.dynamic_bitrate:
+        from .bitalloc import BucketBitPolicy
+
+        state["bit_policy"] = BucketBitPolicy(spec.bits)
+    return [state]
+
+
+def register(model, method: str = "dynamiQ_aee_5bit", config: Optional[DynamiqConfig] = None, group=None,
+             **overrides) -> HookState:
+    """Register the hook for `method` on a DDP model; returns the state (call ``begin_step``)."""
+    cfg = config or DynamiqConfig.from_env(method=method, **overrides)
+    cfg.method = method
+    state_list = build_comm_state(cfg, group)
+    model.register_comm_hook(state_list, select_comm_hook(method, cfg.topology))
+    return state_list[0]

@@ -14,6 +14,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from . import require
+from ..utils import counters
 
 
 class _NormFn(torch.autograd.Function):
@@ -22,6 +23,7 @@ class _NormFn(torch.autograd.Function):
         ops = require()
         xc = x.contiguous()
         y, mean, rstd = ops.norm_fwd(xc, w, b, eps, rms)
+        counters.add("norm_fwd")
         ctx.save_for_backward(xc, w, mean, rstd)
         ctx.rms = rms
         ctx.has_bias = b is not None
@@ -32,6 +34,7 @@ class _NormFn(torch.autograd.Function):
         ops = require()
         x, w, mean, rstd = ctx.saved_tensors
         dx, dw, db = ops.norm_bwd(dy.contiguous(), x, w, mean, rstd, ctx.rms)
+        counters.add("norm_bwd", 2 if ctx.rms else 3)
         return dx, dw, (db if ctx.has_bias else None), None, None
 
 
@@ -67,11 +70,13 @@ class _RopeFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, cos, sin):
         ctx.save_for_backward(cos, sin)
+        counters.add("rope")
         return require().rope(x.contiguous(), cos, sin, False)
 
     @staticmethod
     def backward(ctx, dy):
         cos, sin = ctx.saved_tensors
+        counters.add("rope")
         return require().rope(dy.contiguous(), cos, sin, True), None, None
 
 
@@ -150,6 +155,7 @@ class FusedAdamW(torch.optim.Optimizer):
                 for table, numel, starts, chunks, pbf, gbf, _ in self._table(gi, group):
                     ops.adamw_step(table, numel, starts, chunks, pbf, gbf, group["lr"], b1, b2, group["eps"],
                                    group["weight_decay"], self._step, grad_scale)
+                    counters.add("adamw")
             else:
                 for p in params:
                     st = self.state[p]

@@ -21,6 +21,7 @@ import torch
 import torch.distributed as dist
 
 from .. import ops as _ops
+from ..utils import counters
 from . import schedules as sch
 from .symm import SymmetricBuffer
 
@@ -139,6 +140,7 @@ class FusedAllreduce:
             self.ctas, self.threads, lay.blocks_per_shard, lay.slot_stride, lay.scales_off,
             parity * self.flag_words_per_set, self.epoch, seed, step, bucket_id, 1.0 / self.world, self.timeout_ns,
             no_transmit)
+        counters.add("fused_allreduce")
         return bucket
 
     def check(self) -> None:

@@ -1,0 +1,140 @@
+"""Training engine: model + DDP + comm hook + fused optimizer, one call per step.
+
+The public entry point is :meth:`Trainer.train_step`: it takes a batch of token ids in pinned
+host memory, copies it to the device, runs forward, backward (the hook's collectives overlap
+it on a side stream), the optimizer, and returns the loss as a Python float.
+
+Reference counterpart: ``train()`` and its set-up in testbed_evaluation/train_llm_causal.py:331-394,
+398-646 (HF model in bf16, torch AdamW, LinearLR, DDP through a patched ``accelerate`` with
+``bucket_cap_mb=4000`` for DynamiQ so that the whole model is one bucket, :216,:416).  Here DDP
+is plain ``torch.nn.parallel.DistributedDataParallel`` with 25 MB buckets and
+``gradient_as_bucket_view``; compute is bf16 autocast over fp32 master weights and fp32
+gradient buckets.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+from torch.nn.parallel import DistributedDataParallel as DDP
+
+from .. import hooks
+from ..config import DynamiqConfig
+from ..models import build_model, mask_tokens
+from ..ops.layers import FusedAdamW
+
+
+@dataclass
+class TrainConfig:
+    model: str = "gpt2-small"
+    method: str = "dynamiQ_aee_5bit"
+    micro_batch: int = 8
+    seq_len: int = 1024
+    lr: float = 1e-5
+    weight_decay: float = 0.0
+    total_steps: int = 10_000
+    bucket_cap_mb: int = 25
+    seed: int = 0
+    dtype: str = "bf16"  # autocast dtype; parameters, gradients and optimizer state are fp32
+    task: str = "causal"  # causal | mlm
+    topology: Optional[str] = None
+    comm_ctas: int = 64
+    warmup_steps: int = 2
+    measure_comm_error: bool = False
+
+
+class Trainer:
+    def __init__(self, cfg: TrainConfig, device: Optional[torch.device] = None):
+        self.cfg = cfg
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        if device is None:
+            device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0))) if torch.cuda.is_available() \
+                else torch.device("cpu")
+        self.device = device
+        torch.manual_seed(cfg.seed)  # identical initial weights on every rank
+        self.model = build_model(cfg.model).to(device)
+        self.state = None
+        if self.world > 1:
+            self.ddp = DDP(self.model, device_ids=[device.index] if device.type == "cuda" else None,
+                           bucket_cap_mb=cfg.bucket_cap_mb, gradient_as_bucket_view=True)
+            dcfg = DynamiqConfig.from_env(method=cfg.method, seed=cfg.seed, topology=cfg.topology,
+                                          comm_ctas=cfg.comm_ctas, warmup_steps=cfg.warmup_steps,
+                                          measure_comm_error=cfg.measure_comm_error)
+            self.state = hooks.register(self.ddp, cfg.method, config=dcfg)
+            self.net = self.ddp
+        else:
+            self.ddp = None
+            self.net = self.model
+            self._flatten_grads()
+        self.opt = FusedAdamW(self.model.parameters(), lr=cfg.lr, weight_decay=cfg.weight_decay)
+        self.sched = torch.optim.lr_scheduler.LinearLR(self.opt, start_factor=1.0, end_factor=0.0,
+                                                       total_iters=cfg.total_steps)
+        self.step_idx = 0
+        self._dev_ids = None
+        self._gen = torch.Generator(device=device).manual_seed(cfg.seed + 17 * self.rank + 1) \
+            if device.type == "cuda" else torch.Generator().manual_seed(cfg.seed + 17 * self.rank + 1)
+        self.autocast_dtype = {"bf16": torch.bfloat16, "fp32": None}[cfg.dtype]
+
+    def _flatten_grads(self) -> None:
+        """Single-process runs: all gradients live in one flat buffer, zeroed by one memset."""
+        params = [p for p in self.model.parameters() if p.requires_grad]
+        total = sum(p.numel() for p in params)
+        self._flat_grad = torch.zeros(total, dtype=torch.float32, device=self.device)
+        off = 0
+        for p in params:
+            p.grad = self._flat_grad[off: off + p.numel()].view_as(p)
+            off += p.numel()
+
+    # -- one step ------------------------------------------------------------------------
+    def train_step_device(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One optimizer step on device-resident token ids; returns the loss tensor (no sync)."""
+        cfg = self.cfg
+        if self.state is not None:
+            self.state.begin_step(self.step_idx)
+        if cfg.task == "mlm" and labels is None:
+            c = self.model.config
+            input_ids, labels = mask_tokens(input_ids, c.vocab, c.mask_token_id, self._gen)
+        elif labels is None:
+            labels = input_ids
+        if self.autocast_dtype is not None and self.device.type == "cuda":
+            with torch.autocast("cuda", dtype=self.autocast_dtype):
+                loss = self.net(input_ids, labels)
+        else:
+            loss = self.net(input_ids, labels)
+        loss.backward()
+        self.opt.step()
+        self.sched.step()
+        if self.ddp is None:
+            self._flat_grad.zero_()
+        else:
+            self.opt.zero_grad(set_to_none=False)
+        self.step_idx += 1
+        return loss.detach()
+
+    def train_step(self, input_ids_host: torch.Tensor, labels_host: Optional[torch.Tensor] = None) -> float:
+        """Public API: host batch in, loss out.  Copies the batch to the device every call."""
+        ids = input_ids_host.to(self.device, non_blocking=True)
+        lab = labels_host.to(self.device, non_blocking=True) if labels_host is not None else None
+        return float(self.train_step_device(ids, lab).item())
+
+    def tokens_per_step(self) -> int:
+        return self.cfg.micro_batch * self.cfg.seq_len * self.world
+
+    def synthetic_batch(self, pinned: bool = True) -> torch.Tensor:
+        """Token ids uniform in [0, vocab) from a seeded generator, in (pinned) host memory."""
+        g = torch.Generator().manual_seed(self.cfg.seed * 7919 + self.rank * 104729 + self.step_idx)
+        c = self.model.config
+        ids = torch.randint(0, c.vocab, (self.cfg.micro_batch, self.cfg.seq_len), generator=g, dtype=torch.int64)
+        return ids.pin_memory() if pinned and torch.cuda.is_available() else ids
+
+    def check(self) -> None:
+        if self.state is not None and self.state["engine"] is not None:
+            self.state["engine"].check()
+
+    def close(self) -> None:
+        if self.state is not None:
+            self.state.close()

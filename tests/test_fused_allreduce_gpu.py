@@ -1,0 +1,109 @@
+"""Fused compressed all-reduce kernel against the CPU oracle (all ranks emulated on one GPU)."""
+import numpy as np
+import pytest
+import torch
+
+from dynamiq_sigcomm_artifact_b200 import codec_ref as cr
+from dynamiq_sigcomm_artifact_b200.parallel import cpu_backend as cb
+from dynamiq_sigcomm_artifact_b200.parallel import schedules as sch
+from dynamiq_sigcomm_artifact_b200.utils import philox
+
+from helpers import heavy_tail_grad
+
+pytestmark = pytest.mark.gpu
+
+
+def _cluster(world, n, **kw):
+    from dynamiq_sigcomm_artifact_b200.parallel.fused import LocalCluster
+
+    return LocalCluster(world, n, **kw)
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4, 5, 6, 7, 8])
+def test_standalone_ops_match_oracle_bytes(bits):
+    from dynamiq_sigcomm_artifact_b200.parallel.fused import RhtCodec
+
+    n, seed, step, bucket = 7 * 1024 + 333, 99, 5, 3
+    x = heavy_tail_grad(n, 1)
+    x[5] = np.inf
+    x[6] = np.nan
+    codec = RhtCodec(bits, n, seed=seed, ctas=4)
+    words, scales = codec.compress(torch.from_numpy(x).cuda(), step=step, bucket_id=bucket)
+    ref = cb.RhtCodecCPU(bits, seed, step, bucket, world=1)
+    y = ref.rotate(cr.to_blocks(x))
+    codes, rscale = cr.quantize(y, bits, np.arange(y.shape[0]), ref._tag_base | sch.TAG_ENCODE, step, seed)
+    rwords = cr.pack(codes, bits)
+    assert np.array_equal(words.cpu().numpy().view(np.uint32), rwords)
+    assert np.array_equal(scales.cpu().numpy(), rscale)
+    # decode -> inverse rotation
+    out = codec.decompress((words, scales), n, step=step, bucket_id=bucket, post_scale=0.25)
+    rout = cr.rotate_inv(cr.dequantize(codes, rscale, bits), ref.signs, 0.25).reshape(-1)[:n]
+    assert np.array_equal(out.cpu().numpy(), rout)
+    # one hop: decode + add rotated local + re-encode
+    x2 = heavy_tail_grad(n, 2)
+    w2, s2 = codec.dec_comp((words, scales), torch.from_numpy(x2).cuda(), step=step, bucket_id=bucket)
+    v = (ref.rotate(cr.to_blocks(x2)) + cr.dequantize(codes, rscale, bits)).astype(np.float32)
+    c2, rs2 = cr.quantize(v, bits, np.arange(v.shape[0]), ref._tag_base | (sch.TAG_ENCODE + 1), step, seed)
+    assert np.array_equal(w2.cpu().numpy().view(np.uint32), cr.pack(c2, bits))
+    assert np.array_equal(s2.cpu().numpy(), rs2)
+
+
+@pytest.mark.parametrize("topology", sch.TOPOLOGIES)
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_collective_matches_simulator_bit_for_bit(world, topology):
+    n, bits, seed, step, bucket = 37 * 1024 + 517, 5, 1234, 7, 2
+    xs = [heavy_tail_grad(n, 10 + r) for r in range(world)]
+    want = cb.simulate_allreduce(xs, bits, topology, seed=seed, step=step, bucket=bucket)
+    cl = _cluster(world, n, ctas=6, threads=128)
+    bufs = [torch.from_numpy(x).cuda() for x in xs]
+    cl.allreduce_(bufs, bits, topology, seed=seed, step=step, bucket_id=bucket)
+    cl.check()
+    for r in range(world):
+        got = bufs[r].cpu().numpy()
+        assert np.array_equal(got, want[r]), f"rank {r}: max diff {np.abs(got - want[r]).max()}"
+    exact = np.mean(np.stack(xs).astype(np.float64), 0)
+    assert cr.nmse(bufs[0].cpu().numpy(), exact) < 0.08
+
+
+def test_collective_is_reusable_and_deterministic():
+    world, n = 4, 20 * 1024
+    cl = _cluster(world, n, ctas=4)
+    outs = []
+    for rep in range(3):
+        bufs = [torch.from_numpy(heavy_tail_grad(n, r)).cuda() for r in range(world)]
+        cl.allreduce_(bufs, 4, "butterfly", seed=5, step=1)
+        outs.append(bufs[0].clone())
+    cl.check()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+
+
+def test_bf16_bucket():
+    world, n = 4, 16 * 1024 + 64
+    xs = [torch.from_numpy(heavy_tail_grad(n, r)).cuda().bfloat16() for r in range(world)]
+    exact = torch.stack([x.float() for x in xs]).mean(0)
+    cl = _cluster(world, n, ctas=4)
+    cl.allreduce_(xs, 8, "ring", seed=3)
+    cl.check()
+    assert all(torch.equal(xs[0], x) for x in xs)
+    err = float((xs[0].float() - exact).pow(2).sum() / exact.pow(2).sum())
+    assert err < 2e-3
+
+
+def test_wait_budget_expiry_returns_an_error_status():
+    """A receive whose flag nobody sets: the kernel gives up after its budget and reports it."""
+    from dynamiq_sigcomm_artifact_b200.parallel.fused import CollectiveTimeout
+
+    n = 4 * 1024
+    cl = _cluster(1, n, ctas=2, timeout_ms=20)
+    out = torch.zeros(n, device="cuda")
+    prog = torch.tensor([[sch.Step(shard=0, recv_slot=0, nrecv=1, out=sch.OUT_DECODE).as_ints()]], dtype=torch.int32)
+    cl.run([out], prog, 4)  # flags stay at 0, epoch is 1
+    with pytest.raises(CollectiveTimeout, match="timed out"):
+        cl.check()
+    # the context is still usable and the cluster works afterwards
+    x = torch.randn(n, device="cuda")
+    cl2 = _cluster(2, n, ctas=2)
+    bufs = [x.clone(), x.clone()]
+    cl2.allreduce_(bufs, 8, "ring")
+    cl2.check()
+    assert float((bufs[0] - x).abs().max()) < 0.2

@@ -1,0 +1,80 @@
+"""DDP hook plumbing on CPU: gloo, world_size 2, one 1 Mi-element fp32 bucket, dynamiQ_aee_5bit."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from dynamiq_sigcomm_artifact_b200.config import parse_method
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, method, numel, steps, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    from argparse import Namespace
+
+    from dynamiq_sigcomm_artifact_b200.train import smoke_hooks
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        args = Namespace(aggregation_method=method, topology=None, numel=numel, steps=steps, warmup_steps=2,
+                         seed=1234, dtype="float32", device="cpu", bucket_cap_mb=4000)
+        res = smoke_hooks.run(args)
+        if rank == 0:
+            q.put(res)
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(method, numel=1 << 20, steps=4, world=2):
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, method, numel, steps, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    return q.get()
+
+
+def test_method_grammar():
+    s = parse_method("dynamiQ_aee_5bit")
+    assert (s.hook, s.family, s.bits, s.topology) == ("dynamiq", "rht", 5, "ring")
+    s = parse_method("dynamiQ_mee_5bit_dynamic_bitrate_butterfly")
+    assert (s.hook, s.family, s.lattice, s.topology, s.dynamic_bitrate) == ("dynamiq_bitrate", "superchunk", "mee",
+                                                                            "butterfly", True)
+    assert parse_method("dynamiQ_aee_4bit_fixed").thresholds == {8: 0.0, 4: 1.0, 2: 0.0}
+    assert parse_method("dynamiQ_mee_4bit").thresholds == {8: 0.05, 4: 0.60, 2: 0.35}
+    assert parse_method("MXfp8").hook == "mxfp8" and parse_method("bf16").hook == "bf16"
+    assert parse_method("fp4").fpx_format == "fp4" and parse_method("zero").bits == 0
+    assert parse_method("thc").quantization_levels == 31 and parse_method("omnireduce").hook == "omnireduce"
+    assert parse_method("dynamiQ_aee_5bit_coov").compute_only
+    with pytest.raises(ValueError):
+        parse_method("nonsense")
+
+
+def test_dynamiq_aee_5bit_ring_world2():
+    a = _run("dynamiQ_aee_5bit")
+    # steps 0,1 are the library all-reduce (exact up to fp32 rounding); 2,3 the compressed ring
+    assert max(a["nmse"][:2]) < 1e-12
+    assert all(1e-4 < e < 3e-2 for e in a["nmse"][2:]), a["nmse"]
+    assert max(a["checksum_delta"]) == 0.0
+    b = _run("dynamiQ_aee_5bit")
+    assert a["grad_sum"] == b["grad_sum"], "not bit-reproducible from the seed"
+
+
+def test_bf16_and_fp32_baselines_world2():
+    r = _run("fp32", numel=1 << 16, steps=3)
+    assert max(r["nmse"]) < 1e-12
+    r = _run("bf16", numel=1 << 16, steps=3)
+    assert 0 < max(r["nmse"]) < 1e-4
