@@ -177,6 +177,97 @@ __global__ void __launch_bounds__(kNormWarps * 32) norm_bwd_kernel(
   }
 }
 
+
+// Fast path for H <= 2048: lane owns columns lane*8 + 256*i.  Each warp walks its rows once for
+// the row statistics and once more (L1-resident) for dx, accumulating its share of dw / db in
+// registers; per-warp partial sums go to dw_part[warp] and are reduced by a second kernel in a
+// fixed order.
+template <typename T, bool RMS, int NCHUNK>
+__global__ void __launch_bounds__(kNormWarps * 32) norm_bwd_rows_kernel(
+    const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ w, const float* __restrict__ mean,
+    const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ dw_part, float* __restrict__ db_part,
+    int rows, int H) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gw = blockIdx.x * kNormWarps + warp, nw = gridDim.x * kNormWarps;
+  float adw[NCHUNK][8], adb[RMS ? 1 : NCHUNK][8];
+#pragma unroll
+  for (int i = 0; i < NCHUNK; ++i)
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      adw[i][k] = 0.f;
+      if (!RMS) adb[i][k] = 0.f;
+    }
+  for (int row = gw; row < rows; row += nw) {
+    const T* xr = x + static_cast<size_t>(row) * H;
+    const T* dr = dy + static_cast<size_t>(row) * H;
+    const float mu = RMS ? 0.f : mean[row], rs = rstd[row];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i) {
+      const int c = lane * 8 + 256 * i;
+      if (c < H) {
+        float v[8], d[8], g[8];
+        Vec8<T>::load(xr + c, v);
+        Vec8<T>::load(dr + c, d);
+        Vec8<float>::load(w + c, g);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float gdy = g[k] * d[k];
+          s1 += gdy;
+          s2 += gdy * (v[k] - mu) * rs;
+        }
+      }
+    }
+    s1 = warp_sum(s1), s2 = warp_sum(s2);
+    const float m1 = RMS ? 0.f : s1 / H, m2 = s2 / H;
+    T* dxr = dx + static_cast<size_t>(row) * H;
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i) {
+      const int c = lane * 8 + 256 * i;
+      if (c < H) {
+        float v[8], d[8], g[8], o[8];
+        Vec8<T>::load(xr + c, v);
+        Vec8<T>::load(dr + c, d);
+        Vec8<float>::load(w + c, g);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float xhat = (v[k] - mu) * rs;
+          o[k] = rs * (g[k] * d[k] - m1 - xhat * m2);
+          adw[i][k] += d[k] * xhat;
+          if (!RMS) adb[i][k] += d[k];
+        }
+        Vec8<T>::store(dxr + c, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NCHUNK; ++i) {
+    const int c = lane * 8 + 256 * i;
+    if (c < H) {
+      Vec8<float>::store(dw_part + static_cast<size_t>(gw) * H + c, adw[i]);
+      if (!RMS) Vec8<float>::store(db_part + static_cast<size_t>(gw) * H + c, adb[i]);
+    }
+  }
+}
+
+// out[c] = sum over parts; 8 row-groups per CTA combined through shared memory in a fixed order
+__global__ void __launch_bounds__(256) reduce_parts2_kernel(const float* __restrict__ part, float* __restrict__ out,
+                                                            int nparts, int H) {
+  __shared__ float sm[8][32];
+  const int c = blockIdx.x * 32 + threadIdx.x, g = threadIdx.y;
+  float s = 0.f;
+  if (c < H)
+    for (int p = g; p < nparts; p += 8) s += part[static_cast<size_t>(p) * H + c];
+  sm[g][threadIdx.x] = s;
+  __syncthreads();
+  if (g == 0 && c < H) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += sm[k][threadIdx.x];
+    out[c] = t;
+  }
+}
+
 __global__ void reduce_parts_kernel(const float* __restrict__ part, float* __restrict__ out, int nparts, int H) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= H) return;
@@ -315,11 +406,44 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> norm_bwd(at::Tensor dy, at::Tenso
   const int rows = static_cast<int>(x.numel() / H);
   at::Tensor dx = at::empty_like(x);
   auto fopt = x.options().dtype(at::kFloat);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  at::Tensor dw = at::empty({H}, fopt), db = at::empty({rms ? 0 : H}, fopt);
+  if (H <= 2048) {
+    const int grid = std::max(1, std::min((rows + kNormWarps - 1) / kNormWarps, sm_count()));
+    const int nparts = grid * kNormWarps;
+    at::Tensor dw_part = at::empty({nparts, H}, fopt), db_part = at::empty({rms ? 0 : nparts, H}, fopt);
+    const int nchunk = (H + 255) / 256;
+#define DQ_ROWS(T, RMS, NC)                                                                                        \
+  norm_bwd_rows_kernel<T, RMS, NC><<<grid, kNormWarps * 32, 0, stream>>>(                                          \
+      reinterpret_cast<const T*>(dy.data_ptr()), reinterpret_cast<const T*>(x.data_ptr()), w.data_ptr<float>(),    \
+      rms ? nullptr : mean.data_ptr<float>(), rstd.data_ptr<float>(), reinterpret_cast<T*>(dx.data_ptr()),         \
+      dw_part.data_ptr<float>(), rms ? nullptr : db_part.data_ptr<float>(), rows, H)
+#define DQ_ROWS_NC(T, RMS)                                 \
+  switch (nchunk) {                                        \
+    case 1: DQ_ROWS(T, RMS, 1); break;                     \
+    case 2: DQ_ROWS(T, RMS, 2); break;                     \
+    case 3: DQ_ROWS(T, RMS, 3); break;                     \
+    case 4: DQ_ROWS(T, RMS, 4); break;                     \
+    case 5: case 6: DQ_ROWS(T, RMS, 6); break;             \
+    default: DQ_ROWS(T, RMS, 8); break;                    \
+  }
+    if (x.scalar_type() == at::kBFloat16) {
+      if (rms) { DQ_ROWS_NC(__nv_bfloat16, true) } else { DQ_ROWS_NC(__nv_bfloat16, false) }
+    } else {
+      if (rms) { DQ_ROWS_NC(float, true) } else { DQ_ROWS_NC(float, false) }
+    }
+#undef DQ_ROWS_NC
+#undef DQ_ROWS
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    dim3 rb(32, 8);
+    reduce_parts2_kernel<<<(H + 31) / 32, rb, 0, stream>>>(dw_part.data_ptr<float>(), dw.data_ptr<float>(), nparts, H);
+    if (!rms) reduce_parts2_kernel<<<(H + 31) / 32, rb, 0, stream>>>(db_part.data_ptr<float>(), db.data_ptr<float>(), nparts, H);
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    return {dx, dw, db};
+  }
   const int grid = std::max(1, std::min((rows + kNormWarps - 1) / kNormWarps, sm_count() * 2));
   at::Tensor dw_part = at::empty({grid, H}, fopt), db_part = at::empty({rms ? 0 : grid, H}, fopt);
-  at::Tensor dw = at::empty({H}, fopt), db = at::empty({rms ? 0 : H}, fopt);
   const size_t smem = static_cast<size_t>(rms ? 1 : 2) * H * sizeof(float);
-  auto stream = at::cuda::getCurrentCUDAStream();
 #define DQ_LAUNCH(T, RMS)                                                                                          \
   do {                                                                                                             \
     C10_CUDA_CHECK(cudaFuncSetAttribute(norm_bwd_kernel<T, RMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem))); \

@@ -8,7 +8,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops.layers import LayerNorm
+from ..ops.layers import LayerNorm, fused_cross_entropy, padded_vocab_logits, shift_labels
 from .common import GeluMLP, SelfAttention, init_linear
 
 
@@ -69,10 +69,10 @@ class BertMLM(nn.Module):
         for layer in self.layers:
             x = layer(x)
         h = self.head_ln(F.gelu(self.head_dense(x)))
-        logits = F.linear(h, self.tok.weight, self.head_bias.to(h.dtype) if h.dtype != torch.float32 else self.head_bias)
         if labels is None:
-            return logits
-        return F.cross_entropy(logits.reshape(-1, logits.size(-1)).float(), labels.reshape(-1), ignore_index=-100)
+            return F.linear(h, self.tok.weight.to(h.dtype), self.head_bias.to(h.dtype))
+        logits = padded_vocab_logits(h, self.tok.weight, self.head_bias)
+        return fused_cross_entropy(logits, labels.reshape(-1), self.config.vocab)
 
 
 def mask_tokens(input_ids: torch.Tensor, vocab: int, mask_token_id: int, generator: torch.Generator | None = None,

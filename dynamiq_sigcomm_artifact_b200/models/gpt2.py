@@ -8,7 +8,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops.layers import LayerNorm
+from ..ops.layers import LayerNorm, fused_cross_entropy, padded_vocab_logits, shift_labels
 from .common import GeluMLP, SelfAttention, init_linear
 
 
@@ -60,7 +60,8 @@ class GPT2(nn.Module):
             x = x.to(torch.get_autocast_dtype(x.device.type))
         for blk in self.blocks:
             x = blk(x)
-        logits = F.linear(self.ln_f(x), self.wte.weight)
+        h = self.ln_f(x)
         if labels is None:
-            return logits
-        return F.cross_entropy(logits[:, :-1].reshape(-1, logits.size(-1)).float(), labels[:, 1:].reshape(-1))
+            return F.linear(h, self.wte.weight)
+        logits = padded_vocab_logits(h, self.wte.weight)
+        return fused_cross_entropy(logits, shift_labels(labels).reshape(-1), self.config.vocab)

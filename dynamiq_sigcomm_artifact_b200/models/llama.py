@@ -8,7 +8,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops.layers import RMSNorm, rope_tables
+from ..ops.layers import fused_cross_entropy, padded_vocab_logits, shift_labels, RMSNorm, rope_tables
 from .common import SelfAttention, SwiGLU, init_linear
 
 
@@ -68,7 +68,8 @@ class Llama(nn.Module):
         for blk in self.blocks:
             x = blk(x, cos, sin)
         w = self.embed.weight if self.lm_head is None else self.lm_head.weight
-        logits = F.linear(self.norm(x), w)
+        h = self.norm(x)
         if labels is None:
-            return logits
-        return F.cross_entropy(logits[:, :-1].reshape(-1, logits.size(-1)).float(), labels[:, 1:].reshape(-1))
+            return F.linear(h, w)
+        logits = padded_vocab_logits(h, w)
+        return fused_cross_entropy(logits, shift_labels(labels).reshape(-1), self.config.vocab)

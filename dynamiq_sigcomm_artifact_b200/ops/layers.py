@@ -97,6 +97,65 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
     return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).to(x.dtype)
 
 
+class _CrossEntropyFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, labels, vocab: int, ignore_index: int):
+        ops = require()
+        lse, rows = ops.ce_fwd(logits, labels, vocab, ignore_index)
+        counters.add("ce_fwd")
+        n_valid = (labels != ignore_index).sum().to(torch.float32).clamp_(min=1.0).view(1)
+        ctx.save_for_backward(logits, labels, lse, n_valid)
+        ctx.vocab, ctx.ignore_index = vocab, ignore_index
+        return rows.sum() / n_valid[0]
+
+    @staticmethod
+    def backward(ctx, g):
+        logits, labels, lse, n_valid = ctx.saved_tensors
+        counters.add("ce_bwd")
+        grad = require().ce_bwd(logits, labels, lse, g.to(torch.float32).reshape(1).contiguous(), n_valid, ctx.vocab,
+                                ctx.ignore_index)
+        return grad, None, None, None
+
+
+def fused_cross_entropy(logits: torch.Tensor, labels: torch.Tensor, vocab: int, ignore_index: int = -100
+                        ) -> torch.Tensor:
+    """Mean cross-entropy over rows whose label is not `ignore_index`.
+
+    `logits` is [N, Vp] with Vp >= vocab; columns >= vocab are padding.  On CUDA the backward
+    pass overwrites `logits` with its gradient (the caller must not use `logits` afterwards).
+    """
+    if logits.is_cuda:
+        return _CrossEntropyFn.apply(logits, labels.contiguous(), vocab, ignore_index)
+    return F.cross_entropy(logits[:, :vocab].float(), labels, ignore_index=ignore_index)
+
+
+def padded_vocab_logits(x: torch.Tensor, weight: torch.Tensor, bias=None, multiple: int = 128) -> torch.Tensor:
+    """x @ weight.T with the vocabulary dimension zero-padded to a multiple of `multiple`.
+
+    An unaligned vocabulary (50257, 30522) sends the projection GEMM and both of its backward
+    GEMMs down the library's unaligned legacy path; padding the bf16 copy of the weight (made
+    every step anyway under autocast) keeps the parameter shape and the maths unchanged.
+    Returns [N, Vp]; use :func:`fused_cross_entropy` with ``vocab=weight.shape[0]``.
+    """
+    V = weight.shape[0]
+    pad = (-V) % multiple
+    w = weight.to(x.dtype)
+    if pad:
+        w = F.pad(w, (0, 0, 0, pad))
+    out = x.reshape(-1, x.shape[-1]) @ w.t()
+    if bias is not None:
+        b = bias.to(x.dtype)
+        out = out + (F.pad(b, (0, pad)) if pad else b)
+    return out
+
+
+def shift_labels(labels: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
+    """Next-token targets: position t predicts labels[t+1]; the last position is ignored."""
+    out = torch.full_like(labels, ignore_index)
+    out[:, :-1] = labels[:, 1:]
+    return out
+
+
 class FusedAdamW(torch.optim.Optimizer):
     """AdamW with one kernel launch per step for all parameters of a dtype pair (fp32 state)."""
 

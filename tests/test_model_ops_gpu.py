@@ -94,3 +94,45 @@ def test_tiny_models_train_on_gpu(name):
     batch = tr.synthetic_batch()
     losses = [tr.train_step(batch) for _ in range(8)]
     assert all(l == l for l in losses) and losses[-1] < losses[0]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_cross_entropy(dtype):
+    from dynamiq_sigcomm_artifact_b200.ops.layers import fused_cross_entropy
+
+    torch.manual_seed(2)
+    N, V, Vp = 37, 1000, 1024
+    base = (torch.randn(N, Vp, device="cuda") * 3).to(dtype)
+    labels = torch.randint(0, V, (N,), device="cuda")
+    labels[::5] = -100
+    ref_in = base.float()[:, :V].clone().requires_grad_(True)
+    ref = F.cross_entropy(ref_in, labels, ignore_index=-100)
+    (ref * 2.0).backward()
+    logits = base.clone().requires_grad_(True)
+    work = logits * 1.0  # non-leaf, overwritten by the backward pass
+    loss = fused_cross_entropy(work, labels, V)
+    (loss * 2.0).backward()
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    assert abs(float(loss) - float(ref)) < tol
+    g = logits.grad.float()
+    assert torch.allclose(g[:, :V], ref_in.grad, atol=tol / 10, rtol=tol)
+    assert float(g[:, V:].abs().max()) == 0.0 and float(g[::5].abs().max()) == 0.0
+
+
+def test_padded_vocab_head_matches_plain_head():
+    from dynamiq_sigcomm_artifact_b200.ops.layers import fused_cross_entropy, padded_vocab_logits, shift_labels
+
+    torch.manual_seed(3)
+    B, S, H, V = 2, 16, 64, 1001
+    x = torch.randn(B, S, H, device="cuda", requires_grad=True)
+    w = torch.randn(V, H, device="cuda", requires_grad=True)
+    ids = torch.randint(0, V, (B, S), device="cuda")
+    loss = fused_cross_entropy(padded_vocab_logits(x, w), shift_labels(ids).reshape(-1), V)
+    loss.backward()
+    x2, w2 = x.detach().clone().requires_grad_(True), w.detach().clone().requires_grad_(True)
+    logits = F.linear(x2, w2)
+    ref = F.cross_entropy(logits[:, :-1].reshape(-1, V), ids[:, 1:].reshape(-1))
+    ref.backward()
+    assert abs(float(loss) - float(ref)) < 1e-4
+    assert torch.allclose(x.grad, x2.grad, atol=1e-4, rtol=1e-3)
+    assert torch.allclose(w.grad, w2.grad, atol=1e-4, rtol=1e-3)
