@@ -1,0 +1,211 @@
+"""Standalone all-reduce benchmark: library fp32 / bf16 against the fused compressed collectives.
+
+Multi-GPU (one rank per GPU):
+
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
+        -m dynamiq_sigcomm_artifact_b200.train.bench_allreduce --sizes-mb 1,16,256 --bits 4,5,8
+
+Single GPU, kernel throughput of the codec stages (the reference's kernel benchmark,
+cuda_kernels/tests/benchmark_scaling_quantization.py:41-112):
+
+    python -m dynamiq_sigcomm_artifact_b200.train.bench_allreduce --kernels --numel 268435456
+
+Protocol (rdma_comm_compress/sample_allreduce.py:688-739): warm-up iterations, then timed
+iterations of ``work.copy_(base); allreduce_(work)``, MAX over ranks; here timed on the device
+with CUDA events and with the copy outside the timed interval.  ``algbw = 2(W-1)/W * input
+bytes / t`` as in the reference (:721-727); ``wire_gbs`` counts the bytes that really cross
+NVLink per GPU and direction.  Inputs: N(0,1) with a lognormal (sigma 2) scale per 1024-element
+block, seeded per rank.  NMSE is against the exact fp64 mean.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..parallel import schedules as sch
+from ..parallel.fused import BLOCK, FusedAllreduce, Layout, LocalCluster
+
+NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction per GPU on this pool
+HBM_GBS_FALLBACK = 6650.0
+
+
+def measured_peaks() -> dict:
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                        "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return json.load(f)
+    except OSError:
+        return {}
+
+
+def make_input(numel: int, rank: int, seed: int, device) -> torch.Tensor:
+    g = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
+    x = torch.randn(numel, generator=g, device=device)
+    nb = (numel + BLOCK - 1) // BLOCK
+    s = torch.exp(2.0 * torch.randn(nb, generator=g, device=device))
+    return x * s.repeat_interleave(BLOCK)[:numel]
+
+
+def time_op(fn, prepare, iters: int, warmup: int) -> float:
+    """Mean device milliseconds of fn(); prepare() runs before each call, outside the interval."""
+    for _ in range(warmup):
+        prepare()
+        fn()
+    total = 0.0
+    for _ in range(iters):
+        prepare()
+        if dist.is_initialized():
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    ms = total / iters
+    if dist.is_initialized():
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    return ms
+
+
+def nmse_vs(exact: torch.Tensor, got: torch.Tensor) -> float:
+    return float(((got.double() - exact) ** 2).sum() / (exact ** 2).sum())
+
+
+def run_collectives(args) -> None:
+    dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0))))
+    rank, world = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    torch.cuda.set_device(dev)
+    sizes = [int(float(s) * (1 << 20)) // 4 for s in args.sizes_mb.split(",")]
+    bits_list = [int(b) for b in args.bits.split(",")]
+    topologies = args.topologies.split(",")
+    eng = FusedAllreduce(max_numel=max(sizes), ctas=args.ctas, threads=args.threads, timeout_ms=5000)
+    rows = []
+    for numel in sizes:
+        base = make_input(numel, rank, args.seed, dev)
+        exact = base.double().clone()
+        dist.all_reduce(exact)
+        exact /= world
+        work = torch.empty_like(base)
+        in_bytes = numel * 4
+
+        def record(name, ms, wire_bytes, err, extra=None):
+            row = {"method": name, "world": world, "numel": numel, "input_mb": in_bytes / 2 ** 20, "ms": ms,
+                   "algbw_gbs": 2 * (world - 1) / world * in_bytes / ms / 1e6,
+                   "input_gbs": in_bytes / ms / 1e6, "wire_gbs": wire_bytes / ms / 1e6,
+                   "link_fraction_of_measured": wire_bytes / ms / 1e6 / NVLINK_GBS, "nmse": err}
+            row.update(extra or {})
+            rows.append(row)
+            if rank == 0:
+                print(json.dumps(row), flush=True)
+
+        # library baselines
+        def nccl32():
+            dist.all_reduce(work)
+            work.div_(world)
+
+        ms = time_op(nccl32, lambda: work.copy_(base), args.iters, args.warmup)
+        record("nccl_fp32", ms, 2 * (world - 1) / world * in_bytes, nmse_vs(exact, work))
+        wb = torch.empty(numel, dtype=torch.bfloat16, device=dev)
+
+        def nccl16():
+            wb.copy_(work)
+            dist.all_reduce(wb)
+            work.copy_(wb)
+            work.div_(world)
+
+        ms = time_op(nccl16, lambda: work.copy_(base), args.iters, args.warmup)
+        record("nccl_bf16", ms, 2 * (world - 1) / world * numel * 2, nmse_vs(exact, work))
+        for topo in topologies:
+            if topo == "butterfly" and world & (world - 1):
+                continue
+            for bits in bits_list:
+                lay = Layout(numel, world, bits)
+                shard_bytes = lay.blocks_per_shard * (128 * bits + 4)
+                wire = 2 * (world - 1) * shard_bytes  # per GPU, each direction
+                it = [0]
+
+                def fused():
+                    it[0] += 1
+                    eng.allreduce_(work, bits, topo, seed=args.seed, step=it[0], bucket_id=0)
+
+                ms = time_op(fused, lambda: work.copy_(base), args.iters, args.warmup)
+                eng.check()
+                hbm = measured_peaks().get("hbm_gbs", HBM_GBS_FALLBACK)
+                t_link = wire / (NVLINK_GBS * 1e6)
+                t_hbm = (2 * in_bytes + 3 * wire) / (hbm * 1e6)
+                record(f"fused_{topo}_{bits}bit", ms, wire, nmse_vs(exact, work),
+                       {"roofline_ms": max(t_link, t_hbm), "roofline_fraction": max(t_link, t_hbm) / ms,
+                        "bound": "nvlink" if t_link > t_hbm else "hbm"})
+    if rank == 0 and args.out:
+        with open(args.out, "w") as f:
+            json.dump(rows, f, indent=1)
+    eng.close()
+    dist.destroy_process_group()
+
+
+def run_kernels(args) -> None:
+    """Codec stages on one GPU: encode, hop (decode + add + encode), decode; bytes over HBM."""
+    dev = torch.device("cuda", 0)
+    numel = args.numel
+    hbm = measured_peaks().get("hbm_gbs", HBM_GBS_FALLBACK)
+    x = make_input(numel, 0, args.seed, dev)
+    rows = []
+    for bits in [int(b) for b in args.bits.split(",")]:
+        cl = LocalCluster(1, numel, ctas=args.ctas, threads=args.threads, device=dev)
+        lay = Layout(numel, 1, bits)
+        work = torch.empty_like(x)
+        msg = lay.nblocks * (128 * bits + 4)
+        progs = {
+            "encode": (sch.Step(shard=0, out=sch.OUT_SEND, dst=0, send_slot=0, tag=sch.TAG_ENCODE), 4 * numel + msg),
+            "hop": (sch.Step(shard=0, recv_slot=0, nrecv=1, out=sch.OUT_SEND, dst=0, send_slot=1,
+                             tag=sch.TAG_ENCODE + 1), 4 * numel + 2 * msg),
+            "decode": (sch.Step(shard=0, recv_slot=0, nrecv=1, out=sch.OUT_DECODE), 4 * numel + msg),
+            "final": (sch.Step(shard=0, recv_slot=0, nrecv=1, out=sch.OUT_FINAL, tag=sch.TAG_FINAL), 8 * numel + msg),
+        }
+        for name, (step, nbytes) in progs.items():
+            prog = torch.tensor([[step.as_ints()]], dtype=torch.int32)
+            ms = time_op(lambda: cl.run([work], prog, bits, seed=args.seed, preset_flags=True),
+                         lambda: work.copy_(x), args.iters, args.warmup)
+            cl.check()
+            row = {"kernel": f"rht_{name}", "bits": bits, "numel": numel, "ms": ms, "gbs": nbytes / ms / 1e6,
+                   "gelem_s": numel / ms / 1e6, "hbm_fraction_of_measured": nbytes / ms / 1e6 / hbm,
+                   "ctas": args.ctas, "threads": args.threads}
+            rows.append(row)
+            print(json.dumps(row), flush=True)
+    if args.out:
+        with open(args.out, "w") as f:
+            json.dump(rows, f, indent=1)
+
+
+def main(argv=None) -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--kernels", action="store_true", help="single-GPU codec kernel throughput")
+    ap.add_argument("--numel", type=int, default=1 << 26)
+    ap.add_argument("--sizes-mb", default="1,4,16,64,256")
+    ap.add_argument("--bits", default="4,5,8")
+    ap.add_argument("--topologies", default="ring,butterfly,direct")
+    ap.add_argument("--ctas", type=int, default=148)
+    ap.add_argument("--threads", type=int, default=512)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--seed", type=int, default=1)
+    ap.add_argument("--out", default=None)
+    args = ap.parse_args(argv)
+    if args.kernels:
+        run_kernels(args)
+    else:
+        run_collectives(args)
+
+
+if __name__ == "__main__":
+    main()
