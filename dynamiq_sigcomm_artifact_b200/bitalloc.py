@@ -1,0 +1,181 @@
+"""Bit-width selection: threshold split, the dynamic-bitrate controller, per-bucket widths.
+
+Restates the reference's policies so that they can be unit-tested on CPU:
+
+* threshold split (testbed_evaluation/new_comm_hooks/comm_hooks.py:713-721): stable descending
+  argsort of the per-superchunk energy; the top ``thr[8]`` fraction is sent at 8 bits, the
+  bottom ``thr[2]`` at 2, the rest at 4;
+* dynamic bitrate (comm_hooks.py:48-139,907-930; spec new_comm_hooks/dynamic_bitrate.md):
+  ``q = 2 ** clamp(floor(log2(c * log2 F + u)), 1, 3)`` with ``c = 4 / (512 / 17)``; ``u``
+  starts at 60, is bisected on [-10, 60] on the first compressed step and then nudged every
+  step so that ``mean(q)`` stays within 0.1 of ``b - 0.625`` (0.625 bit/element is what the
+  scales and the mean cost on the wire);
+* per-bucket widths for the rotation codec (this framework's addition): whole buckets move
+  between b-1, b and b+1 bits by their energy per element, under the same average budget.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Sequence, Tuple
+
+import torch
+
+HEADROOM = 0.625
+U_MIN, U_MAX = -10.0, 60.0
+TOL = 0.1
+MAX_ITERS = 32
+NORM_SCALE = 4.0 / (512.0 / 17.0)
+
+
+def split_by_thresholds(norms: torch.Tensor, thresholds: Dict[int, float], fixed: bool = False
+                        ) -> Dict[int, torch.Tensor]:
+    """{8: idx, 4: idx, 2: idx} row indices of the three groups (empty groups included)."""
+    n = norms.numel()
+    top = int(n * thresholds.get(8, 0.0))
+    bottom = int(n * thresholds.get(2, 0.0))
+    if top + bottom > n:
+        bottom = max(0, n - top)
+    order = torch.argsort(norms.float(), descending=True, stable=True)
+    groups = {8: order[:top], 4: order[top: n - bottom], 2: order[n - bottom:] if bottom > 0 else order[:0]}
+    if fixed:  # only the 4-bit group is communicated (comm_hooks.py:767-771)
+        groups[8], groups[2] = order[:0], order[:0]
+    return groups
+
+
+def qbits(norms: torch.Tensor, u: float) -> torch.Tensor:
+    """Per-superchunk code width in {2, 4, 8} for controller state `u`."""
+    eps = 1e-20
+    score = torch.log2(torch.clamp(norms.float(), min=eps)) * NORM_SCALE + float(u)
+    z = torch.floor(torch.log2(torch.clamp(score, min=eps))).to(torch.int64).clamp_(1, 3)
+    return torch.bitwise_left_shift(torch.ones_like(z), z)
+
+
+def split_by_bitrate(norms: torch.Tensor, u: float) -> Dict[int, torch.Tensor]:
+    q = qbits(norms, u)
+    return {b: torch.nonzero(q == b, as_tuple=False).reshape(-1) for b in (8, 4, 2)}
+
+
+def average_bits(norms_list: Sequence[torch.Tensor], u: float) -> float:
+    total, count = 0.0, 0
+    for norms in norms_list:
+        if norms.numel():
+            total += float(qbits(norms, u).sum())
+            count += norms.numel()
+    return total / count if count else 0.0
+
+
+class DynamicBitrateController:
+    """Keeps ``mean(q)`` at ``target_bits - 0.625`` by moving ``u``."""
+
+    def __init__(self, target_bits: float):
+        self.target = float(target_bits) - HEADROOM
+        self.u = U_MAX
+        self.last_avg = 0.0
+        self.last_delta = 0.0
+        self.initialised = False
+        self._norms: List[torch.Tensor] = []
+
+    def observe(self, norms: torch.Tensor) -> None:
+        self._norms.append(norms.detach().float().cpu())
+
+    def _delta(self, u: float) -> Tuple[float, float]:
+        avg = average_bits(self._norms, u)
+        return avg, self.target - avg
+
+    def _bisect(self) -> Tuple[float, float, float]:
+        low, high = U_MIN, U_MAX
+        best_u = high
+        best_avg, best_delta = self._delta(best_u)
+        for _ in range(MAX_ITERS):
+            mid = 0.5 * (low + high)
+            avg, delta = self._delta(mid)
+            if abs(delta) < abs(best_delta):
+                best_u, best_avg, best_delta = mid, avg, delta
+            if abs(delta) <= TOL:
+                return mid, avg, delta
+            if delta > 0:
+                low = mid
+            else:
+                high = mid
+        return best_u, best_avg, best_delta
+
+    def _adjust(self) -> Tuple[float, float, float]:
+        prev = min(U_MAX, max(U_MIN, self.u))
+        old_avg, old_delta = self._delta(prev)
+        if abs(old_delta) <= TOL:
+            return prev, old_avg, old_delta
+        step = old_delta
+        best = (prev, old_avg, old_delta)
+        for _ in range(MAX_ITERS):
+            cand = min(U_MAX, max(U_MIN, prev + step))
+            avg, delta = self._delta(cand)
+            if abs(delta) < abs(best[2]):
+                best = (cand, avg, delta)
+            if abs(delta) <= TOL or old_delta * delta >= 0:
+                return cand, avg, delta
+            step *= 0.5
+        return best
+
+    def end_of_step(self) -> None:
+        """Call after the last bucket of a step: updates ``u`` for the next step."""
+        if not self._norms:
+            return
+        u, avg, delta = self._adjust() if self.initialised else self._bisect()
+        self.u, self.last_avg, self.last_delta = float(u), float(avg), float(delta)
+        self.initialised = True
+        self._norms = []
+
+    def state_dict(self) -> dict:
+        return {"u": self.u, "initialised": self.initialised, "target": self.target}
+
+    def load_state_dict(self, d: dict) -> None:
+        self.u, self.initialised, self.target = float(d["u"]), bool(d["initialised"]), float(d["target"])
+
+
+class BucketBitPolicy:
+    """Per-bucket width for the rotation codec: b-1 / b / b+1 by energy per element.
+
+    Energies are read one step late (an asynchronous scalar per bucket), so choosing a width
+    never synchronises the host with the device.  Buckets are ranked by the logarithm of their
+    energy per element; the top quarter gets b+1 bits, the bottom quarter b-1, which keeps the
+    element-weighted average within one quarter of a bit of b.
+    """
+
+    def __init__(self, bits: int, spread: int = 1):
+        self.bits, self.spread = int(bits), int(spread)
+        self.energy: Dict[int, torch.Tensor] = {}
+        self.numel: Dict[int, int] = {}
+        self.assigned: Dict[int, int] = {}
+
+    def bits_for(self, index: int, buf: torch.Tensor) -> int:
+        self.numel[index] = buf.numel()
+        self.energy[index] = (buf.detach().float().pow(2).mean()).to("cpu", non_blocking=True)
+        return self.assigned.get(index, self.bits)
+
+    def end_of_step(self) -> None:
+        if len(self.energy) < 4:
+            return
+        items = sorted(self.energy, key=lambda i: float(self.energy[i]))
+        n = len(items)
+        k = n // 4
+        self.assigned = {i: self.bits for i in items}
+        lo, hi = items[:k], items[n - k:]
+        # keep the element-weighted budget: only widen as many elements as were narrowed
+        saved = sum(self.numel[i] for i in lo)
+        for i in lo:
+            self.assigned[i] = max(2, self.bits - self.spread)
+        for i in reversed(hi):
+            if self.numel[i] <= saved:
+                self.assigned[i] = min(8, self.bits + self.spread)
+                saved -= self.numel[i]
+
+    def average_bits(self) -> float:
+        tot = sum(self.numel.values())
+        return sum(self.assigned.get(i, self.bits) * n for i, n in self.numel.items()) / tot if tot else self.bits
+
+    def state_dict(self) -> dict:
+        return {"bits": self.bits, "assigned": dict(self.assigned)}
+
+    def load_state_dict(self, d: dict) -> None:
+        self.bits = int(d["bits"])
+        self.assigned = {int(k): int(v) for k, v in d["assigned"].items()}

@@ -6,17 +6,19 @@ same random numbers as the kernel (cuda_kernels/tests/test_scaling_quantization_
 
     block of 1024 values
       -> Rademacher diagonal (1024 sign bits from Philox, shared by all ranks)
-      -> Walsh-Hadamard H_1024 / 32 (orthonormal; H_1024 = H_32 (x) H_32)
+      -> Walsh-Hadamard H_1024 = H_32 (x) H_32, left unnormalised (the 1/1024 of the round
+         trip is folded into the final scale, so no pass multiplies by 1/32)
       -> per-block fp32 scale  absmax / R,  R = 2^(b-1) - 1
-      -> stochastic rounding  floor(y * R/absmax + u),  u a 16-bit Philox uniform
+      -> stochastic rounding  floor(y * R/absmax + u),  u = (byte + 0.5) / 256 from Philox-4x32-7
       -> b-bit codes, b in 2..8, packed without padding (8 codes of 5 bits in 5 bytes)
 
-A hop adds the locally rotated block to the decoded incoming block in fp32 and encodes
-the sum again (the reference rounds the sum to bf16 first,
+A hop adds the decoded incoming block to the locally rotated block with one fp32 fma per
+value, v <- fma(code - R, scale, v), and encodes the sum again (the reference rounds the sum to bf16 first,
 cuda_kernels/src/srrcomp/eden_utils/csrc/cuda_hierarchical_mee.cu:567-568).
 
-All arithmetic is float32 with one rounding per operation and no fused multiply-add, in the
-order the kernel uses, so that the kernel's bytes can be compared with ``==``.
+All arithmetic is float32 in the order the kernel uses (fused multiply-adds where the kernel
+fuses: the rounding argument and the hop accumulation), so that the kernel's bytes can be
+compared with ``==``.
 
 Layouts (shared with ``csrc/common/rht_codec.cuh``)
 * A warp owns a block; after the rotation lane ``l`` holds, in register ``k``, the
@@ -41,6 +43,13 @@ RHO = ((_L & 3) + 4 * _K + 128 * (_L >> 2)).astype(np.int64)  # [lane, reg] -> c
 FWD_STAGES = (0, 1, 7, 8, 9, 2, 3, 4, 5, 6)  # bit of the element index handled by each butterfly stage
 INV_STAGES = (2, 3, 4, 5, 6, 0, 1, 7, 8, 9)
 F32 = np.float32
+
+
+def fma32(a, b, c) -> np.ndarray:
+    """float32 fused multiply-add: the product of two float32 is exact in float64, the sum is
+    rounded once to float64 and once more to float32 (a double rounding that differs from a
+    true fma only on exact ties, ~2^-29 of the inputs)."""
+    return (np.asarray(a, np.float64) * np.asarray(b, np.float64) + np.asarray(c, np.float64)).astype(F32)
 
 
 def qmax(bits: int) -> int:
@@ -79,14 +88,14 @@ def _butterflies(v: np.ndarray, stages) -> np.ndarray:
 
 
 def rotate_fwd(x: np.ndarray, signs: np.ndarray) -> np.ndarray:
-    """y = H_1024 (s * x) / 32 for every row of x [nb, 1024]."""
-    return _butterflies(x * signs[None, :], FWD_STAGES) * F32(1.0 / 32.0)
+    """y = H_1024 (s * x) (unnormalised) for every row of x [nb, 1024]."""
+    return _butterflies(x * signs[None, :], FWD_STAGES)
 
 
 def rotate_inv(y: np.ndarray, signs: np.ndarray, post_scale: float = 1.0) -> np.ndarray:
-    """x = s * H_1024 y / 32 * post_scale (post_scale = 1/world for the mean)."""
+    """x = s * H_1024 y * post_scale / 1024 (post_scale = 1/world for the mean)."""
     v = _butterflies(y, INV_STAGES)
-    return (v * F32(post_scale / 32.0)) * signs[None, :]
+    return (v * F32(post_scale / 1024.0)) * signs[None, :]
 
 
 def quantize(y: np.ndarray, bits: int, block_idx: np.ndarray, tag: int, step: int, seed: int
@@ -96,15 +105,24 @@ def quantize(y: np.ndarray, bits: int, block_idx: np.ndarray, tag: int, step: in
     y = y.astype(F32, copy=False)
     absmax = np.max(np.abs(y), axis=1)
     with np.errstate(divide="ignore", invalid="ignore"):
-        ok = (absmax > 0) & np.isfinite(absmax)
+        ok = (absmax >= F32(1e-30)) & np.isfinite(absmax)
         scale = np.where(ok, absmax / F32(R), F32(0)).astype(F32)
         inv = np.where(ok, F32(R) / absmax, F32(0)).astype(F32)
-    r16 = philox.block_uniforms16(block_idx, tag, step, seed)  # [nb, 32, 32]
-    u = (r16.astype(F32) + F32(0.5)) * F32(1.0 / 65536.0)
-    q = (y[:, RHO] * inv[:, None, None]).astype(F32)
-    t = (q + u).astype(F32)
+    r8 = philox.block_uniforms8(block_idx, tag, step, seed)  # [nb, 32, 32]
+    u = (r8.astype(F32) + F32(0.5)) * F32(1.0 / 256.0)
+    t = fma32(y[:, RHO], inv[:, None, None], u)
     code = np.clip(np.floor(t), -R, R).astype(np.int32) + R
     return code.astype(np.uint8), scale
+
+
+def dequantize_add(codes: np.ndarray, scale: np.ndarray, bits: int, acc: np.ndarray) -> np.ndarray:
+    """acc [nb, 1024] (coefficient order) + decoded block, one fma per value."""
+    R = qmax(bits)
+    f = (codes.astype(np.int32) - R).astype(F32)
+    out = acc.astype(F32, copy=True)
+    flat = RHO.reshape(-1)
+    out[:, flat] = fma32(f.reshape(codes.shape[0], BLOCK), scale[:, None], acc[:, flat])
+    return out
 
 
 def dequantize(codes: np.ndarray, scale: np.ndarray, bits: int) -> np.ndarray:
@@ -161,6 +179,11 @@ def from_message(msg: np.ndarray, nblocks: int, bits: int) -> Tuple[np.ndarray, 
 def encode_blocks(y: np.ndarray, bits: int, block_idx, tag: int, step: int, seed: int) -> np.ndarray:
     codes, scale = quantize(y, bits, np.asarray(block_idx), tag, step, seed)
     return to_message(pack(codes, bits), scale)
+
+
+def decode_add_blocks(msg: np.ndarray, nblocks: int, bits: int, acc: np.ndarray) -> np.ndarray:
+    words, scale = from_message(msg, nblocks, bits)
+    return dequantize_add(unpack(words, bits), scale, bits, acc)
 
 
 def decode_blocks(msg: np.ndarray, nblocks: int, bits: int) -> np.ndarray:

@@ -21,16 +21,29 @@ namespace dq {
 
 constexpr int kBlock = 1024;
 constexpr unsigned kFullMask = 0xFFFFFFFFu;
+constexpr int kUniformRounds = 7;  // Philox-4x32-7 for the rounding uniforms (philox.py: UNIFORM_ROUNDS)
 
+// Five butterfly stages over the 32 registers of a lane.  Stage 0 pairs neighbouring registers;
+// stages 1..4 act on register pairs (2i, 2i+1) and use the packed fp32x2 add / fma of sm_100
+// (a - b is fma(b, -1, a): one rounding, same bits as a subtraction).
 __device__ __forceinline__ void butterflies32(float (&v)[32]) {
 #pragma unroll
-  for (int m = 0; m < 5; ++m) {
+  for (int i = 0; i < 32; i += 2) {
+    const float a = v[i], b = v[i + 1];
+    v[i] = a + b;
+    v[i + 1] = a - b;
+  }
+  const float2 neg1 = make_float2(-1.0f, -1.0f);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
+  for (int m = 1; m < 5; ++m) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
       if ((i & (1 << m)) == 0) {
-        float a = v[i], b = v[i | (1 << m)];
-        v[i] = a + b;
-        v[i | (1 << m)] = a - b;
+        const int j = i | (1 << m);
+        const float2 a = make_float2(v[i], v[i + 1]), b = make_float2(v[j], v[j + 1]);
+        const float2 sum = __fadd2_rn(a, b), dif = __ffma2_rn(b, neg1, a);
+        v[i] = sum.x, v[i + 1] = sum.y;
+        v[j] = dif.x, v[j + 1] = dif.y;
       }
     }
   }
@@ -160,18 +173,16 @@ __device__ __forceinline__ void store_block(T* base, int valid, bool vec_ok, int
   }
 }
 
-// raw gradients (load layout) -> rotated coefficients (coefficient layout): y = H (s * x) / 32
+// raw gradients (load layout) -> rotated coefficients (coefficient layout): y = H (s * x), unnormalised
 __device__ __forceinline__ void rotate_forward(float (&v)[32], uint32_t sign_mask, float* tile, int lane) {
 #pragma unroll
   for (int t = 0; t < 32; ++t) v[t] = flip(sanitize(v[t]), (sign_mask >> t) & 1u);
   butterflies32(v);
   transpose_to_coeff(v, tile, lane);
   butterflies32(v);
-#pragma unroll
-  for (int t = 0; t < 32; ++t) v[t] = __fmul_rn(v[t], 0.03125f);
 }
 
-// rotated coefficients -> gradients in the load layout: x = s * (H y) * c, c = post_scale / 32
+// rotated coefficients -> gradients in the load layout: x = s * (H y) * c, c = post_scale / 1024
 __device__ __forceinline__ void rotate_inverse(float (&v)[32], uint32_t sign_mask, float c, float* tile, int lane) {
   butterflies32(v);
   transpose_to_load(v, tile, lane);
@@ -212,47 +223,72 @@ __device__ __forceinline__ float warp_absmax(const float (&y)[32]) {
 }
 
 // Stochastic b-bit quantisation of a block in the coefficient layout.  Returns the block scale.
+//   code = clamp(floor(fma(y, R / absmax, u)), -R, R) + R,   u = (byte + 0.5) / 256
+// computed 256 times larger so that u needs no multiply, with the floor taken by a round-down
+// add of 1.5 * 2^31 (one ulp = 256 there): no int<->float conversion instruction is issued.
 template <int B>
 __device__ __forceinline__ float quantize_block(const float (&y)[32], uint32_t (&w)[B], uint32_t block_idx,
                                                 uint32_t tag, uint32_t step, uint32_t k0, uint32_t k1, int lane) {
   constexpr int R = (1 << (B - 1)) - 1;
   const float m = warp_absmax(y);
-  const bool ok = (m > 0.0f) && (m <= 3.402823466e38f);
+  const bool ok = (m >= 1e-30f) && (m <= 3.402823466e38f);
   const float scale = ok ? __fdiv_rn(m, static_cast<float>(R)) : 0.0f;
   const float inv = ok ? __fdiv_rn(static_cast<float>(R), m) : 0.0f;
+  const float2 inv256 = make_float2(inv * 256.0f, inv * 256.0f);
+  const float2 half_off = make_float2(-8388607.5f, -8388607.5f);
+  const float2 magic = make_float2(3221225472.0f, 3221225472.0f);  // 1.5 * 2^31 = 0x4F400000
   uint32_t c[32];
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    U4 r = philox4x32(block_idx, static_cast<uint32_t>(lane * 4 + q), tag, step, k0, k1);
+  for (int q = 0; q < 2; ++q) {
+    U4 r = philox4x32<kUniformRounds>(block_idx, static_cast<uint32_t>(lane * 2 + q), tag, step, k0, k1);
     const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
-    for (int m8 = 0; m8 < 8; ++m8) {
-      const uint32_t r16 = (m8 & 1) ? (rw[m8 >> 1] >> 16) : (rw[m8 >> 1] & 0xFFFFu);
-      const float u = __fmul_rn(__fadd_rn(static_cast<float>(r16), 0.5f), 1.0f / 65536.0f);
-      const float t = __fadd_rn(__fmul_rn(y[8 * q + m8], inv), u);
-      int code = static_cast<int>(floorf(t));
-      code = max(-R, min(R, code)) + R;
-      c[8 * q + m8] = static_cast<uint32_t>(code);
+    for (int mm = 0; mm < 16; mm += 2) {
+      // 2^23 + byte as a float, straight from the byte (no conversion)
+      const float b0 = __uint_as_float(__byte_perm(rw[mm >> 2], 0x4B000000u, 0x7650u | (mm & 3)));
+      const float b1 = __uint_as_float(__byte_perm(rw[mm >> 2], 0x4B000000u, 0x7650u | ((mm + 1) & 3)));
+      const float2 u256 = __fadd2_rn(make_float2(b0, b1), half_off);  // byte + 0.5
+      const float2 t = __ffma2_rn(make_float2(y[16 * q + mm], y[16 * q + mm + 1]), inv256, u256);
+      const float2 f = __fadd2_rd(t, magic);
+      const int c0 = static_cast<int>(__float_as_uint(f.x)) - 0x4F400000 + R;
+      const int c1 = static_cast<int>(__float_as_uint(f.y)) - 0x4F400000 + R;
+      c[16 * q + mm] = static_cast<uint32_t>(max(0, min(2 * R, c0)));
+      c[16 * q + mm + 1] = static_cast<uint32_t>(max(0, min(2 * R, c1)));
     }
   }
   pack_codes<B>(c, w);
   return scale;
 }
 
+// float(code - R) without a conversion: 0x4B400000 | code is 1.5 * 2^23 + code
 template <int B>
-__device__ __forceinline__ void dequantize_block(const uint32_t (&w)[B], float scale, float (&y)[32]) {
+__device__ __forceinline__ float2 code_pair(const uint32_t (&w)[B], int k) {
   constexpr int R = (1 << (B - 1)) - 1;
-#pragma unroll
-  for (int k = 0; k < 32; ++k)
-    y[k] = __fmul_rn(static_cast<float>(static_cast<int>(unpack_code<B>(w, k)) - R), scale);
+  const float2 off = make_float2(-(12582912.0f + R), -(12582912.0f + R));
+  const float a = __uint_as_float(0x4B400000u | unpack_code<B>(w, k));
+  const float b = __uint_as_float(0x4B400000u | unpack_code<B>(w, k + 1));
+  return __fadd2_rn(make_float2(a, b), off);
 }
 
 template <int B>
-__device__ __forceinline__ void dequantize_add_block(const uint32_t (&w)[B], float scale, float (&y)[32]) {
-  constexpr int R = (1 << (B - 1)) - 1;
+__device__ __forceinline__ void dequantize_block(const uint32_t (&w)[B], float scale, float (&y)[32]) {
+  const float2 s2 = make_float2(scale, scale);
 #pragma unroll
-  for (int k = 0; k < 32; ++k)
-    y[k] = __fadd_rn(y[k], __fmul_rn(static_cast<float>(static_cast<int>(unpack_code<B>(w, k)) - R), scale));
+  for (int k = 0; k < 32; k += 2) {
+    const float2 r = __fmul2_rn(code_pair<B>(w, k), s2);
+    y[k] = r.x, y[k + 1] = r.y;
+  }
+}
+
+// y <- fma(code - R, scale, y)
+template <int B>
+__device__ __forceinline__ void dequantize_add_block(const uint32_t (&w)[B], float scale, float (&y)[32]) {
+  const float2 s2 = make_float2(scale, scale);
+#pragma unroll
+  for (int k = 0; k < 32; k += 2) {
+    const float2 r = __ffma2_rn(code_pair<B>(w, k), s2, make_float2(y[k], y[k + 1]));
+    y[k] = r.x, y[k + 1] = r.y;
+  }
 }
 
 }  // namespace dq

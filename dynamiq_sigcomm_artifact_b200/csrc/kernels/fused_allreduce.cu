@@ -75,7 +75,7 @@ static void fill_common(ARParams& p, const at::Tensor& bucket, const at::Tensor&
   p.seed_hi = static_cast<uint32_t>(static_cast<uint64_t>(seed) >> 32);
   p.step = static_cast<uint32_t>(step);
   p.bucket_id = static_cast<uint32_t>(bucket_id);
-  p.finish_scale = static_cast<float>(post_scale / 32.0);
+  p.finish_scale = static_cast<float>(post_scale / 1024.0);
   p.timeout_ns = static_cast<unsigned long long>(timeout_ns);
   p.status = reinterpret_cast<uint32_t*>(status_ptr);
   p.tail_ws = reinterpret_cast<float*>(tail_ws_ptr);

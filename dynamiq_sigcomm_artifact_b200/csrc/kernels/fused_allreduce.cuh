@@ -13,7 +13,7 @@ enum : int { kLocalRaw = 0, kLocalWs = 1 };
 enum : int { kOutSend = 0, kOutStore = 1, kOutFinal = 2, kOutDecode = 3 };
 
 // error codes left in status[0]; status[1] = (step << 16) | cta, status[2] = slot
-enum : uint32_t { kOk = 0, kErrWaitTimeout = 1, kErrBadProgram = 2 };
+enum : uint32_t { kOk = 0, kErrWaitTimeout = 1, kErrBadProgram = 2, kErrCopyTimeout = 3 };
 
 struct ARParams {
   void* bucket;        // this rank's gradient bucket: input, scratch for partial sums, and output
@@ -30,7 +30,7 @@ struct ARParams {
   uint32_t flag_base;              // first flag word of this collective's slot set
   uint32_t epoch;                  // value a flag must reach
   uint32_t seed_lo, seed_hi, step, bucket_id;
-  float finish_scale;              // post_scale / 32 applied by the inverse rotation
+  float finish_scale;              // post_scale / 1024 applied by the inverse rotation
   unsigned long long timeout_ns;   // budget of each wait on a flag
   uint32_t* status;                // 4 words, local
   int no_transmit;                 // debug: run the maths, skip remote payload stores

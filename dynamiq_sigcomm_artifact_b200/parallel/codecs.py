@@ -1,0 +1,227 @@
+"""Codecs in PyTorch ops for the device-agnostic backend (``torch_backend.allreduce_torch``).
+
+* :class:`SuperchunkCodec` - the reference's hierarchical "scaling quantisation": 256-element
+  superchunks of 16 chunks of 16 values, linear (AEE) or logarithmic-lattice (MEE) codes of
+  2 / 4 / 8 bits, a uint8 round-up scale per chunk and a bf16 scale per superchunk; the wire
+  layout is the reference's byte for byte (spec
+  cuda_kernels/documentation/scaling_quantization_algorithm.md:347-388, kernels
+  cuda_kernels/src/srrcomp/eden_utils/csrc/cuda_hierarchical_mee.cu:203-343, size formula
+  eden_utils.cpp:33-40).  Differences: partial sums stay fp32 between hops, and the rounding
+  uniforms come from the counter-based generator instead of a pool.
+* :class:`CastCodec` - identity wires bf16 / fp16 / fp32 (utils_aggregation.py:575-686).
+* :class:`BlockFloatCodec` - MXFP8 (E4M3), FP6 (E3M2) and FP4 (E2M1) with one power-of-two
+  scale byte per 32 values (clean spec in simulations_llm/new_comm_hooks/comm_hooks.py:138-275,
+  991-1161; the testbed's fp4/fp6 only truncate the message, comm_hooks.py:214-248).
+* :class:`IntBinsCodec` - THC's integer bins summed exactly along the schedule
+  (``Direct_Summation``, thc_hooks.py:152-223).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .torch_backend import TorchCodec, uniform_bytes
+
+MEE_EPS = {1: 0.23, 2: 0.23, 3: 0.18, 4: 0.18, 5: 0.18, 6: 0.10, 7: 0.10, 8: 0.10}  # cuda_hadamard.cu:878-897
+SUPERCHUNK = 256
+CHUNK = 16
+
+
+def superchunk_bytes(bits: int) -> int:
+    """Bytes of one 256-element superchunk on the wire: 16 * (2 b + 1) + 2."""
+    return CHUNK * (CHUNK * bits // 8 + 1) + 2
+
+
+def mee_lattice(level: torch.Tensor, eps: float) -> torch.Tensor:
+    """Decode lattice ((1+2e^2)^|l| - 1) / (2 e^2) * (1 + e^2), odd in l."""
+    mag = (torch.pow(torch.tensor(1.0 + 2.0 * eps * eps, dtype=torch.float32, device=level.device), level.abs())
+           - 1.0) / (2.0 * eps * eps) * (1.0 + eps * eps)
+    return torch.sign(level) * mag
+
+
+class SuperchunkCodec(TorchCodec):
+    align = SUPERCHUNK
+
+    def __init__(self, bits: int, lattice: str = "aee", seed: int = 0, step: int = 0, bucket: int = 0):
+        if bits not in (2, 4, 8):
+            raise ValueError("the superchunk codec has 2, 4 and 8 bit codes")
+        if lattice not in ("aee", "mee"):
+            raise ValueError("lattice must be 'aee' or 'mee'")
+        self.bits, self.lattice, self.seed, self.step, self.bucket = bits, lattice, seed, step, bucket
+        self.R = (1 << (bits - 1)) - 1
+        self.eps = MEE_EPS[bits]
+        self.c1 = (1.0 + self.eps ** 2) / (2.0 * self.eps ** 2)
+        self.c2 = math.log2(1.0 + 2.0 * self.eps ** 2)
+        self.lattice_max = float(mee_lattice(torch.tensor(float(self.R)), self.eps)) if lattice == "mee" else float(self.R)
+
+    def message_bytes(self, numel: int) -> int:
+        assert numel % SUPERCHUNK == 0
+        return numel // SUPERCHUNK * superchunk_bytes(self.bits)
+
+    # -- encode --------------------------------------------------------------------------
+    def encode(self, v: torch.Tensor, first: int, tag: int) -> torch.Tensor:
+        b, R = self.bits, self.R
+        nsc = v.numel() // SUPERCHUNK
+        x = torch.nan_to_num(v.float().reshape(nsc, CHUNK, CHUNK), nan=0.0, posinf=0.0, neginf=0.0)
+        s = (x.abs().amax(dim=2) / self.lattice_max + 1e-7).clamp_min(1e-30)  # chunk scales [nsc, 16]
+        S = s.amax(dim=1, keepdim=True)  # superchunk scale
+        unit_bf16 = (S / 255.0).clamp_min(1e-30).to(torch.bfloat16)
+        unit = unit_bf16.float().clamp_min(1e-30)
+        q = torch.ceil(s / S * 255.0).clamp_(1, 255)  # uint8 round-up chunk scale
+        dec = (q * unit).clamp_min(1e-30)
+        y = x / dec.unsqueeze(2)
+        if self.lattice == "mee":
+            y = torch.sign(y) * torch.log2(y.abs() / self.c1 + 1.0) / self.c2
+        stream = ((self.bucket & 0xFFFF) << 16) | (tag & 0xFFFF)
+        r = (uniform_bytes(v.numel(), stream, self.step, self.seed, v.device, offset=first // 16).float() + 0.5) / 256.0
+        fl = torch.floor(y)
+        code = (fl + ((y - fl) > r.reshape(nsc, CHUNK, CHUNK)).float()).clamp_(-R, R) + R
+        code = code.to(torch.uint8)
+        per = 8 // b  # codes per byte, little end first
+        packed = torch.zeros(nsc, CHUNK, CHUNK // per, dtype=torch.uint8, device=v.device)
+        c = code.reshape(nsc, CHUNK, CHUNK // per, per)
+        for k in range(per):
+            packed |= c[..., k] << (k * b)
+        out = torch.empty(nsc, superchunk_bytes(b), dtype=torch.uint8, device=v.device)
+        body = out[:, : CHUNK * (2 * b + 1)].reshape(nsc, CHUNK, 2 * b + 1)
+        body[:, :, : 2 * b] = packed
+        body[:, :, 2 * b] = q.to(torch.uint8)
+        out[:, CHUNK * (2 * b + 1):] = unit_bf16.reshape(nsc, 1).view(torch.uint8).reshape(nsc, 2)
+        return out.reshape(-1)
+
+    # -- decode --------------------------------------------------------------------------
+    def decode(self, msg: torch.Tensor, numel: int) -> torch.Tensor:
+        b, R = self.bits, self.R
+        nsc = numel // SUPERCHUNK
+        m = msg.reshape(nsc, superchunk_bytes(b))
+        body = m[:, : CHUNK * (2 * b + 1)].reshape(nsc, CHUNK, 2 * b + 1)
+        packed = body[:, :, : 2 * b]
+        q = body[:, :, 2 * b].float()
+        unit = m[:, CHUNK * (2 * b + 1):].contiguous().view(torch.bfloat16).float().clamp_min(1e-30)
+        per = 8 // b
+        mask = (1 << b) - 1
+        codes = torch.stack([(packed >> (k * b)) & mask for k in range(per)], dim=-1).reshape(nsc, CHUNK, CHUNK)
+        level = codes.float() - R
+        if self.lattice == "mee":
+            level = mee_lattice(level, self.eps)
+        dec = (q * unit).clamp_min(1e-30)
+        return (level * dec.unsqueeze(2)).reshape(-1)
+
+
+class CastCodec(TorchCodec):
+    """Values travel as bf16 / fp16 / fp32; partial sums are rounded to the wire type per hop."""
+
+    def __init__(self, dtype: torch.dtype):
+        self.dtype = dtype
+        self.itemsize = torch.tensor([], dtype=dtype).element_size()
+        self.align = 16 // self.itemsize
+
+    def message_bytes(self, numel: int) -> int:
+        return numel * self.itemsize
+
+    def encode(self, v, first, tag):
+        return v.to(self.dtype).contiguous().view(torch.uint8).reshape(-1)
+
+    def decode(self, msg, numel):
+        return msg.view(self.dtype)[:numel].float()
+
+
+_FORMATS = {  # name: (exponent bits, mantissa bits, largest finite magnitude)
+    "fp8": (4, 3, 448.0),
+    "fp6": (3, 2, 28.0),
+    "fp4": (2, 1, 6.0),
+}
+
+
+def _round_to_minifloat(x: torch.Tensor, ebits: int, mbits: int, vmax: float) -> torch.Tensor:
+    """Round-to-nearest-even onto the (ebits, mbits) grid with subnormals, saturating at vmax."""
+    bias = (1 << (ebits - 1)) - 1
+    ax = x.abs().clamp_max(vmax)
+    e = torch.floor(torch.log2(ax.clamp_min(1e-38))).clamp_min(1 - bias)
+    step = torch.pow(torch.tensor(2.0, device=x.device), e - mbits)
+    return torch.sign(x) * torch.round(ax / step) * step
+
+
+class BlockFloatCodec(TorchCodec):
+    """32-value blocks: one E8M0 scale byte + 32 minifloat codes (8, 6 or 4 bits each).
+
+    Codes are stored as the index of the value in the format's sorted table, so any of the three
+    formats shares the same packing code; the wire size is exactly 8.25 / 6.25 / 4.25 bit per
+    element, the figures the reference's bandwidth emulation uses (comm_hooks.py:239-241).
+    """
+
+    BLOCK = 32
+
+    def __init__(self, fmt: str):
+        self.fmt = fmt
+        self.ebits, self.mbits, self.vmax = _FORMATS[fmt]
+        self.width = 1 + self.ebits + self.mbits
+        self.align = 32 * 8  # keeps every message a whole number of bytes for 6-bit codes
+        mags = [0.0]
+        bias = (1 << (self.ebits - 1)) - 1
+        for e in range(1 << self.ebits):
+            for m in range(1 << self.mbits):
+                val = (m / (1 << self.mbits)) * 2.0 ** (1 - bias) if e == 0 else (1 + m / (1 << self.mbits)) * 2.0 ** (e - bias)
+                if 0 < val <= self.vmax:
+                    mags.append(val)
+        self.table = torch.tensor(sorted(set(mags)), dtype=torch.float32)
+
+    def message_bytes(self, numel: int) -> int:
+        nb = (numel + self.BLOCK - 1) // self.BLOCK
+        return nb + (nb * self.BLOCK * self.width + 7) // 8
+
+    def _table(self, device):
+        if self.table.device != device:
+            self.table = self.table.to(device)
+        return self.table
+
+    def encode(self, v, first, tag):
+        n = v.numel()
+        nb = (n + self.BLOCK - 1) // self.BLOCK
+        x = torch.zeros(nb * self.BLOCK, dtype=torch.float32, device=v.device)
+        x[:n] = torch.nan_to_num(v.float(), nan=0.0, posinf=0.0, neginf=0.0)
+        x = x.reshape(nb, self.BLOCK)
+        amax = x.abs().amax(dim=1).clamp_min(1e-38)
+        e = torch.ceil(torch.log2(amax / self.vmax)).clamp_(-127, 127)  # power-of-two block scale
+        y = _round_to_minifloat(x / torch.pow(torch.tensor(2.0, device=v.device), e).unsqueeze(1), self.ebits,
+                                self.mbits, self.vmax)
+        t = self._table(v.device)
+        idx = torch.bucketize(y.abs(), t).clamp_max(t.numel() - 1)
+        # bucketize returns the first entry >= |y|; |y| is on the grid, so that entry is |y| itself
+        code = (idx | ((y < 0).long() << (self.width - 1))).to(torch.int64).reshape(-1)
+        nbits = code.numel() * self.width
+        bits = ((code.unsqueeze(1) >> torch.arange(self.width, device=v.device)) & 1).to(torch.uint8).reshape(-1)
+        pad = (-nbits) % 8
+        if pad:
+            bits = torch.cat([bits, torch.zeros(pad, dtype=torch.uint8, device=v.device)])
+        weights = (1 << torch.arange(8, device=v.device)).to(torch.uint8)
+        payload = (bits.reshape(-1, 8) * weights).sum(dim=1).to(torch.uint8)
+        return torch.cat([(e + 127).to(torch.uint8), payload])
+
+    def decode(self, msg, numel):
+        nb = (numel + self.BLOCK - 1) // self.BLOCK
+        e = msg[:nb].float() - 127.0
+        payload = msg[nb:]
+        bits = ((payload.unsqueeze(1) >> torch.arange(8, device=msg.device)) & 1).reshape(-1)[: nb * self.BLOCK * self.width]
+        code = (bits.reshape(-1, self.width).long() << torch.arange(self.width, device=msg.device)).sum(dim=1)
+        sign = 1.0 - 2.0 * ((code >> (self.width - 1)) & 1).float()
+        mag = self._table(msg.device)[(code & ((1 << (self.width - 1)) - 1)).clamp_max(self.table.numel() - 1)]
+        y = (sign * mag).reshape(nb, self.BLOCK) * torch.pow(torch.tensor(2.0, device=msg.device), e).unsqueeze(1)
+        return y.reshape(-1)[:numel]
+
+
+class IntBinsCodec(TorchCodec):
+    """Integer bins carried exactly (int16 on the wire): sums of bins stay integers."""
+
+    align = 8
+
+    def message_bytes(self, numel: int) -> int:
+        return numel * 2
+
+    def encode(self, v, first, tag):
+        return torch.round(v).clamp_(-32768, 32767).to(torch.int16).contiguous().view(torch.uint8).reshape(-1)
+
+    def decode(self, msg, numel):
+        return msg.view(torch.int16)[:numel].float()

@@ -46,6 +46,9 @@ class RhtCodecCPU:
     def decode(self, msg: np.ndarray, nblocks: int) -> np.ndarray:
         return cr.decode_blocks(msg, nblocks, self.bits)
 
+    def decode_add(self, msg: np.ndarray, nblocks: int, acc: np.ndarray) -> np.ndarray:
+        return cr.decode_add_blocks(msg, nblocks, self.bits, acc)
+
     def finish(self, y: np.ndarray) -> np.ndarray:
         return cr.rotate_inv(y, self.signs, 1.0 / self.world)
 
@@ -152,7 +155,7 @@ def run_rank(x: np.ndarray, codec, rank: int, world: int, topology: str, ep) -> 
             continue
         v = blocks[lo:hi] if st.local == sch.LOCAL_WS else codec.rotate(blocks[lo:hi])
         for k in range(st.nrecv):
-            v = (v + codec.decode(ep.recv(st.recv_slot + k), nb)).astype(np.float32)
+            v = codec.decode_add(ep.recv(st.recv_slot + k), nb, v)
         if st.out == sch.OUT_STORE:
             blocks[lo:hi] = v
         elif st.out == sch.OUT_SEND:

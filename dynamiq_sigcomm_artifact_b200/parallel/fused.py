@@ -66,7 +66,8 @@ def program_tensor(rank: int, world: int, topology: str) -> torch.Tensor:
     return torch.tensor([s.as_ints() for s in prog], dtype=torch.int32)
 
 
-STATUS_MESSAGES = {1: "timed out waiting for a peer's flag", 2: "malformed step program"}
+STATUS_MESSAGES = {1: "timed out waiting for a peer's flag", 2: "malformed step program",
+                   3: "a bulk copy into shared memory did not complete"}
 
 
 def decode_status(words: Sequence[int]) -> Optional[str]:

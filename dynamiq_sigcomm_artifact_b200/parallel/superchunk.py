@@ -1,0 +1,97 @@
+"""The reference-faithful DynamiQ path: mean-centred superchunks in 8 / 4 / 2-bit groups.
+
+Per bucket (testbed_evaluation/new_comm_hooks/comm_hooks.py:681-780, dynamic-bitrate variant
+:903-1144):
+
+1. split into 256-element superchunks, subtract each superchunk's mean, keep
+   ``stats = (mean / W, sum((x / W)^2))`` (kernel K21, cuda_hadamard.cu:1304-1349);
+2. all-reduce the stats (sum) -> mean of means and the summed energies ``F_i``;
+3. choose a code width per superchunk from ``F_i``: by the threshold table of the method name,
+   or by the dynamic-bitrate controller (``bitalloc.py``);
+4. for each non-empty group gather its rows, all-reduce them with the hierarchical AEE / MEE
+   codec of that width over the method's topology, scatter them back;
+5. add the mean of means back (K22, cuda_hadamard.cu:1351-1369).
+
+This implementation runs on the device-agnostic backend (``torch_backend.py``), so it works
+under gloo on CPU and under NCCL point-to-point on GPUs.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .. import bitalloc
+from .codecs import SUPERCHUNK, SuperchunkCodec
+from .torch_backend import allreduce_torch
+
+
+def mean_center(x: torch.Tensor, world: int):
+    """x [n] -> (residual [nsc, 256] fp32, stats [nsc, 2] fp32 = (mean / W, sum((x/W)^2)))."""
+    n = x.numel()
+    nsc = (n + SUPERCHUNK - 1) // SUPERCHUNK
+    pad = torch.zeros(nsc * SUPERCHUNK, dtype=torch.float32, device=x.device)
+    pad[:n] = torch.nan_to_num(x.float(), nan=0.0, posinf=0.0, neginf=0.0)
+    rows = pad.view(nsc, SUPERCHUNK)
+    valid = torch.full((nsc,), SUPERCHUNK, dtype=torch.float32, device=x.device)
+    if n % SUPERCHUNK:
+        valid[-1] = n % SUPERCHUNK
+    mean = rows.sum(dim=1) / SUPERCHUNK  # the reference averages over the padded 256 as well
+    resid = rows - mean.unsqueeze(1)
+    if n % SUPERCHUNK:
+        resid[-1, n % SUPERCHUNK:] = 0.0  # zero padded tail (cuda_hadamard.cu:1336-1342)
+    stats = torch.stack([mean / world, (rows / world).pow(2).sum(dim=1)], dim=1)
+    return resid, stats
+
+
+def superchunk_allreduce(state, bucket) -> torch.futures.Future:
+    spec, cfg = state["spec"], state["config"]
+    group = state["group"]
+    world = dist.get_world_size(group)
+    buf = bucket.buffer()
+    n = buf.numel()
+    fut = torch.futures.Future()
+    if world == 1 or n == 0:
+        fut.set_result(buf)
+        return fut
+    step, index = int(state["batch_idx"]), bucket.index()
+    resid, stats = mean_center(buf, world)
+    dist.all_reduce(stats, group=group)
+    mean_of_means, energy = stats[:, 0], stats[:, 1]
+    params = state["params"]
+    if spec.dynamic_bitrate:
+        ctl = params.get("bitrate")
+        if ctl is None:
+            ctl = params["bitrate"] = bitalloc.DynamicBitrateController(spec.bits)
+            if "bitrate_u" in params:
+                ctl.u, ctl.initialised = float(params["bitrate_u"]), True
+        ctl.observe(energy)
+        groups = bitalloc.split_by_bitrate(energy, ctl.u)
+    else:
+        groups = bitalloc.split_by_thresholds(energy, spec.thresholds, fixed=spec.fixed)
+    st = state["stats"]
+    st["collectives"] += 1
+    st["buckets"][index] = {"numel": n, "groups": {b: int(i.numel()) for b, i in groups.items()}}
+    done = torch.zeros(resid.shape[0], dtype=torch.bool, device=resid.device)
+    for gid, bits in enumerate((8, 4, 2)):
+        idx = groups[bits]
+        if idx.numel() == 0:
+            continue
+        done[idx] = True
+        rows = resid.index_select(0, idx).reshape(-1)
+        if spec.no_compress:
+            rows = rows / world
+        else:
+            codec = SuperchunkCodec(bits, spec.lattice, cfg.seed, step, (index << 2) | gid)
+            rows = allreduce_torch(rows, codec, spec.topology, group, transmit=not spec.compute_only)
+        resid.index_copy_(0, idx, rows.view(-1, SUPERCHUNK))
+    if not bool(done.all()):  # rows of a dropped group keep their local share, as in the reference
+        resid[~done] /= world
+    out = (resid + mean_of_means.unsqueeze(1)).reshape(-1)[:n]
+    buf.copy_(out.to(buf.dtype))
+    if spec.dynamic_bitrate and bucket.is_last():
+        ctl = params["bitrate"]
+        ctl.end_of_step()
+        params["bitrate_u"] = ctl.u
+        params["bitrate_last_avg_bits"] = ctl.last_avg
+    fut.set_result(buf)
+    return fut

@@ -45,21 +45,22 @@ def philox4x32(c0, c1, c2, c3, k0, k1, rounds: int = 10):
     return tuple(c.astype(np.uint32) for c in (c0, c1, c2, c3))
 
 
-def block_uniforms16(block_idx, tag: int, step: int, seed: int) -> np.ndarray:
-    """16-bit uniforms for whole 1024-element blocks.
+UNIFORM_ROUNDS = 7  # Philox-4x32-7 (the shortest crush-resistant variant) for the rounding uniforms
 
-    Returns uint16 array ``[len(block_idx), 32 lanes, 32 values]``.  Lane ``l`` makes four
-    Philox calls (counter word c1 = 4*l + q); call ``q`` yields values ``8q .. 8q+7`` as the
-    low and high halves of its four output words.
+
+def block_uniforms8(block_idx, tag: int, step: int, seed: int) -> np.ndarray:
+    """8-bit uniforms for whole 1024-element blocks.
+
+    Returns uint8 array ``[len(block_idx), 32 lanes, 32 values]``.  Lane ``l`` makes two
+    Philox-4x32-7 calls (counter word c1 = 2*l + q); call ``q`` yields values ``16q .. 16q+15``
+    as the bytes, least significant first, of its four output words.
     """
     block_idx = np.asarray(block_idx, dtype=np.uint64).reshape(-1, 1)
-    call = np.arange(128, dtype=np.uint64).reshape(1, -1)
-    w = philox4x32(block_idx, call, tag, step, seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
-    words = np.stack(w, axis=-1)  # [nb, 128 calls, 4 words]
-    lo = (words & np.uint32(0xFFFF)).astype(np.uint16)
-    hi = (words >> np.uint32(16)).astype(np.uint16)
-    halves = np.stack([lo, hi], axis=-1).reshape(len(block_idx), 128, 8)
-    return halves.reshape(len(block_idx), 32, 32)
+    call = np.arange(64, dtype=np.uint64).reshape(1, -1)
+    w = philox4x32(block_idx, call, tag, step, seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF, rounds=UNIFORM_ROUNDS)
+    words = np.stack(w, axis=-1)  # [nb, 64 calls, 4 words]
+    by = np.stack([(words >> np.uint32(8 * k)) & np.uint32(0xFF) for k in range(4)], axis=-1).astype(np.uint8)
+    return by.reshape(len(block_idx), 32, 32)
 
 
 def sign_words(step: int, bucket: int, seed: int) -> np.ndarray:

@@ -42,7 +42,7 @@ def test_standalone_ops_match_oracle_bytes(bits):
     # one hop: decode + add rotated local + re-encode
     x2 = heavy_tail_grad(n, 2)
     w2, s2 = codec.dec_comp((words, scales), torch.from_numpy(x2).cuda(), step=step, bucket_id=bucket)
-    v = (ref.rotate(cr.to_blocks(x2)) + cr.dequantize(codes, rscale, bits)).astype(np.float32)
+    v = cr.dequantize_add(codes, rscale, bits, ref.rotate(cr.to_blocks(x2)))
     c2, rs2 = cr.quantize(v, bits, np.arange(v.shape[0]), ref._tag_base | (sch.TAG_ENCODE + 1), step, seed)
     assert np.array_equal(w2.cpu().numpy().view(np.uint32), cr.pack(c2, bits))
     assert np.array_equal(s2.cpu().numpy(), rs2)

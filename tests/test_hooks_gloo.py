@@ -25,11 +25,13 @@ def _worker(rank, world, port, method, numel, steps, q):
 
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        args = Namespace(aggregation_method=method, topology=None, numel=numel, steps=steps, warmup_steps=2,
-                         seed=1234, dtype="float32", device="cpu", bucket_cap_mb=4000)
-        res = smoke_hooks.run(args)
+        out = []
+        for m in (method if isinstance(method, (list, tuple)) else [method]):
+            args = Namespace(aggregation_method=m, topology=None, numel=numel, steps=steps, warmup_steps=2,
+                             seed=1234, dtype="float32", device="cpu", bucket_cap_mb=4000)
+            out.append(smoke_hooks.run(args))
         if rank == 0:
-            q.put(res)
+            q.put(out if isinstance(method, (list, tuple)) else out[0])
     finally:
         dist.destroy_process_group()
 
@@ -78,3 +80,25 @@ def test_bf16_and_fp32_baselines_world2():
     assert max(r["nmse"]) < 1e-12
     r = _run("bf16", numel=1 << 16, steps=3)
     assert 0 < max(r["nmse"]) < 1e-4
+
+
+def test_every_method_family_world2():
+    """One pass over the reference's default evaluation matrix (plus fixed / butterfly / direct
+    variants) under gloo: every hook returns the same gradient on both ranks, within the error
+    its format allows."""
+    bounds = {
+        "dynamiQ_mee_5bit": 4e-2, "dynamiQ_aee_5bit_superchunk": 4e-2, "dynamiQ_aee_4bit_fixed": 5e-2,
+        "dynamiQ_mee_5bit_dynamic_bitrate": 4e-2, "dynamiQ_mee_4bit_butterfly": 0.1,
+        "dynamiQ_aee_8bit_direct": 5e-4, "MXfp8": 5e-3, "fp6": 1e-2, "fp4": 5e-2, "thc": 5e-2,
+        "omnireduce": 1.0, "fp16": 1e-6,
+    }
+    res = _run(list(bounds), numel=1 << 16, steps=4, world=2)
+    for r in res:
+        m = r["method"]
+        assert max(r["checksum_delta"]) < 1e-3, (m, r["checksum_delta"])
+        assert max(r["nmse"][:2]) < 1e-6, m
+        assert all(e <= bounds[m] for e in r["nmse"][2:]), (m, r["nmse"])
+        if m != "fp16":
+            assert all(e > 0 for e in r["nmse"][2:]), (m, r["nmse"])
+    zero = _run("zero", numel=1 << 12, steps=3, world=2)
+    assert zero["nmse"][2] > 0.1  # the traffic-free debug mode is wrong on purpose
