@@ -32,6 +32,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> norm_bwd(at::Tensor dy, at::Tenso
 std::tuple<at::Tensor, at::Tensor> ce_fwd(at::Tensor logits, at::Tensor labels, int64_t vocab, int64_t ignore_index);
 at::Tensor ce_bwd(at::Tensor logits, at::Tensor labels, at::Tensor lse, at::Tensor gout, at::Tensor n_valid,
                   int64_t vocab, int64_t ignore_index);
+std::tuple<at::Tensor, at::Tensor> fwht1024_tcgen05(at::Tensor x, int64_t seed, int64_t step, int64_t bucket,
+                                                    bool apply_signs, double scale, int64_t ctas);
 at::Tensor rope(at::Tensor x, at::Tensor cos, at::Tensor sin, bool backward);
 void adamw_step(at::Tensor table, at::Tensor numel, at::Tensor chunk_start, int64_t total_chunks, bool param_bf16,
                 bool grad_bf16, double lr, double beta1, double beta2, double eps, double weight_decay, int64_t step,
@@ -43,6 +45,7 @@ TORCH_LIBRARY(dq, m) {
   m.def("norm_bwd(Tensor dy, Tensor x, Tensor w, Tensor mean, Tensor rstd, bool rms) -> (Tensor, Tensor, Tensor)", &dq::norm_bwd);
   m.def("ce_fwd(Tensor logits, Tensor labels, int vocab, int ignore_index) -> (Tensor, Tensor)", &dq::ce_fwd);
   m.def("ce_bwd(Tensor(a!) logits, Tensor labels, Tensor lse, Tensor gout, Tensor n_valid, int vocab, int ignore_index) -> Tensor(a!)", &dq::ce_bwd);
+  m.def("fwht1024_tcgen05(Tensor x, int seed, int step, int bucket, bool apply_signs, float scale, int ctas) -> (Tensor, Tensor)", &dq::fwht1024_tcgen05);
   m.def("rope(Tensor x, Tensor cos, Tensor sin, bool backward) -> Tensor", &dq::rope);
   m.def("adamw_step(Tensor table, Tensor numel, Tensor chunk_start, int total_chunks, bool param_bf16, bool grad_bf16, "
         "float lr, float beta1, float beta2, float eps, float weight_decay, int step, float grad_scale) -> ()", &dq::adamw_step);
