@@ -182,6 +182,19 @@ def run_kernels(args) -> None:
                    "ctas": args.ctas, "threads": args.threads}
             rows.append(row)
             print(json.dumps(row), flush=True)
+    # the tensor-core Hadamard kernel on its own: reads and writes every element once
+    from ..ops import require
+
+    dq = require()
+    n4 = numel // 4096 * 4096
+    xin = x[:n4].contiguous()
+    ms = time_op(lambda: dq.fwht1024_tcgen05(xin, args.seed, 0, 0, True, 1.0 / 32.0, 0), lambda: None, args.iters,
+                 args.warmup)
+    row = {"kernel": "fwht1024_tcgen05", "numel": n4, "ms": ms, "gbs": 8 * n4 / ms / 1e6,
+           "gelem_s": n4 / ms / 1e6, "hbm_fraction_of_measured": 8 * n4 / ms / 1e6 / hbm,
+           "tf32_tflops": 2 * 2 * 2 * 32 * n4 / ms / 1e9}
+    rows.append(row)
+    print(json.dumps(row), flush=True)
     if args.out:
         with open(args.out, "w") as f:
             json.dump(rows, f, indent=1)
