@@ -20,6 +20,7 @@ import torch
 import torch.distributed as dist
 
 from .config import DynamiqConfig, MethodSpec, parse_method
+from .utils import tracing
 
 
 class HookState(dict):
@@ -159,7 +160,7 @@ def _rht_allreduce(state: HookState, bucket) -> torch.futures.Future:
             stream = state["comm_stream"]
             stream.wait_stream(torch.cuda.current_stream())
             fut = torch.futures.Future(devices=[buf.device])
-            with torch.cuda.stream(stream):
+            with torch.cuda.stream(stream), tracing.nvtx_range(f"bucket{index}.fused_{spec.topology}_{bits}bit"):
                 eng.allreduce_(buf, bits, spec.topology, cfg.seed, step, index, no_transmit=spec.compute_only)
                 buf.record_stream(stream)
                 if exact is not None:

@@ -56,10 +56,13 @@ class RhtCodecCPU:
 class LocalTransport:
     """Mailboxes between threads of one process (one thread per simulated rank)."""
 
-    def __init__(self, world: int):
+    def __init__(self, world: int, timeout: float = 60.0, drop=None):
+        """`drop(src, dst, slot) -> bool` lets a test lose messages; `timeout` bounds every receive."""
         self.boxes: List[Dict[int, "queue.Queue"]] = [dict() for _ in range(world)]
         self.lock = threading.Lock()
         self.sent_bytes = [0] * world
+        self.timeout = timeout
+        self.drop = drop
 
     def _box(self, rank: int, slot: int) -> "queue.Queue":
         with self.lock:
@@ -78,10 +81,15 @@ class LocalEndpoint:
 
     def send(self, dst: int, slot: int, msg: np.ndarray) -> None:
         self.t.sent_bytes[self.rank] += msg.nbytes
+        if self.t.drop is not None and self.t.drop(self.rank, dst, slot):
+            return
         self.t._box(dst, slot).put(msg.copy())
 
-    def recv(self, slot: int, timeout: float = 60.0) -> np.ndarray:
-        return self.t._box(self.rank, slot).get(timeout=timeout)
+    def recv(self, slot: int, timeout: Optional[float] = None) -> np.ndarray:
+        try:
+            return self.t._box(self.rank, slot).get(timeout=self.t.timeout if timeout is None else timeout)
+        except queue.Empty:
+            raise TimeoutError(f"rank {self.rank}: no message in slot {slot} within the time budget") from None
 
     def flush(self) -> None:
         pass
@@ -171,10 +179,11 @@ def run_rank(x: np.ndarray, codec, rank: int, world: int, topology: str, ep) -> 
 
 
 def simulate_allreduce(xs: Sequence[np.ndarray], bits: int, topology: str = "ring", seed: int = 0,
-                       step: int = 0, bucket: int = 0, codec_factory=None, return_transport: bool = False):
+                       step: int = 0, bucket: int = 0, codec_factory=None, return_transport: bool = False,
+                       transport: Optional[LocalTransport] = None):
     """Run all ranks of one collective as threads; returns the per-rank results."""
     world = len(xs)
-    transport = LocalTransport(world)
+    transport = transport or LocalTransport(world)
     out: List[Optional[np.ndarray]] = [None] * world
     errs: List[BaseException] = []
 

@@ -59,6 +59,28 @@ def nvlink_summary(device: int) -> dict:
         return {}
 
 
+def validate_metas(metas, device: int, p2p) -> None:
+    """Handshake checks before any peer mapping is opened: one host, one GPU per rank, rank order,
+    and peer access from `device` to every other rank's GPU (`p2p[i, j, 0]`).  The reference
+    validates rank layout and NVLink pairs the same way before it connects
+    (testbed_evaluation/new_comm_hooks/ring_rdma.py:144-161, validate_nvlink_pair)."""
+    if any(m is None for m in metas):
+        raise TopologyError("a rank did not publish its metadata")
+    if [m.rank for m in metas] != list(range(len(metas))):
+        raise TopologyError(f"rank metadata out of order: {[m.rank for m in metas]}")
+    hosts = {m.host for m in metas}
+    if len(hosts) != 1:
+        raise TopologyError(f"symmetric buffers need all ranks on one host, got {sorted(hosts)}")
+    devs = [m.device for m in metas]
+    if len(set(devs)) != len(devs):
+        raise TopologyError(f"two ranks share a GPU: {devs}")
+    if any(len(m.handle) != 64 for m in metas):
+        raise TopologyError("malformed IPC handle (expected 64 bytes)")
+    for m in metas:
+        if m.device != device and not int(p2p[device][m.device][0]):
+            raise TopologyError(f"GPU {device} cannot access GPU {m.device} peer-to-peer")
+
+
 class SymmetricBuffer:
     """One allocation per rank of a group, all of them mapped into this process."""
 
@@ -92,16 +114,7 @@ class SymmetricBuffer:
         self._closed = False
 
     def _validate(self) -> None:
-        hosts = {m.host for m in self.metas}
-        if len(hosts) != 1:
-            raise TopologyError(f"symmetric buffers need all ranks on one host, got {sorted(hosts)}")
-        devs = [m.device for m in self.metas]
-        if len(set(devs)) != len(devs):
-            raise TopologyError(f"two ranks share a GPU: {devs}")
-        mat = p2p_matrix()
-        for m in self.metas:
-            if m.device != self.device and not int(mat[self.device, m.device, 0]):
-                raise TopologyError(f"GPU {self.device} cannot access GPU {m.device} peer-to-peer")
+        validate_metas(self.metas, self.device, p2p_matrix())
 
     def local(self) -> torch.Tensor:
         """This rank's buffer as a uint8 tensor (no ownership)."""
