@@ -98,9 +98,16 @@ def rotate_inv(y: np.ndarray, signs: np.ndarray, post_scale: float = 1.0) -> np.
     return (v * F32(post_scale / 1024.0)) * signs[None, :]
 
 
-def quantize(y: np.ndarray, bits: int, block_idx: np.ndarray, tag: int, step: int, seed: int
-             ) -> Tuple[np.ndarray, np.ndarray]:
-    """Rotated blocks [nb, 1024] -> (codes uint8 [nb, 32 lanes, 32 regs], scale f32 [nb])."""
+TAG_STRATIFIED = 0x4000
+
+
+def quantize(y: np.ndarray, bits: int, block_idx: np.ndarray, tag: int, step: int, seed: int,
+             rank: int = 0, world: int = 1) -> Tuple[np.ndarray, np.ndarray]:
+    """Rotated blocks [nb, 1024] -> (codes uint8 [nb, 32 lanes, 32 regs], scale f32 [nb]).
+
+    With TAG_STRATIFIED set in `tag` the uniform of value k is the rank's stratum of a uniform all
+    ranks share: u = (((rank + shift) mod W) * 256 + byte_k + 0.5) / (256 W), where shift is the
+    byte of the neighbouring value ((k + 1) mod 32 of the same lane)."""
     R = qmax(bits)
     y = y.astype(F32, copy=False)
     absmax = np.max(np.abs(y), axis=1)
@@ -108,8 +115,13 @@ def quantize(y: np.ndarray, bits: int, block_idx: np.ndarray, tag: int, step: in
         ok = (absmax >= F32(1e-30)) & np.isfinite(absmax)
         scale = np.where(ok, absmax / F32(R), F32(0)).astype(F32)
         inv = np.where(ok, F32(R) / absmax, F32(0)).astype(F32)
-    r8 = philox.block_uniforms8(block_idx, tag, step, seed)  # [nb, 32, 32]
-    u = (r8.astype(F32) + F32(0.5)) * F32(1.0 / 256.0)
+    r8 = philox.block_uniforms8(block_idx, tag & ~TAG_STRATIFIED, step, seed)  # [nb, 32, 32]
+    if tag & TAG_STRATIFIED and world > 1:
+        shift = np.roll(r8, -1, axis=2).astype(np.int64)
+        stratum = ((rank + shift) % world).astype(F32)
+        u = ((stratum * F32(256.0) + r8.astype(F32)) + F32(0.5)) * F32(1.0 / (256.0 * world))
+    else:
+        u = (r8.astype(F32) + F32(0.5)) * F32(1.0 / 256.0)
     t = fma32(y[:, RHO], inv[:, None, None], u)
     code = np.clip(np.floor(t), -R, R).astype(np.int32) + R
     return code.astype(np.uint8), scale
@@ -176,8 +188,9 @@ def from_message(msg: np.ndarray, nblocks: int, bits: int) -> Tuple[np.ndarray, 
     return words, scale
 
 
-def encode_blocks(y: np.ndarray, bits: int, block_idx, tag: int, step: int, seed: int) -> np.ndarray:
-    codes, scale = quantize(y, bits, np.asarray(block_idx), tag, step, seed)
+def encode_blocks(y: np.ndarray, bits: int, block_idx, tag: int, step: int, seed: int, rank: int = 0,
+                  world: int = 1) -> np.ndarray:
+    codes, scale = quantize(y, bits, np.asarray(block_idx), tag, step, seed, rank, world)
     return to_message(pack(codes, bits), scale)
 
 

@@ -226,9 +226,14 @@ __device__ __forceinline__ float warp_absmax(const float (&y)[32]) {
 //   code = clamp(floor(fma(y, R / absmax, u)), -R, R) + R,   u = (byte + 0.5) / 256
 // computed 256 times larger so that u needs no multiply, with the floor taken by a round-down
 // add of 1.5 * 2^31 (one ulp = 256 there): no int<->float conversion instruction is issued.
+//
+// Stratified ("correlated") rounding, strat_world > 1: all ranks draw the same byte per value and
+// rank r uses u = (((r + shift) mod W) * 256 + byte + 0.5) / (256 W), shift = the byte of the
+// lane's next value, so the W rounding errors that meet in a sum are negatively correlated.
 template <int B>
 __device__ __forceinline__ float quantize_block(const float (&y)[32], uint32_t (&w)[B], uint32_t block_idx,
-                                                uint32_t tag, uint32_t step, uint32_t k0, uint32_t k1, int lane) {
+                                                uint32_t tag, uint32_t step, uint32_t k0, uint32_t k1, int lane,
+                                                int strat_rank = 0, int strat_world = 1) {
   constexpr int R = (1 << (B - 1)) - 1;
   const float m = warp_absmax(y);
   const bool ok = (m >= 1e-30f) && (m <= 3.402823466e38f);
@@ -238,22 +243,49 @@ __device__ __forceinline__ float quantize_block(const float (&y)[32], uint32_t (
   const float2 half_off = make_float2(-8388607.5f, -8388607.5f);
   const float2 magic = make_float2(3221225472.0f, 3221225472.0f);  // 1.5 * 2^31 = 0x4F400000
   uint32_t c[32];
+  uint32_t rw[8];
 #pragma unroll
   for (int q = 0; q < 2; ++q) {
     U4 r = philox4x32<kUniformRounds>(block_idx, static_cast<uint32_t>(lane * 2 + q), tag, step, k0, k1);
-    const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+    rw[4 * q] = r.x, rw[4 * q + 1] = r.y, rw[4 * q + 2] = r.z, rw[4 * q + 3] = r.w;
+  }
+  if (strat_world > 1) {
+    const float cw = 1.0f / (256.0f * static_cast<float>(strat_world));
+    const uint32_t recip = 65536u / static_cast<uint32_t>(strat_world) + 1u;  // x / W for x < 512
+    const float2 inv2 = make_float2(inv, inv), cw2 = make_float2(cw, cw);
+    const float2 magic1 = make_float2(12582912.0f, 12582912.0f);  // 1.5 * 2^23 = 0x4B400000, one ulp = 1
 #pragma unroll
-    for (int mm = 0; mm < 16; mm += 2) {
+    for (int k = 0; k < 32; k += 2) {
+      float xs[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int kk = k + j, kn = (kk + 1) & 31;
+        const uint32_t byte = (rw[kk >> 2] >> (8 * (kk & 3))) & 0xFFu;
+        const uint32_t sh = ((rw[kn >> 2] >> (8 * (kn & 3))) & 0xFFu) + static_cast<uint32_t>(strat_rank);
+        const uint32_t stratum = sh - static_cast<uint32_t>(strat_world) * ((sh * recip) >> 16);
+        xs[j] = __uint_as_float(0x4B000000u | (stratum * 256u + byte));  // 2^23 + (stratum * 256 + byte)
+      }
+      const float2 u = __fmul2_rn(__fadd2_rn(make_float2(xs[0], xs[1]), half_off), cw2);
+      const float2 t = __ffma2_rn(make_float2(y[k], y[k + 1]), inv2, u);
+      const float2 f = __fadd2_rd(t, magic1);
+      const int c0 = static_cast<int>(__float_as_uint(f.x)) - 0x4B400000 + R;
+      const int c1 = static_cast<int>(__float_as_uint(f.y)) - 0x4B400000 + R;
+      c[k] = static_cast<uint32_t>(max(0, min(2 * R, c0)));
+      c[k + 1] = static_cast<uint32_t>(max(0, min(2 * R, c1)));
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 32; k += 2) {
       // 2^23 + byte as a float, straight from the byte (no conversion)
-      const float b0 = __uint_as_float(__byte_perm(rw[mm >> 2], 0x4B000000u, 0x7650u | (mm & 3)));
-      const float b1 = __uint_as_float(__byte_perm(rw[mm >> 2], 0x4B000000u, 0x7650u | ((mm + 1) & 3)));
+      const float b0 = __uint_as_float(__byte_perm(rw[k >> 2], 0x4B000000u, 0x7650u | (k & 3)));
+      const float b1 = __uint_as_float(__byte_perm(rw[k >> 2], 0x4B000000u, 0x7650u | ((k + 1) & 3)));
       const float2 u256 = __fadd2_rn(make_float2(b0, b1), half_off);  // byte + 0.5
-      const float2 t = __ffma2_rn(make_float2(y[16 * q + mm], y[16 * q + mm + 1]), inv256, u256);
+      const float2 t = __ffma2_rn(make_float2(y[k], y[k + 1]), inv256, u256);
       const float2 f = __fadd2_rd(t, magic);
       const int c0 = static_cast<int>(__float_as_uint(f.x)) - 0x4F400000 + R;
       const int c1 = static_cast<int>(__float_as_uint(f.y)) - 0x4F400000 + R;
-      c[16 * q + mm] = static_cast<uint32_t>(max(0, min(2 * R, c0)));
-      c[16 * q + mm + 1] = static_cast<uint32_t>(max(0, min(2 * R, c1)));
+      c[k] = static_cast<uint32_t>(max(0, min(2 * R, c0)));
+      c[k + 1] = static_cast<uint32_t>(max(0, min(2 * R, c1)));
     }
   }
   pack_codes<B>(c, w);

@@ -7,6 +7,7 @@ namespace dq {
 constexpr int kMaxWorld = 8;
 constexpr int kMaxSteps = 32;
 constexpr int kStepInts = 8;
+constexpr uint32_t kTagStratified = 0x4000u;  // step tag flag: stratified rounding (schedules.py)
 
 // local operand / result of a step: keep in sync with parallel/schedules.py
 enum : int { kLocalRaw = 0, kLocalWs = 1 };

@@ -148,7 +148,8 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
   for (int s = 0; s < p.nsteps; ++s) {
     const int local = p.steps[s][1], recv_slot = p.steps[s][2], nrecv = p.steps[s][3];
     const int out = p.steps[s][4], dst = p.steps[s][5], send_slot = p.steps[s][6];
-    const uint32_t tag = stream_tag(p.bucket_id, static_cast<uint32_t>(p.steps[s][7]));
+    const uint32_t tag = stream_tag(p.bucket_id, static_cast<uint32_t>(p.steps[s][7]) & ~kTagStratified);
+    const int strat_world = (static_cast<uint32_t>(p.steps[s][7]) & kTagStratified) ? p.world : 1;
     int shard_lo, lo, hi;
     step_range(p, s, cta, per_cta, shard_lo, lo, hi);
     if (hi <= lo) continue;  // producer and consumer agree on empty ranges: no flag traffic
@@ -219,7 +220,8 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
         if (blk == tail_block) store_block<float>(p.tail_ws, kBlock, true, lane, v);
         else store_block<T>(bucket + e0, kBlock, vec_ok, lane, v);
       } else if (out == kOutSend) {
-        scale = quantize_block<BITS>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi, lane);
+        scale = quantize_block<BITS>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi, lane, p.rank,
+                                     strat_world);
         if (!p.no_transmit) {
           uint8_t* slot = p.mail[dst] + static_cast<unsigned long long>(send_slot) * p.slot_stride;
           uint32_t* codes = reinterpret_cast<uint32_t*>(slot) + static_cast<size_t>(bs) * (BITS * 32);

@@ -161,18 +161,20 @@ def _rht_allreduce(state: HookState, bucket) -> torch.futures.Future:
             stream.wait_stream(torch.cuda.current_stream())
             fut = torch.futures.Future(devices=[buf.device])
             with torch.cuda.stream(stream), tracing.nvtx_range(f"bucket{index}.fused_{spec.topology}_{bits}bit"):
-                eng.allreduce_(buf, bits, spec.topology, cfg.seed, step, index, no_transmit=spec.compute_only)
+                eng.allreduce_(buf, bits, spec.topology, cfg.seed, step, index, no_transmit=spec.compute_only,
+                               correlated=spec.correlated)
                 buf.record_stream(stream)
                 if exact is not None:
                     _account_error(state, buf, exact)
                 fut.set_result(buf)
             return fut
-        eng.allreduce_(buf, bits, spec.topology, cfg.seed, step, index, no_transmit=spec.compute_only)
+        eng.allreduce_(buf, bits, spec.topology, cfg.seed, step, index, no_transmit=spec.compute_only,
+                               correlated=spec.correlated)
     else:
         from .parallel.cpu_backend import allreduce_gloo
 
         out = allreduce_gloo(buf.detach().float().numpy(), bits, spec.topology, cfg.seed, step, index,
-                             group=state["group"])
+                             group=state["group"], correlated=spec.correlated)
         buf.copy_(torch.from_numpy(out).to(buf.dtype))
     if exact is not None:
         _account_error(state, buf, exact)

@@ -28,8 +28,9 @@ class RhtCodecCPU:
 
     block = cr.BLOCK
 
-    def __init__(self, bits: int, seed: int, step: int, bucket: int, world: int):
+    def __init__(self, bits: int, seed: int, step: int, bucket: int, world: int, rank: int = 0):
         self.bits, self.seed, self.step, self.bucket, self.world = bits, seed, step, bucket, world
+        self.rank = rank
         self.signs = philox.sign_vector(step, bucket, seed)
         # the RNG stream id mixes the bucket in so that buckets do not share uniforms
         self._tag_base = (bucket & 0xFFFF) << 16
@@ -41,7 +42,8 @@ class RhtCodecCPU:
         return cr.rotate_fwd(x_blocks, self.signs)
 
     def encode(self, y: np.ndarray, block_idx: np.ndarray, tag: int) -> np.ndarray:
-        return cr.encode_blocks(y, self.bits, block_idx, self._tag_base | tag, self.step, self.seed)
+        return cr.encode_blocks(y, self.bits, block_idx, self._tag_base | tag, self.step, self.seed, self.rank,
+                                self.world)
 
     def decode(self, msg: np.ndarray, nblocks: int) -> np.ndarray:
         return cr.decode_blocks(msg, nblocks, self.bits)
@@ -133,7 +135,7 @@ class GlooEndpoint:
         self._sends.clear()
 
 
-def message_sizes(codec, nblocks: int, world: int, topology: str, rank: int) -> Dict[int, int]:
+def message_sizes(codec, nblocks: int, world: int, topology: str, rank: int) -> Dict[int, int]:  # noqa: D401
     """{slot: bytes} of every message `rank` receives."""
     sizes = {}
     progs = sch.build_all(world, topology)
@@ -147,13 +149,14 @@ def message_sizes(codec, nblocks: int, world: int, topology: str, rank: int) -> 
     return sizes
 
 
-def run_rank(x: np.ndarray, codec, rank: int, world: int, topology: str, ep) -> np.ndarray:
+def run_rank(x: np.ndarray, codec, rank: int, world: int, topology: str, ep, correlated: bool = False
+             ) -> np.ndarray:
     """Execute `rank`'s program on its flat fp32 gradient `x`; returns the mean estimate."""
     n = x.size
     blocks = cr.to_blocks(x)
     nblocks = blocks.shape[0]
     ep.expect(sch.incoming(world, topology)[rank], message_sizes(codec, nblocks, world, topology, rank))
-    for st in sch.build_program(rank, world, topology):
+    for st in sch.build_program(rank, world, topology, correlated):
         lo, hi = sch.shard_range(nblocks, world, st.shard)
         nb = hi - lo
         idx = np.arange(lo, hi)
@@ -180,7 +183,7 @@ def run_rank(x: np.ndarray, codec, rank: int, world: int, topology: str, ep) -> 
 
 def simulate_allreduce(xs: Sequence[np.ndarray], bits: int, topology: str = "ring", seed: int = 0,
                        step: int = 0, bucket: int = 0, codec_factory=None, return_transport: bool = False,
-                       transport: Optional[LocalTransport] = None):
+                       transport: Optional[LocalTransport] = None, correlated: bool = False):
     """Run all ranks of one collective as threads; returns the per-rank results."""
     world = len(xs)
     transport = transport or LocalTransport(world)
@@ -189,8 +192,9 @@ def simulate_allreduce(xs: Sequence[np.ndarray], bits: int, topology: str = "rin
 
     def work(r: int) -> None:
         try:
-            codec = (codec_factory or RhtCodecCPU)(bits, seed, step, bucket, world)
-            out[r] = run_rank(np.asarray(xs[r], dtype=np.float32), codec, r, world, topology, transport.endpoint(r))
+            codec = (codec_factory or RhtCodecCPU)(bits, seed, step, bucket, world, r)
+            out[r] = run_rank(np.asarray(xs[r], dtype=np.float32), codec, r, world, topology, transport.endpoint(r),
+                              correlated)
         except BaseException as e:  # surfaced to the caller below
             errs.append(e)
 
@@ -205,13 +209,14 @@ def simulate_allreduce(xs: Sequence[np.ndarray], bits: int, topology: str = "rin
 
 
 def allreduce_gloo(x: np.ndarray, bits: int, topology: str, seed: int, step: int, bucket: int, group=None,
-                   codec_factory=None) -> np.ndarray:
+                   codec_factory=None, correlated: bool = False) -> np.ndarray:
     """One compressed all-reduce (mean) of a flat fp32 array over a gloo process group."""
     import torch.distributed as dist
 
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     if world == 1:
         return np.asarray(x, dtype=np.float32).copy()
-    codec = (codec_factory or RhtCodecCPU)(bits, seed, step, bucket, world)
+    codec = (codec_factory or RhtCodecCPU)(bits, seed, step, bucket, world, rank)
     tag_base = ((step & 0xFF) << 16) | ((bucket & 0xFF) << 8)
-    return run_rank(np.asarray(x, dtype=np.float32), codec, rank, world, topology, GlooEndpoint(group, tag_base))
+    return run_rank(np.asarray(x, dtype=np.float32), codec, rank, world, topology, GlooEndpoint(group, tag_base),
+                    correlated)

@@ -61,8 +61,8 @@ class Layout:
         return _align(self.scales_off + 4 * self.blocks_per_shard, 256)
 
 
-def program_tensor(rank: int, world: int, topology: str) -> torch.Tensor:
-    prog = sch.build_program(rank, world, topology)
+def program_tensor(rank: int, world: int, topology: str, correlated: bool = False) -> torch.Tensor:
+    prog = sch.build_program(rank, world, topology, correlated)
     return torch.tensor([s.as_ints() for s in prog], dtype=torch.int32)
 
 
@@ -92,7 +92,7 @@ class FusedAllreduce:
         self.validate = validate
         self.device = torch.cuda.current_device()
         self.epoch = 0
-        self._programs: Dict[str, torch.Tensor] = {}
+        self._programs: Dict[tuple, torch.Tensor] = {}
         self.buf: Optional[SymmetricBuffer] = None
         self.max_numel = 0
         self._alloc(max_numel)
@@ -118,14 +118,15 @@ class FusedAllreduce:
         if numel > self.max_numel:
             self._alloc(max(numel, int(self.max_numel * 1.5)))
 
-    def program(self, topology: str) -> torch.Tensor:
-        if topology not in self._programs:
-            self._programs[topology] = program_tensor(self.rank, self.world, topology)
-        return self._programs[topology]
+    def program(self, topology: str, correlated: bool = False) -> torch.Tensor:
+        key = (topology, correlated)
+        if key not in self._programs:
+            self._programs[key] = program_tensor(self.rank, self.world, topology, correlated)
+        return self._programs[key]
 
     # -- the collective --------------------------------------------------------------------
     def allreduce_(self, bucket: torch.Tensor, bits: int, topology: str = "ring", seed: int = 0, step: int = 0,
-                   bucket_id: int = 0, no_transmit: bool = False) -> torch.Tensor:
+                   bucket_id: int = 0, no_transmit: bool = False, correlated: bool = False) -> torch.Tensor:
         """In-place mean all-reduce of a flat fp32/bf16 CUDA tensor on the current stream."""
         if self.world == 1:
             return bucket
@@ -136,7 +137,7 @@ class FusedAllreduce:
         mail = [p + parity * self.set_bytes for p in self.buf.ptrs]
         flags = [p + self.off_flags for p in self.buf.ptrs]
         self.ops.fused_allreduce(
-            bucket, self.program(topology), mail, flags, self.set_bytes, 2 * self.flag_words_per_set, self.nslots,
+            bucket, self.program(topology, correlated), mail, flags, self.set_bytes, 2 * self.flag_words_per_set, self.nslots,
             self.buf.local_ptr + self.off_status, self.buf.local_ptr + self.off_tail, self.rank, self.world, bits,
             self.ctas, self.threads, lay.blocks_per_shard, lay.slot_stride, lay.scales_off,
             parity * self.flag_words_per_set, self.epoch, seed, step, bucket_id, 1.0 / self.world, self.timeout_ns,
@@ -194,8 +195,9 @@ class LocalCluster:
             self.threads, lay.blocks_per_shard, lay.slot_stride, lay.scales_off, 0, self.epoch, seed, step, bucket_id,
             (1.0 / self.world) if post_scale is None else post_scale, self.timeout_ns, no_transmit)
 
-    def allreduce_(self, buckets: List[torch.Tensor], bits: int, topology: str = "ring", **kw) -> List[torch.Tensor]:
-        progs = torch.stack([program_tensor(r, self.world, topology) for r in range(self.world)])
+    def allreduce_(self, buckets: List[torch.Tensor], bits: int, topology: str = "ring", correlated: bool = False,
+                   **kw) -> List[torch.Tensor]:
+        progs = torch.stack([program_tensor(r, self.world, topology, correlated) for r in range(self.world)])
         self.run(buckets, progs, bits, **kw)
         return buckets
 

@@ -61,6 +61,18 @@ class Step:
 STEP_INTS = 8
 TAG_ENCODE = 0x100
 TAG_FINAL = 0x200
+TAG_STRATIFIED = 0x4000  # flag: round with the rank's stratum of a uniform shared by all ranks
+
+
+def stratify(prog: List["Step"]) -> List["Step"]:
+    """Correlated rounding: every reduce-scatter encode of a block draws from one shared uniform
+    per value, u_r = ((r + shift) mod W + u0) / W, so that the W rounding errors that meet in the
+    sum are negatively correlated (the reference's `correlated` methods load per-rank stratified
+    pools, testbed_evaluation/new_comm_hooks/utils_aggregation.py:385-387,
+    simulations_llm/gen_correlated_rand.py:37-56).  The owner's final encode stays independent."""
+    import dataclasses
+
+    return [dataclasses.replace(st, tag=TAG_ENCODE | TAG_STRATIFIED) if st.out == OUT_SEND else st for st in prog]
 
 
 def calc_order(rank: int, size: int) -> List[Tuple[int, int, int, int]]:
@@ -109,7 +121,9 @@ def owner_of(world: int, topology: str, shard: int) -> int:
     return (shard - 1) % world  # ring and butterfly: rank r ends up owning shard r+1
 
 
-def build_program(rank: int, world: int, topology: str) -> List[Step]:
+def build_program(rank: int, world: int, topology: str, correlated: bool = False) -> List[Step]:
+    if correlated:
+        return stratify(build_program(rank, world, topology))
     W = world
     if topology not in TOPOLOGIES:
         raise ValueError(f"unknown topology {topology!r}")
@@ -140,7 +154,10 @@ def build_program(rank: int, world: int, topology: str) -> List[Step]:
     else:  # direct
         for k in range(1, W):
             dst = (rank + k) % W
-            steps.append(Step(shard=dst, out=OUT_SEND, dst=dst, send_slot=(rank - dst - 1) % W, tag=TAG_ENCODE))
+            # every source rank rounds with its own RNG stream: with a shared stream the W-1 rounding
+            # errors of a block would share the term (u - 1/2) and add coherently at the owner
+            steps.append(Step(shard=dst, out=OUT_SEND, dst=dst, send_slot=(rank - dst - 1) % W,
+                              tag=TAG_ENCODE + rank))
         own = rank
         steps.append(Step(shard=own, recv_slot=0, nrecv=W - 1, out=OUT_FINAL, tag=TAG_FINAL,
                           send_slot=ag_slot(W, topology, own)))
@@ -152,8 +169,8 @@ def build_program(rank: int, world: int, topology: str) -> List[Step]:
     return steps
 
 
-def build_all(world: int, topology: str) -> List[List[Step]]:
-    return [build_program(r, world, topology) for r in range(world)]
+def build_all(world: int, topology: str, correlated: bool = False) -> List[List[Step]]:
+    return [build_program(r, world, topology, correlated) for r in range(world)]
 
 
 def incoming(world: int, topology: str) -> List[Dict[int, int]]:

@@ -107,3 +107,19 @@ def test_wait_budget_expiry_returns_an_error_status():
     cl2.allreduce_(bufs, 8, "ring")
     cl2.check()
     assert float((bufs[0] - x).abs().max()) < 0.2
+
+
+@pytest.mark.parametrize("topology,world", [("direct", 8), ("ring", 4), ("butterfly", 4), ("direct", 3)])
+def test_correlated_rounding_matches_simulator_and_lowers_error(topology, world):
+    n, bits, seed = 24 * 1024 + 100, 5, 77
+    xs = [heavy_tail_grad(n, 50 + r) for r in range(world)]
+    want = cb.simulate_allreduce(xs, bits, topology, seed=seed, step=2, bucket=1, correlated=True)
+    cl = _cluster(world, n, ctas=4, threads=128)
+    bufs = [torch.from_numpy(x).cuda() for x in xs]
+    cl.allreduce_(bufs, bits, topology, correlated=True, seed=seed, step=2, bucket_id=1)
+    cl.check()
+    for r in range(world):
+        assert np.array_equal(bufs[r].cpu().numpy(), want[r]), f"rank {r}"
+    exact = np.mean(np.stack(xs).astype(np.float64), 0)
+    plain = cb.simulate_allreduce(xs, bits, topology, seed=seed, step=2, bucket=1)
+    assert cr.nmse(want[0], exact) < cr.nmse(plain[0], exact)

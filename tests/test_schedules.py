@@ -119,3 +119,19 @@ def test_wire_bytes_match_the_schedule():
 def test_butterfly_requantises_less_than_ring():
     assert sch.quantisations(8, "ring") == 8 and sch.quantisations(8, "butterfly") == 4
     assert sch.quantisations(8, "direct") == 2
+
+
+def test_direct_sources_round_with_distinct_streams_and_correlated_is_better():
+    progs = sch.build_all(4, "direct")
+    tags = {(r, st.tag) for r, p in enumerate(progs) for st in p if st.out == sch.OUT_SEND}
+    assert len({t for _, t in tags}) == 4  # one RNG stream per source rank
+    strat = sch.build_program(1, 4, "ring", correlated=True)
+    assert all((st.tag & sch.TAG_STRATIFIED) for st in strat if st.out == sch.OUT_SEND)
+    assert all(not (st.tag & sch.TAG_STRATIFIED) for st in strat if st.out != sch.OUT_SEND)
+    world, n = 8, 32 * 1024
+    xs = [heavy_tail_grad(n, 30 + r) for r in range(world)]
+    exact = np.mean(np.stack(xs).astype(np.float64), 0)
+    a = cb.simulate_allreduce(xs, 4, "direct", seed=9)
+    b = cb.simulate_allreduce(xs, 4, "direct", seed=9, correlated=True)
+    assert all(np.array_equal(b[0], o) for o in b)
+    assert cr.nmse(b[0], exact) < cr.nmse(a[0], exact)
