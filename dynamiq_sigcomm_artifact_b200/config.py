@@ -124,6 +124,7 @@ class DynamiqConfig:
     warmup_steps: int = 2  # steps served by the plain library all-reduce (reference: batch_idx 0 and 1)
     comm_ctas: int = 64  # CTAs of the persistent collective kernel (SM carve-out against backward)
     comm_threads: int = 256
+    rotation: str = "simt"  # "simt": fp32 butterflies (bit-exact with the CPU oracle); "tc": tcgen05 / TMEM
     wait_timeout_ms: int = 2000  # budget of every device-side wait before it gives up with an error status
     max_bucket_mb: int = 128  # symmetric-buffer capacity (grown on demand between steps)
     overlap: bool = True  # run the collective on a side stream under backward
@@ -140,6 +141,7 @@ class DynamiqConfig:
         c.wait_timeout_ms = int(1000 * _env(["DQ_TIMEOUT_SECONDS", "RING_RDMA_TIMEOUT_SECONDS"],
                                              c.wait_timeout_ms / 1000, float))
         c.max_bucket_mb = _env(["DQ_MAX_BUCKET_MB"], c.max_bucket_mb, int)
+        c.rotation = _env(["DQ_ROTATION"], c.rotation, str)
         c.overlap = _env(["DQ_OVERLAP", "RING_OVERLAP_LOCAL_P2P"], c.overlap, _bool)
         c.use_nvls = _env(["DQ_USE_NVLS"], c.use_nvls, _bool)
         c.debug = _env(["DQ_DEBUG", "RING_RDMA_DEBUG"], c.debug, _bool)

@@ -28,23 +28,31 @@ namespace dq {
 static constexpr int kBlock = 1024;  // codec block, elements
 
 // defined in fused_allreduce_b{2..8}.cu
-template <int BITS, typename T>
+template <int BITS, typename T, bool TC>
 void launch_one(const ARParams* host_params, const ARParams* dev_params, int nranks, int ctas, int threads,
                 cudaStream_t stream);
 
-template <typename T>
-static void launch_bits(int bits, const ARParams* hp, const ARParams* dp, int nranks, int ctas, int threads,
-                        cudaStream_t stream) {
+template <typename T, bool TC>
+static void launch_bits_tc(int bits, const ARParams* hp, const ARParams* dp, int nranks, int ctas, int threads,
+                           cudaStream_t stream) {
   switch (bits) {
-    case 2: launch_one<2, T>(hp, dp, nranks, ctas, threads, stream); break;
-    case 3: launch_one<3, T>(hp, dp, nranks, ctas, threads, stream); break;
-    case 4: launch_one<4, T>(hp, dp, nranks, ctas, threads, stream); break;
-    case 5: launch_one<5, T>(hp, dp, nranks, ctas, threads, stream); break;
-    case 6: launch_one<6, T>(hp, dp, nranks, ctas, threads, stream); break;
-    case 7: launch_one<7, T>(hp, dp, nranks, ctas, threads, stream); break;
-    case 8: launch_one<8, T>(hp, dp, nranks, ctas, threads, stream); break;
+    case 2: launch_one<2, T, TC>(hp, dp, nranks, ctas, threads, stream); break;
+    case 3: launch_one<3, T, TC>(hp, dp, nranks, ctas, threads, stream); break;
+    case 4: launch_one<4, T, TC>(hp, dp, nranks, ctas, threads, stream); break;
+    case 5: launch_one<5, T, TC>(hp, dp, nranks, ctas, threads, stream); break;
+    case 6: launch_one<6, T, TC>(hp, dp, nranks, ctas, threads, stream); break;
+    case 7: launch_one<7, T, TC>(hp, dp, nranks, ctas, threads, stream); break;
+    case 8: launch_one<8, T, TC>(hp, dp, nranks, ctas, threads, stream); break;
     default: TORCH_CHECK(false, "bits must be in 2..8, got ", bits);
   }
+}
+
+// hp->tensor_rotation (or dp's host copy, passed in `tensor`) selects tcgen05 or SIMT rotation
+template <typename T>
+static void launch_bits(int bits, const ARParams* hp, const ARParams* dp, int nranks, int ctas, int threads,
+                        cudaStream_t stream, bool tensor) {
+  if (tensor) launch_bits_tc<T, true>(bits, hp, dp, nranks, ctas, threads, stream);
+  else launch_bits_tc<T, false>(bits, hp, dp, nranks, ctas, threads, stream);
 }
 
 static void fill_common(ARParams& p, const at::Tensor& bucket, const at::Tensor& steps, int64_t rank, int64_t world,
@@ -110,7 +118,7 @@ void fused_allreduce(at::Tensor bucket, at::Tensor steps, std::vector<int64_t> m
                      int64_t status_ptr, int64_t tail_ws_ptr, int64_t rank, int64_t world, int64_t bits, int64_t ctas,
                      int64_t threads, int64_t blocks_per_shard, int64_t slot_stride, int64_t scales_off,
                      int64_t flag_base, int64_t epoch, int64_t seed, int64_t step, int64_t bucket_id,
-                     double post_scale, int64_t timeout_ns, bool no_transmit) {
+                     double post_scale, int64_t timeout_ns, bool no_transmit, bool tensor_rotation) {
   c10::cuda::CUDAGuard guard(bucket.device());
   TORCH_CHECK(static_cast<int64_t>(mail_ptrs.size()) == world && static_cast<int64_t>(flag_ptrs.size()) == world,
               "need one mailbox and one flag pointer per rank");
@@ -125,9 +133,9 @@ void fused_allreduce(at::Tensor bucket, at::Tensor steps, std::vector<int64_t> m
   check_layout(p, static_cast<int>(bits), mailbox_bytes, nslots, flag_words, static_cast<int>(ctas));
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   if (bucket.scalar_type() == at::kFloat)
-    launch_bits<float>(static_cast<int>(bits), &p, nullptr, 1, static_cast<int>(ctas), static_cast<int>(threads), stream);
+    launch_bits<float>(static_cast<int>(bits), &p, nullptr, 1, static_cast<int>(ctas), static_cast<int>(threads), stream, tensor_rotation);
   else
-    launch_bits<__nv_bfloat16>(static_cast<int>(bits), &p, nullptr, 1, static_cast<int>(ctas), static_cast<int>(threads), stream);
+    launch_bits<__nv_bfloat16>(static_cast<int>(bits), &p, nullptr, 1, static_cast<int>(ctas), static_cast<int>(threads), stream, tensor_rotation);
 }
 
 // All ranks of a collective in one launch on one GPU.  buckets[r], mailboxes[r] (uint8),
@@ -137,7 +145,7 @@ void fused_allreduce_local(std::vector<at::Tensor> buckets, at::Tensor steps, st
                            std::vector<at::Tensor> flags, at::Tensor status, at::Tensor tail_ws, int64_t nslots,
                            int64_t bits, int64_t ctas, int64_t threads, int64_t blocks_per_shard, int64_t slot_stride,
                            int64_t scales_off, int64_t flag_base, int64_t epoch, int64_t seed, int64_t step,
-                           int64_t bucket_id, double post_scale, int64_t timeout_ns, bool no_transmit) {
+                           int64_t bucket_id, double post_scale, int64_t timeout_ns, bool no_transmit, bool tensor_rotation) {
   const int64_t world = static_cast<int64_t>(buckets.size());
   TORCH_CHECK(world >= 1 && world <= kMaxWorld, "1..8 ranks");
   TORCH_CHECK(steps.dim() == 3 && steps.size(0) == world, "steps must be [world, nsteps, 8]");
@@ -170,9 +178,9 @@ void fused_allreduce_local(std::vector<at::Tensor> buckets, at::Tensor steps, st
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   if (world == 1) {
     if (buckets[0].scalar_type() == at::kFloat)
-      launch_bits<float>(static_cast<int>(bits), hp.data(), nullptr, 1, static_cast<int>(ctas), static_cast<int>(threads), stream);
+      launch_bits<float>(static_cast<int>(bits), hp.data(), nullptr, 1, static_cast<int>(ctas), static_cast<int>(threads), stream, tensor_rotation);
     else
-      launch_bits<__nv_bfloat16>(static_cast<int>(bits), hp.data(), nullptr, 1, static_cast<int>(ctas), static_cast<int>(threads), stream);
+      launch_bits<__nv_bfloat16>(static_cast<int>(bits), hp.data(), nullptr, 1, static_cast<int>(ctas), static_cast<int>(threads), stream, tensor_rotation);
     return;
   }
   at::Tensor dev = at::empty({static_cast<int64_t>(world * sizeof(ARParams))},
@@ -181,9 +189,9 @@ void fused_allreduce_local(std::vector<at::Tensor> buckets, at::Tensor steps, st
   C10_CUDA_CHECK(cudaStreamSynchronize(stream));  // hp is pageable host memory
   const ARParams* dp = reinterpret_cast<const ARParams*>(dev.data_ptr());
   if (buckets[0].scalar_type() == at::kFloat)
-    launch_bits<float>(static_cast<int>(bits), nullptr, dp, static_cast<int>(world), static_cast<int>(ctas), static_cast<int>(threads), stream);
+    launch_bits<float>(static_cast<int>(bits), nullptr, dp, static_cast<int>(world), static_cast<int>(ctas), static_cast<int>(threads), stream, tensor_rotation);
   else
-    launch_bits<__nv_bfloat16>(static_cast<int>(bits), nullptr, dp, static_cast<int>(world), static_cast<int>(ctas), static_cast<int>(threads), stream);
+    launch_bits<__nv_bfloat16>(static_cast<int>(bits), nullptr, dp, static_cast<int>(world), static_cast<int>(ctas), static_cast<int>(threads), stream, tensor_rotation);
   C10_CUDA_CHECK(cudaStreamSynchronize(stream));  // keep `dev` alive until the kernel has read it
 }
 

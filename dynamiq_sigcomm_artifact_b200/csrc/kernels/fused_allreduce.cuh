@@ -14,7 +14,7 @@ enum : int { kLocalRaw = 0, kLocalWs = 1 };
 enum : int { kOutSend = 0, kOutStore = 1, kOutFinal = 2, kOutDecode = 3 };
 
 // error codes left in status[0]; status[1] = (step << 16) | cta, status[2] = slot
-enum : uint32_t { kOk = 0, kErrWaitTimeout = 1, kErrBadProgram = 2, kErrCopyTimeout = 3 };
+enum : uint32_t { kOk = 0, kErrWaitTimeout = 1, kErrBadProgram = 2, kErrCopyTimeout = 3, kErrMmaTimeout = 4 };
 
 struct ARParams {
   void* bucket;        // this rank's gradient bucket: input, scratch for partial sums, and output
@@ -35,6 +35,7 @@ struct ARParams {
   unsigned long long timeout_ns;   // budget of each wait on a flag
   uint32_t* status;                // 4 words, local
   int no_transmit;                 // debug: run the maths, skip remote payload stores
+  int tensor_rotation;             // host-side selector: 1 = tcgen05 rotation, 0 = SIMT butterflies
   int steps[kMaxSteps][kStepInts];
 };
 

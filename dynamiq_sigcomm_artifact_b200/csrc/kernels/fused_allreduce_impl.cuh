@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include "../common/rht_codec.cuh"
+#include "../common/rht_tc.cuh"
 #include "fused_allreduce.cuh"
 
 namespace dq {
@@ -44,34 +45,10 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, 
 // block (4 KiB fp32 / 2 KiB bf16) from this GPU's own bucket into the warp's staging buffer; the
 // warp later waits on the barrier's phase (bounded) and reads the block from shared memory.
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
+using tc::mbar_init;
+using tc::mbar_wait;
 __device__ __forceinline__ void bulk_prefetch(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // earlier generic reads of dst precede the copy
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   smem_u32(dst_smem)),
-               "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
-// true when the phase with the given parity has completed; gives up after ~2^22 polls
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t it = 0; it < (1u << 22); ++it) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  return false;
+  tc::bulk_load(dst_smem, src_gmem, bytes, bar);
 }
 
 struct RawItem {
@@ -101,22 +78,82 @@ __device__ __forceinline__ RawItem next_raw_item(const ARParams& p, int s, int b
   return RawItem{-1, -1};
 }
 
-template <int BITS, typename T>
+// Shared-memory layout of a CTA (nwarps warps, nwg = nwarps / 4 warpgroups):
+//   SIMT rotation:   [tile: nwarps x 4 KiB][stage: nwarps x 4 KiB][sign words][prefetch barriers]
+//   tensor rotation: [operands: nwg x 18 KiB][stage: nwarps x 4 KiB][H_32][sign words][prefetch barriers]
+//                    [MMA barriers: nwg][TMEM slot][error flag]
+template <bool TC>
+__host__ __device__ constexpr size_t fused_smem_bytes(int threads) {
+  const size_t nwarps = threads / 32, nwg = threads / 128;
+  return (TC ? nwg * tc::kOperandBytes + tc::kHBytes + nwg * 8 + 16 : nwarps * kBlock * 4) + nwarps * kBlock * 4 +
+         32 * 4 + nwarps * 8 + 128;
+}
+
+template <int BITS, typename T, bool TC>
 __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
-  extern __shared__ __align__(128) float smem[];
+  extern __shared__ __align__(128) uint8_t smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
   const int cta = blockIdx.x, G = gridDim.x;
-  float* tile = smem + warp * kBlock;
-  float* stage = smem + (nwarps + warp) * kBlock;
-  uint32_t* sign_words = reinterpret_cast<uint32_t*>(smem + 2 * nwarps * kBlock);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sign_words + 32);
-  uint64_t* bar = bars + warp;
+  constexpr int GS = TC ? 4 : 1;  // warps that move through the block loop together
+  const int nwg = nwarps / 4, wg = warp >> 2, wi = warp & 3;
+
+  uint8_t* cursor = smem_raw;
+  float* tile = nullptr;
+  uint8_t* operands = nullptr;
+  if (TC) {
+    operands = cursor;
+    cursor += static_cast<size_t>(nwg) * tc::kOperandBytes;
+  } else {
+    tile = reinterpret_cast<float*>(cursor) + warp * kBlock;
+    cursor += static_cast<size_t>(nwarps) * kBlock * 4;
+  }
+  float* stage = reinterpret_cast<float*>(cursor) + warp * kBlock;
+  cursor += static_cast<size_t>(nwarps) * kBlock * 4;
+  uint8_t* hmat = cursor;
+  if (TC) cursor += tc::kHBytes;
+  uint32_t* sign_words = reinterpret_cast<uint32_t*>(cursor);
+  cursor += 32 * 4;
+  uint64_t* bar = reinterpret_cast<uint64_t*>(cursor) + warp;
+  cursor += static_cast<size_t>(nwarps) * 8;
+  uint64_t* mma_bars = reinterpret_cast<uint64_t*>(cursor);
+  if (TC) cursor += static_cast<size_t>(nwg) * 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cursor);
+  int* tc_error = reinterpret_cast<int*>(cursor + 8);
 
   if (tid < 32) sign_words[tid] = sign_word(tid, p.step, p.bucket_id, p.seed_lo, p.seed_hi);
   if (lane == 0) mbar_init(bar, 1);
+  if (TC) {
+    tc::fill_hadamard32(hmat, tid, blockDim.x);
+    if (tid < nwg) tc::mbar_init(&mma_bars[tid], 1);
+    if (tid == 0) *tc_error = 0;
+  }
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  const uint32_t tmem_cols = static_cast<uint32_t>(nwg) * 64u;  // D1 | D2 per warpgroup; 64 / 128 / 256
+  if (TC) {
+    if (warp == 0) tc::tmem_alloc(tmem_slot, tmem_cols);
+    tc::fence_async_smem();
+    tc::tc_fence_before();
+  }
   __syncthreads();
+  if (TC) tc::tc_fence_after();
   const uint32_t sign_mask = lane_sign_mask(sign_words, lane);
+  const uint32_t row_signs = sign_words[lane];  // tensor path, row layout: element 32 lane + n -> word lane, bit n
+
+  TcGroup tg{};
+  uint32_t tmem_base = 0;
+  if (TC) {
+    tmem_base = *tmem_slot;
+    tg.a = operands + static_cast<size_t>(wg) * tc::kOperandBytes;
+    tg.hmat = tc::smem_u32(hmat);
+    tg.bar = &mma_bars[wg];
+    tg.tmem_wg = tmem_base + static_cast<uint32_t>(wg) * 64u;
+    tg.tmem_d1 = tg.tmem_wg + (static_cast<uint32_t>(wi * 32) << 16);
+    tg.parity = 0;
+    tg.barrier_id = 1 + wg;
+    tg.wi = wi;
+    tg.leader = (wi == 0 && lane == 0);
+    tg.error = tc_error;
+  }
 
   T* bucket = static_cast<T*>(p.bucket);
   const bool vec_ok = (reinterpret_cast<uintptr_t>(bucket) & 15u) == 0;
@@ -145,7 +182,8 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
     }
   };
 
-  for (int s = 0; s < p.nsteps; ++s) {
+  bool aborted = false;
+  for (int s = 0; s < p.nsteps && !aborted; ++s) {
     const int local = p.steps[s][1], recv_slot = p.steps[s][2], nrecv = p.steps[s][3];
     const int out = p.steps[s][4], dst = p.steps[s][5], send_slot = p.steps[s][6];
     const uint32_t tag = stream_tag(p.bucket_id, static_cast<uint32_t>(p.steps[s][7]) & ~kTagStratified);
@@ -164,12 +202,16 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
       }
       if (__syncthreads_or(timed_out)) {
         if (timed_out) fail(kErrWaitTimeout, s, bad_slot);
-        if (pf.s >= 0) mbar_wait(bar, pf_parity);  // let this warp's copy in flight land before leaving
-        return;  // the whole CTA gives up; peers that depend on it time out the same way
+        aborted = true;  // the whole CTA gives up; peers that depend on it time out the same way
+        break;
       }
     }
+    const bool rotate_in = (out != kOutDecode) && (local == kLocalRaw);
+    const bool rotate_out = (out == kOutFinal) || (out == kOutDecode);
 
-    for (int blk = lo + warp; blk < hi; blk += nwarps) {
+    for (int base = lo + GS * (warp / GS); base < hi; base += nwarps) {
+      const int blk = base + (warp % GS);
+      const bool active = blk < hi;  // warps of a warpgroup past the end still join its barriers
       const int bs = blk - shard_lo;  // block index inside the shard = inside the message
       const long long e0 = static_cast<long long>(blk) * kBlock;
       const int valid = static_cast<int>(min(static_cast<long long>(kBlock), p.n - e0));
@@ -177,7 +219,7 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
       uint32_t w[BITS];
       float scale = 0.f;
 
-      if (nrecv > 0) {  // first incoming message: issue its loads before the local work
+      if (active && nrecv > 0) {  // first incoming message: issue its loads before the local work
         const uint8_t* slot = my_mail + static_cast<unsigned long long>(recv_slot) * p.slot_stride;
         const uint32_t* codes = reinterpret_cast<const uint32_t*>(slot) + static_cast<size_t>(bs) * (BITS * 32);
 #pragma unroll
@@ -185,7 +227,7 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
         scale = __ldcg(reinterpret_cast<const float*>(slot + p.scales_off) + bs);
       }
 
-      if (out != kOutDecode) {
+      if (active && out != kOutDecode) {
         if (local == kLocalRaw) {
           if (pf.s == s && pf.blk == blk && mbar_wait(bar, pf_parity)) {
             pf_parity ^= 1u;
@@ -199,12 +241,18 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
             load_block<T>(bucket + e0, valid, vec_ok, lane, v);
           }
           issue_prefetch(next_raw_item(p, s, blk, cta, per_cta, warp, nwarps));
-          rotate_forward(v, sign_mask, tile, lane);
         } else if (blk == tail_block) {
           load_block<float>(p.tail_ws, kBlock, true, lane, v);
         } else {
           load_block<T>(bucket + e0, kBlock, vec_ok, lane, v);
         }
+      }
+      if (rotate_in) {
+        if (TC) rotate_forward_tc(v, sign_mask, tg, lane);
+        else rotate_forward(v, sign_mask, tile, lane);
+      }
+
+      if (active && out != kOutDecode) {
         if (nrecv > 0) dequantize_add_block<BITS>(w, scale, v);
         for (int r = 1; r < nrecv; ++r) {
           const uint8_t* slot = my_mail + static_cast<unsigned long long>(recv_slot + r) * p.slot_stride;
@@ -217,36 +265,48 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
       }
 
       if (out == kOutStore) {
-        if (blk == tail_block) store_block<float>(p.tail_ws, kBlock, true, lane, v);
-        else store_block<T>(bucket + e0, kBlock, vec_ok, lane, v);
-      } else if (out == kOutSend) {
-        scale = quantize_block<BITS>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi, lane, p.rank,
-                                     strat_world);
-        if (!p.no_transmit) {
-          uint8_t* slot = p.mail[dst] + static_cast<unsigned long long>(send_slot) * p.slot_stride;
-          uint32_t* codes = reinterpret_cast<uint32_t*>(slot) + static_cast<size_t>(bs) * (BITS * 32);
-#pragma unroll
-          for (int j = 0; j < BITS; ++j) codes[j * 32 + lane] = w[j];
-          if (lane == 0) reinterpret_cast<float*>(slot + p.scales_off)[bs] = scale;
+        if (active) {
+          if (blk == tail_block) store_block<float>(p.tail_ws, kBlock, true, lane, v);
+          else store_block<T>(bucket + e0, kBlock, vec_ok, lane, v);
         }
-      } else {
-        if (out == kOutFinal) {
-          scale = quantize_block<BITS>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi, lane);
+      } else if (out == kOutSend) {
+        if (active) {
+          scale = quantize_block<BITS>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi, lane,
+                                       p.rank, strat_world);
           if (!p.no_transmit) {
-            for (int peer = 0; peer < p.world; ++peer) {
-              if (peer == p.rank) continue;
-              uint8_t* slot = p.mail[peer] + static_cast<unsigned long long>(send_slot) * p.slot_stride;
-              uint32_t* codes = reinterpret_cast<uint32_t*>(slot) + static_cast<size_t>(bs) * (BITS * 32);
+            uint8_t* slot = p.mail[dst] + static_cast<unsigned long long>(send_slot) * p.slot_stride;
+            uint32_t* codes = reinterpret_cast<uint32_t*>(slot) + static_cast<size_t>(bs) * (BITS * 32);
 #pragma unroll
-              for (int j = 0; j < BITS; ++j) codes[j * 32 + lane] = w[j];
-              if (lane == 0) reinterpret_cast<float*>(slot + p.scales_off)[bs] = scale;
-            }
+            for (int j = 0; j < BITS; ++j) codes[j * 32 + lane] = w[j];
+            if (lane == 0) reinterpret_cast<float*>(slot + p.scales_off)[bs] = scale;
           }
         }
-        // kOutDecode: w / scale were loaded from the all-gather slot above
-        dequantize_block<BITS>(w, scale, v);
-        rotate_inverse(v, sign_mask, p.finish_scale, tile, lane);
-        store_block<T>(bucket + e0, valid, vec_ok, lane, v);
+      } else {
+        if (active) {
+          if (out == kOutFinal) {
+            scale = quantize_block<BITS>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi, lane);
+            if (!p.no_transmit) {
+              for (int peer = 0; peer < p.world; ++peer) {
+                if (peer == p.rank) continue;
+                uint8_t* slot = p.mail[peer] + static_cast<unsigned long long>(send_slot) * p.slot_stride;
+                uint32_t* codes = reinterpret_cast<uint32_t*>(slot) + static_cast<size_t>(bs) * (BITS * 32);
+#pragma unroll
+                for (int j = 0; j < BITS; ++j) codes[j * 32 + lane] = w[j];
+                if (lane == 0) reinterpret_cast<float*>(slot + p.scales_off)[bs] = scale;
+              }
+            }
+          }
+          // kOutDecode: w / scale were loaded from the all-gather slot above
+          dequantize_block<BITS>(w, scale, v);
+        }
+        if (rotate_out) {
+          if (TC) rotate_inverse_tc(v, row_signs, p.finish_scale, tg, lane);
+          else rotate_inverse(v, sign_mask, p.finish_scale, tile, lane);
+        }
+        if (active) {
+          if (TC) store_block_rows<T>(bucket + e0, valid, vec_ok, lane, v);
+          else store_block<T>(bucket + e0, valid, vec_ok, lane, v);
+        }
       }
     }
 
@@ -263,27 +323,38 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
       }
     }
   }
+
+  if (aborted && pf.s >= 0) mbar_wait(bar, pf_parity);  // let this warp's copy in flight land before leaving
+  if (TC) {
+    if (tid == 0 && *tc_error) fail(kErrMmaTimeout, 0, -1);
+    tc::tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tc::tmem_dealloc(tmem_base, tmem_cols);
+  }
 }
 
-template <int BITS, typename T>
+template <int BITS, typename T, bool TC>
 __global__ void __launch_bounds__(512, 1) fused_allreduce_kernel(const __grid_constant__ ARParams p) {
-  fused_allreduce_body<BITS, T>(p);
+  fused_allreduce_body<BITS, T, TC>(p);
 }
 
 // Several ranks in one launch on one GPU (blockIdx.y = rank): the single-GPU form of the
 // collective used by the standalone codec ops and by tests.  Cooperative, so that CTAs that
 // wait on one another are co-resident.
-template <int BITS, typename T>
+template <int BITS, typename T, bool TC>
 __global__ void __launch_bounds__(512, 1) fused_allreduce_multi_kernel(const ARParams* __restrict__ plist) {
-  fused_allreduce_body<BITS, T>(plist[blockIdx.y]);
+  fused_allreduce_body<BITS, T, TC>(plist[blockIdx.y]);
 }
 
-template <int BITS, typename T>
+template <int BITS, typename T, bool TC>
 void launch_one(const ARParams* host_params, const ARParams* dev_params, int nranks, int ctas, int threads,
-                       cudaStream_t stream) {
-  const size_t smem = static_cast<size_t>(threads / 32) * (2 * kBlock * sizeof(float) + sizeof(uint64_t)) + 32 * sizeof(uint32_t);
-  const void* fn = nranks == 1 ? reinterpret_cast<const void*>(&fused_allreduce_kernel<BITS, T>)
-                               : reinterpret_cast<const void*>(&fused_allreduce_multi_kernel<BITS, T>);
+                cudaStream_t stream) {
+  TORCH_CHECK(!TC || threads == 128 || threads == 256 || threads == 512,
+              "the tensor-core rotation needs 1, 2 or 4 whole warpgroups (128, 256 or 512 threads): TMEM columns are "
+              "allocated in powers of two");
+  const size_t smem = fused_smem_bytes<TC>(threads);
+  const void* fn = nranks == 1 ? reinterpret_cast<const void*>(&fused_allreduce_kernel<BITS, T, TC>)
+                               : reinterpret_cast<const void*>(&fused_allreduce_multi_kernel<BITS, T, TC>);
   // attribute and occupancy are queried once per (kernel, device, block size) and cached
   struct Cache {
     int dev = -1, threads = -1, capacity = 0;
@@ -313,7 +384,9 @@ void launch_one(const ARParams* host_params, const ARParams* dev_params, int nra
 
 
 #define DQ_INSTANTIATE_FUSED_ALLREDUCE(BITS)                                                                   \
-  template void launch_one<BITS, float>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);         \
-  template void launch_one<BITS, __nv_bfloat16>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);
+  template void launch_one<BITS, float, false>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);         \
+  template void launch_one<BITS, __nv_bfloat16, false>(const ARParams*, const ARParams*, int, int, int, cudaStream_t); \
+  template void launch_one<BITS, float, true>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);          \
+  template void launch_one<BITS, __nv_bfloat16, true>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);
 
 }  // namespace dq

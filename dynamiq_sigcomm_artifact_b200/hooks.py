@@ -126,7 +126,8 @@ def _engine(state: HookState):
         cfg: DynamiqConfig = state["config"]
         state["engine"] = FusedAllreduce(group=state["group"], max_numel=cfg.max_bucket_mb * (1 << 20) // 4,
                                          ctas=cfg.comm_ctas, threads=cfg.comm_threads,
-                                         timeout_ms=cfg.wait_timeout_ms, validate=cfg.validate_topology)
+                                         timeout_ms=cfg.wait_timeout_ms, validate=cfg.validate_topology,
+                                         rotation=cfg.rotation)
         state["comm_stream"] = torch.cuda.Stream(priority=-1)
     return state["engine"]
 

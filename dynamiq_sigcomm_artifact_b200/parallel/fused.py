@@ -66,8 +66,16 @@ def program_tensor(rank: int, world: int, topology: str, correlated: bool = Fals
     return torch.tensor([s.as_ints() for s in prog], dtype=torch.int32)
 
 
+def _rotation_flag(rotation: str) -> bool:
+    """"simt": fp32 butterflies, bit-exact against the CPU oracle; "tc": tcgen05 / TMEM rotation."""
+    if rotation not in ("simt", "tc"):
+        raise ValueError("rotation must be 'simt' or 'tc'")
+    return rotation == "tc"
+
+
 STATUS_MESSAGES = {1: "timed out waiting for a peer's flag", 2: "malformed step program",
-                   3: "a bulk copy into shared memory did not complete"}
+                   3: "a bulk copy into shared memory did not complete",
+                   4: "a tensor-core pass did not signal completion"}
 
 
 def decode_status(words: Sequence[int]) -> Optional[str]:
@@ -82,7 +90,7 @@ class FusedAllreduce:
     """Compressed all-reduce (mean) over NVLink for the ranks of a process group."""
 
     def __init__(self, group=None, max_numel: int = 32 << 20, ctas: int = 64, threads: int = 256,
-                 timeout_ms: int = 2000, validate: bool = True):
+                 timeout_ms: int = 2000, validate: bool = True, rotation: str = "simt"):
         self.ops = _ops.require()
         self.group = group
         self.world = dist.get_world_size(group)
@@ -90,6 +98,7 @@ class FusedAllreduce:
         self.ctas, self.threads = int(ctas), int(threads)
         self.timeout_ns = int(timeout_ms) * 1_000_000
         self.validate = validate
+        self.tensor_rotation = _rotation_flag(rotation)
         self.device = torch.cuda.current_device()
         self.epoch = 0
         self._programs: Dict[tuple, torch.Tensor] = {}
@@ -141,7 +150,7 @@ class FusedAllreduce:
             self.buf.local_ptr + self.off_status, self.buf.local_ptr + self.off_tail, self.rank, self.world, bits,
             self.ctas, self.threads, lay.blocks_per_shard, lay.slot_stride, lay.scales_off,
             parity * self.flag_words_per_set, self.epoch, seed, step, bucket_id, 1.0 / self.world, self.timeout_ns,
-            no_transmit)
+            no_transmit, self.tensor_rotation)
         counters.add("fused_allreduce")
         return bucket
 
@@ -166,8 +175,9 @@ class LocalCluster:
     """All ranks of a collective on one GPU, one cooperative launch (blockIdx.y = rank)."""
 
     def __init__(self, world: int, max_numel: int, ctas: int = 8, threads: int = 256, device="cuda",
-                 timeout_ms: int = 1000):
+                 timeout_ms: int = 1000, rotation: str = "simt"):
         self.ops = _ops.require()
+        self.tensor_rotation = _rotation_flag(rotation)
         self.world, self.ctas, self.threads = world, ctas, threads
         self.device = torch.device(device)
         self.timeout_ns = timeout_ms * 1_000_000
@@ -193,7 +203,8 @@ class LocalCluster:
         self.ops.fused_allreduce_local(
             buckets, programs, self.mail, self.flags, self.status, self.tail_ws, self.nslots, bits, self.ctas,
             self.threads, lay.blocks_per_shard, lay.slot_stride, lay.scales_off, 0, self.epoch, seed, step, bucket_id,
-            (1.0 / self.world) if post_scale is None else post_scale, self.timeout_ns, no_transmit)
+            (1.0 / self.world) if post_scale is None else post_scale, self.timeout_ns, no_transmit,
+            self.tensor_rotation)
 
     def allreduce_(self, buckets: List[torch.Tensor], bits: int, topology: str = "ring", correlated: bool = False,
                    **kw) -> List[torch.Tensor]:
@@ -224,9 +235,10 @@ class RhtCodec:
     scales fp32 [nb]).
     """
 
-    def __init__(self, bits: int, max_numel: int, seed: int = 0, ctas: int = 32, threads: int = 256, device="cuda"):
+    def __init__(self, bits: int, max_numel: int, seed: int = 0, ctas: int = 32, threads: int = 256, device="cuda",
+                 rotation: str = "simt"):
         self.bits, self.seed = bits, seed
-        self.cluster = LocalCluster(1, max_numel, ctas=ctas, threads=threads, device=device)
+        self.cluster = LocalCluster(1, max_numel, ctas=ctas, threads=threads, device=device, rotation=rotation)
 
     def _prog(self, step: sch.Step) -> torch.Tensor:
         return torch.tensor([[step.as_ints()]], dtype=torch.int32)

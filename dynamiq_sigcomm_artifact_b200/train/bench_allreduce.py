@@ -88,7 +88,8 @@ def run_collectives(args) -> None:
     sizes = [int(float(s) * (1 << 20)) // 4 for s in args.sizes_mb.split(",")]
     bits_list = [int(b) for b in args.bits.split(",")]
     topologies = args.topologies.split(",")
-    eng = FusedAllreduce(max_numel=max(sizes), ctas=args.ctas, threads=args.threads, timeout_ms=5000)
+    eng = FusedAllreduce(max_numel=max(sizes), ctas=args.ctas, threads=args.threads, timeout_ms=5000,
+                         rotation=args.rotation)
     rows = []
     for numel in sizes:
         base = make_input(numel, rank, args.seed, dev)
@@ -143,7 +144,7 @@ def run_collectives(args) -> None:
                 hbm = measured_peaks().get("hbm_gbs", HBM_GBS_FALLBACK)
                 t_link = wire / (NVLINK_GBS * 1e6)
                 t_hbm = (2 * in_bytes + 3 * wire) / (hbm * 1e6)
-                record(f"fused_{topo}_{bits}bit", ms, wire, nmse_vs(exact, work),
+                record(f"fused_{topo}_{bits}bit" + ("_tc" if args.rotation == "tc" else ""), ms, wire, nmse_vs(exact, work),
                        {"roofline_ms": max(t_link, t_hbm), "roofline_fraction": max(t_link, t_hbm) / ms,
                         "bound": "nvlink" if t_link > t_hbm else "hbm"})
     if rank == 0 and args.out:
@@ -161,7 +162,7 @@ def run_kernels(args) -> None:
     x = make_input(numel, 0, args.seed, dev)
     rows = []
     for bits in [int(b) for b in args.bits.split(",")]:
-        cl = LocalCluster(1, numel, ctas=args.ctas, threads=args.threads, device=dev)
+        cl = LocalCluster(1, numel, ctas=args.ctas, threads=args.threads, device=dev, rotation=args.rotation)
         lay = Layout(numel, 1, bits)
         work = torch.empty_like(x)
         msg = lay.nblocks * (128 * bits + 4)
@@ -179,7 +180,7 @@ def run_kernels(args) -> None:
             cl.check()
             row = {"kernel": f"rht_{name}", "bits": bits, "numel": numel, "ms": ms, "gbs": nbytes / ms / 1e6,
                    "gelem_s": numel / ms / 1e6, "hbm_fraction_of_measured": nbytes / ms / 1e6 / hbm,
-                   "ctas": args.ctas, "threads": args.threads}
+                   "ctas": args.ctas, "threads": args.threads, "rotation": args.rotation}
             rows.append(row)
             print(json.dumps(row), flush=True)
     # the tensor-core Hadamard kernel on its own: reads and writes every element once
@@ -209,6 +210,7 @@ def main(argv=None) -> None:
     ap.add_argument("--topologies", default="ring,butterfly,direct")
     ap.add_argument("--ctas", type=int, default=148)
     ap.add_argument("--threads", type=int, default=512)
+    ap.add_argument("--rotation", default="simt", choices=["simt", "tc"])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--seed", type=int, default=1)

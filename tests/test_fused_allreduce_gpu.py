@@ -123,3 +123,50 @@ def test_correlated_rounding_matches_simulator_and_lowers_error(topology, world)
     exact = np.mean(np.stack(xs).astype(np.float64), 0)
     plain = cb.simulate_allreduce(xs, bits, topology, seed=seed, step=2, bucket=1)
     assert cr.nmse(want[0], exact) < cr.nmse(plain[0], exact)
+
+
+def test_tensor_core_rotation_inside_the_fused_kernel():
+    """STORE program = rotate and keep: compare the tcgen05 rotation with a float64 Hadamard product."""
+    n, seed, step, bucket = 8 * 1024, 11, 2, 5
+    x = heavy_tail_grad(n, 3)
+    cl = _cluster(1, n, ctas=2, threads=128, rotation="tc")
+    buf = torch.from_numpy(x).cuda()
+    prog = torch.tensor([[sch.Step(shard=0, out=sch.OUT_STORE).as_ints()]], dtype=torch.int32)
+    cl.run([buf], prog, 8, seed=seed, step=step, bucket_id=bucket)
+    cl.check()
+    got = buf.cpu().numpy().reshape(-1, 8, 32, 4)  # [block, j, lane, k] = register 4 j + k of a lane
+    h = np.array([[1.0]])
+    for _ in range(10):
+        h = np.block([[h, h], [h, -h]])
+    want = (cr.to_blocks(x).astype(np.float64) * philox.sign_vector(step, bucket, seed)) @ h.T  # unnormalised
+    nidx = (4 * np.arange(8)[:, None, None] + np.arange(4)[None, None, :])  # register n
+    coeff = 32 * nidx + np.arange(32)[None, :, None]  # coefficient 32 n + lane
+    ref = want[:, coeff.reshape(-1)].reshape(got.shape)
+    err = np.abs(got - ref).max() / np.abs(ref).max()
+    assert err < 2e-3, err
+
+
+@pytest.mark.parametrize("topology", sch.TOPOLOGIES)
+def test_collective_with_tensor_core_rotation(topology):
+    world, n, bits = 4, 45 * 1024 + 77, 5
+    xs = [heavy_tail_grad(n, 20 + r) for r in range(world)]
+    exact = np.mean(np.stack(xs).astype(np.float64), 0)
+    ref_nmse = cr.nmse(cb.simulate_allreduce(xs, bits, topology, seed=4)[0], exact)
+    cl = _cluster(world, n, ctas=3, threads=256, rotation="tc")
+    for rep in range(2):  # twice: TMEM columns and barriers are reused across launches
+        bufs = [torch.from_numpy(x).cuda() for x in xs]
+        cl.allreduce_(bufs, bits, topology, seed=4)
+        cl.check()
+        assert all(torch.equal(bufs[0], b) for b in bufs), "ranks disagree"
+        got = cr.nmse(bufs[0].cpu().numpy(), exact)
+        assert abs(got - ref_nmse) < 0.15 * ref_nmse, (got, ref_nmse)
+    # 8-bit round trip through the standalone operators
+    from dynamiq_sigcomm_artifact_b200.parallel.fused import RhtCodec
+
+    codec = RhtCodec(8, n, seed=1, ctas=4, threads=128, rotation="tc")
+    x = torch.from_numpy(xs[0]).cuda()
+    back = codec.decompress(codec.compress(x), n)
+    assert float((back - x).pow(2).sum() / x.pow(2).sum()) < 3e-4
+    xb = x.bfloat16()
+    back16 = codec.decompress(codec.compress(xb), n, dtype=torch.bfloat16)
+    assert float((back16.float() - xb.float()).pow(2).sum() / xb.float().pow(2).sum()) < 1e-3
