@@ -230,10 +230,20 @@ __device__ __forceinline__ float warp_absmax(const float (&y)[32]) {
 // Stratified ("correlated") rounding, strat_world > 1: all ranks draw the same byte per value and
 // rank r uses u = (((r + shift) mod W) * 256 + byte + 0.5) / (256 W), shift = the byte of the
 // lane's next value, so the W rounding errors that meet in a sum are negatively correlated.
+// The 32 random bytes of a lane for one block (two Philox-4x32-7 calls); independent of the data, so a
+// caller may draw them while something else (a tensor-core pass) is in flight.
+__device__ __forceinline__ void draw_block_randoms(uint32_t (&rw)[8], uint32_t block_idx, uint32_t tag, uint32_t step,
+                                                   uint32_t k0, uint32_t k1, int lane) {
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    U4 r = philox4x32<kUniformRounds>(block_idx, static_cast<uint32_t>(lane * 2 + q), tag, step, k0, k1);
+    rw[4 * q] = r.x, rw[4 * q + 1] = r.y, rw[4 * q + 2] = r.z, rw[4 * q + 3] = r.w;
+  }
+}
+
 template <int B>
-__device__ __forceinline__ float quantize_block(const float (&y)[32], uint32_t (&w)[B], uint32_t block_idx,
-                                                uint32_t tag, uint32_t step, uint32_t k0, uint32_t k1, int lane,
-                                                int strat_rank = 0, int strat_world = 1) {
+__device__ __forceinline__ float quantize_block_rw(const float (&y)[32], uint32_t (&w)[B], const uint32_t (&rw)[8],
+                                                   int lane, int strat_rank = 0, int strat_world = 1) {
   constexpr int R = (1 << (B - 1)) - 1;
   const float m = warp_absmax(y);
   const bool ok = (m >= 1e-30f) && (m <= 3.402823466e38f);
@@ -243,12 +253,6 @@ __device__ __forceinline__ float quantize_block(const float (&y)[32], uint32_t (
   const float2 half_off = make_float2(-8388607.5f, -8388607.5f);
   const float2 magic = make_float2(3221225472.0f, 3221225472.0f);  // 1.5 * 2^31 = 0x4F400000
   uint32_t c[32];
-  uint32_t rw[8];
-#pragma unroll
-  for (int q = 0; q < 2; ++q) {
-    U4 r = philox4x32<kUniformRounds>(block_idx, static_cast<uint32_t>(lane * 2 + q), tag, step, k0, k1);
-    rw[4 * q] = r.x, rw[4 * q + 1] = r.y, rw[4 * q + 2] = r.z, rw[4 * q + 3] = r.w;
-  }
   if (strat_world > 1) {
     const float cw = 1.0f / (256.0f * static_cast<float>(strat_world));
     const uint32_t recip = 65536u / static_cast<uint32_t>(strat_world) + 1u;  // x / W for x < 512
@@ -290,6 +294,15 @@ __device__ __forceinline__ float quantize_block(const float (&y)[32], uint32_t (
   }
   pack_codes<B>(c, w);
   return scale;
+}
+
+template <int B>
+__device__ __forceinline__ float quantize_block(const float (&y)[32], uint32_t (&w)[B], uint32_t block_idx,
+                                                uint32_t tag, uint32_t step, uint32_t k0, uint32_t k1, int lane,
+                                                int strat_rank = 0, int strat_world = 1) {
+  uint32_t rw[8];
+  draw_block_randoms(rw, block_idx, tag, step, k0, k1, lane);
+  return quantize_block_rw<B>(y, w, rw, lane, strat_rank, strat_world);
 }
 
 // float(code - R) without a conversion: 0x4B400000 | code is 1.5 * 2^23 + code

@@ -8,7 +8,7 @@
 // Register layouts of a lane
 //   load layout (as in rht_codec.cuh)  reg t = 4 j + k holds element e = 128 j + 4 lane + k
 //   coefficient layout (tensor path)   reg n holds coefficient        e = 32 n + lane
-//   row layout (after the inverse)     reg n holds element            e = 32 lane + n
+//   column layout (after the inverse)  reg m holds element            e = 32 m + lane
 //
 // Operands are single TF32 (10 explicit mantissa bits): the rotation then carries a relative
 // error of ~2^-11 per value, three orders of magnitude below the rounding noise of an 8-bit code.
@@ -35,8 +35,14 @@ struct TcGroup {
 
 __device__ __forceinline__ void wg_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
 
-// operand in shared memory -> one pass D = A . H_32 -> 32 accumulator columns into registers
-__device__ __forceinline__ void tc_pass(TcGroup& g, uint32_t col_off, float (&out)[32]) {
+struct NoWork {
+  __device__ __forceinline__ void operator()() const {}
+};
+
+// operand in shared memory -> one pass D = A . H_32 -> 32 accumulator columns into registers.
+// `while_in_flight` runs between the issue of the MMAs and the wait for their completion.
+template <class F = NoWork>
+__device__ __forceinline__ void tc_pass(TcGroup& g, uint32_t col_off, float (&out)[32], F&& while_in_flight = F()) {
   tc::fence_async_smem();
   tc::tc_fence_before();
   wg_sync(g.barrier_id);
@@ -45,6 +51,7 @@ __device__ __forceinline__ void tc_pass(TcGroup& g, uint32_t col_off, float (&ou
     tc::mma_tile_k32(g.tmem_wg + col_off, tc::smem_u32(g.a), g.hmat, false);
     tc::mma_commit(g.bar);
   }
+  while_in_flight();
   if (!tc::mbar_wait(g.bar, g.parity)) atomicExch(g.error, 1);
   g.parity ^= 1u;
   tc::tc_fence_after();
@@ -58,7 +65,9 @@ __device__ __forceinline__ void tc_scatter_transposed(TcGroup& g, const float (&
 }
 
 // raw gradients in the load layout -> rotated coefficients in the tensor-path coefficient layout
-__device__ __forceinline__ void rotate_forward_tc(float (&v)[32], uint32_t sign_mask, TcGroup& g, int lane) {
+template <class F = NoWork>
+__device__ __forceinline__ void rotate_forward_tc(float (&v)[32], uint32_t sign_mask, TcGroup& g, int lane,
+                                                  F&& while_in_flight = F()) {
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     float o[4];
@@ -68,41 +77,41 @@ __device__ __forceinline__ void rotate_forward_tc(float (&v)[32], uint32_t sign_
     *reinterpret_cast<float4*>(g.a + off) = make_float4(o[0], o[1], o[2], o[3]);
   }
   float d[32];
-  tc_pass(g, 0, d);
+  tc_pass(g, 0, d, while_in_flight);
   tc_scatter_transposed(g, d, lane);
   tc_pass(g, 32, v);
 }
 
-// coefficients (tensor-path layout) -> gradients in the row layout: x = s * (H y) * c
-__device__ __forceinline__ void rotate_inverse_tc(float (&v)[32], uint32_t row_signs, float c, TcGroup& g, int lane) {
-#pragma unroll
-  for (int q = 0; q < 8; ++q) {
-    const uint32_t off = tc::operand_offset(32 * g.wi + lane, 4 * q);
-    *reinterpret_cast<float4*>(g.a + off) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-  }
+// coefficients (tensor-path layout: reg n = W[n][lane]) -> gradients in the column layout:
+// x = s * (H W H) * c.  Both operands are transposed scatters, so that the thread ends with a
+// column of the result and the global stores of a warp are contiguous 128-byte lines.
+//   pass 1: A1[(b, n), k = lane] = W[n][lane]      -> D1 = W H, thread (b, n) holds row n
+//   pass 2: A2[(b, c), k = n]    = D1[n][c]        -> D2[(b, c)][m] = (H W H)[m][c]
+__device__ __forceinline__ void rotate_inverse_tc(float (&v)[32], uint32_t col_signs, float c, TcGroup& g, int lane) {
+  tc_scatter_transposed(g, v, lane);
   float d[32];
   tc_pass(g, 0, d);
   tc_scatter_transposed(g, d, lane);
   tc_pass(g, 32, v);
 #pragma unroll
-  for (int n = 0; n < 32; ++n) v[n] = flip(__fmul_rn(v[n], c), (row_signs >> n) & 1u);
+  for (int m = 0; m < 32; ++m) v[m] = flip(__fmul_rn(v[m], c), (col_signs >> m) & 1u);
 }
 
-// 1024 elements in the row layout: lane writes elements [32 lane, 32 lane + 32)
+// bit m of the result = sign bit of element 32 m + lane (the column layout's register m)
+__device__ __forceinline__ uint32_t lane_col_signs(const uint32_t* sign_words, int lane) {
+  uint32_t mask = 0;
+#pragma unroll
+  for (int m = 0; m < 32; ++m) mask |= ((sign_words[m] >> lane) & 1u) << m;
+  return mask;
+}
+
+// 1024 elements in the column layout: register m of a lane is element 32 m + lane
 template <typename T>
-__device__ __forceinline__ void store_block_rows(T* base, int valid, bool vec_ok, int lane, const float (&v)[32]) {
-  if (valid == kBlock && vec_ok) {
+__device__ __forceinline__ void store_block_cols(T* base, int valid, int lane, const float (&v)[32]) {
 #pragma unroll
-    for (int q = 0; q < 8; ++q) {
-      float o[4] = {v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]};
-      Elem<T>::store4(base + 32 * lane + 4 * q, o);
-    }
-  } else {
-#pragma unroll
-    for (int n = 0; n < 32; ++n) {
-      const int e = 32 * lane + n;
-      if (e < valid) base[e] = Elem<T>::from_float(v[n]);
-    }
+  for (int m = 0; m < 32; ++m) {
+    const int e = 32 * m + lane;
+    if (e < valid) base[e] = Elem<T>::from_float(v[m]);
   }
 }
 

@@ -137,7 +137,7 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
   __syncthreads();
   if (TC) tc::tc_fence_after();
   const uint32_t sign_mask = lane_sign_mask(sign_words, lane);
-  const uint32_t row_signs = sign_words[lane];  // tensor path, row layout: element 32 lane + n -> word lane, bit n
+  const uint32_t col_signs = lane_col_signs(sign_words, lane);  // tensor path: element 32 m + lane
 
   TcGroup tg{};
   uint32_t tmem_base = 0;
@@ -247,9 +247,16 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
           load_block<T>(bucket + e0, kBlock, vec_ok, lane, v);
         }
       }
+      uint32_t rw[8];  // rounding bytes, drawn under the first tensor-core pass when there is one
+      const bool have_rw = TC && rotate_in && active && (out == kOutSend || out == kOutFinal);
       if (rotate_in) {
-        if (TC) rotate_forward_tc(v, sign_mask, tg, lane);
-        else rotate_forward(v, sign_mask, tile, lane);
+        if (TC) {
+          rotate_forward_tc(v, sign_mask, tg, lane, [&]() {
+            if (have_rw) draw_block_randoms(rw, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi, lane);
+          });
+        } else {
+          rotate_forward(v, sign_mask, tile, lane);
+        }
       }
 
       if (active && out != kOutDecode) {
@@ -271,8 +278,9 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
         }
       } else if (out == kOutSend) {
         if (active) {
-          scale = quantize_block<BITS>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi, lane,
-                                       p.rank, strat_world);
+          scale = have_rw ? quantize_block_rw<BITS>(v, w, rw, lane, p.rank, strat_world)
+                          : quantize_block<BITS>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi,
+                                                 lane, p.rank, strat_world);
           if (!p.no_transmit) {
             uint8_t* slot = p.mail[dst] + static_cast<unsigned long long>(send_slot) * p.slot_stride;
             uint32_t* codes = reinterpret_cast<uint32_t*>(slot) + static_cast<size_t>(bs) * (BITS * 32);
@@ -284,7 +292,9 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
       } else {
         if (active) {
           if (out == kOutFinal) {
-            scale = quantize_block<BITS>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi, lane);
+            scale = have_rw ? quantize_block_rw<BITS>(v, w, rw, lane)
+                            : quantize_block<BITS>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi,
+                                                   lane);
             if (!p.no_transmit) {
               for (int peer = 0; peer < p.world; ++peer) {
                 if (peer == p.rank) continue;
@@ -300,11 +310,11 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
           dequantize_block<BITS>(w, scale, v);
         }
         if (rotate_out) {
-          if (TC) rotate_inverse_tc(v, row_signs, p.finish_scale, tg, lane);
+          if (TC) rotate_inverse_tc(v, col_signs, p.finish_scale, tg, lane);
           else rotate_inverse(v, sign_mask, p.finish_scale, tile, lane);
         }
         if (active) {
-          if (TC) store_block_rows<T>(bucket + e0, valid, vec_ok, lane, v);
+          if (TC) store_block_cols<T>(bucket + e0, valid, lane, v);
           else store_block<T>(bucket + e0, valid, vec_ok, lane, v);
         }
       }
