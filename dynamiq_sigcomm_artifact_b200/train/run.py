@@ -36,6 +36,36 @@ def default_lr(task: str, world: int, model: str = "") -> float:
     return base * (w / 2) ** 0.5 * (8 / w) ** 0.4
 
 
+def evaluate(tr: Trainer, batches: int):
+    """Mean loss and perplexity over held-out synthetic batches, averaged over ranks
+    (simulations_llm/distributed_llm_clm.py:350-374)."""
+    import math
+
+    tr.model.eval()
+    total = 0.0
+    saved = tr.step_idx
+    with torch.no_grad():
+        for i in range(batches):
+            tr.step_idx = 10_000_000 + i  # batches the training loop never sees
+            ids = tr.synthetic_batch(pinned=False).to(tr.device)
+            if tr.cfg.task == "mlm":
+                from ..models import mask_tokens
+
+                c = tr.model.config
+                x, y = mask_tokens(ids, c.vocab, c.mask_token_id, tr._gen)
+                total += float(tr.model(x, y))
+            else:
+                total += float(tr.model(ids, ids))
+    tr.step_idx = saved
+    tr.model.train()
+    mean = torch.tensor([total / max(batches, 1)], dtype=torch.float64, device=tr.device)
+    if dist.is_initialized():
+        dist.all_reduce(mean)
+        mean /= dist.get_world_size()
+    m = float(mean)
+    return m, math.exp(min(m, 50.0))
+
+
 def build_parser(task: str, default_model: str, default_seq: int, default_batch: int) -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(description=f"{task} training throughput / accuracy run on synthetic tokens")
     ap.add_argument("--model_name", "--model", default=default_model)
@@ -57,6 +87,7 @@ def build_parser(task: str, default_model: str, default_seq: int, default_batch:
     ap.add_argument("--measure_comm_error", action="store_true")
     ap.add_argument("--enable_nvtx", action="store_true")
     ap.add_argument("--nsys_profile_step", type=int, default=-1)
+    ap.add_argument("--eval_batches", type=int, default=0, help="held-out batches for a final loss / perplexity")
     ap.add_argument("--gradient_accumulation_steps", type=int, default=1,
                     help="accepted for command-line compatibility; the reference parses it and never uses it")
     return ap
@@ -113,6 +144,9 @@ def main(task: str, argv=None, default_model: str = "gpt2-small", default_seq: i
             line = log.results(measured, time.perf_counter() - t_start)
             if rank == 0:
                 print(line, flush=True)
+    if args.eval_batches > 0:
+        ppl = evaluate(tr, args.eval_batches)
+        log.log(f"eval_loss={ppl[0]:.4f} perplexity={ppl[1]:.2f}")
     tr.check()
     tr.close()
     if dist.is_initialized():

@@ -79,3 +79,25 @@ def test_masked_lm_masking_statistics():
     masked = float((x[sel] == 3).float().mean())
     assert abs(masked - 0.8) < 0.03
     assert bool((x[~sel] == ids[~sel]).all()) and bool((y[sel] == ids[sel]).all())
+
+
+def test_mmlu_entry_point_learns_the_synthetic_task(tmp_path):
+    from dynamiq_sigcomm_artifact_b200.train import mmlu
+    from dynamiq_sigcomm_artifact_b200.utils import data
+
+    acc = mmlu.main(["--model_name", "llama-tiny", "--per_device_train_batch_size", "16", "--block_size", "8",
+                     "--max_train_steps", "150", "--learning_rate", "3e-3", "--eval_items", "128",
+                     "--output_dir", str(tmp_path / "m")])
+    assert acc > 0.5  # chance is 0.25
+    assert data.format_mmlu_prompt("Q?", ["w", "x", "y", "z"], 2).endswith("Answer: C")
+    orders = data.gen_orders(10, 2, 1)
+    assert sorted(orders[0]) == list(range(10)) and orders[0] != orders[1]
+    assert list(data.PrecomputedSampler(orders[0], 1, 2)) == orders[0][1::2]
+
+
+def test_eval_reports_perplexity(tmp_path, capsys):
+    from dynamiq_sigcomm_artifact_b200.train import masked_lm
+
+    masked_lm.main(["--model_name", "bert-tiny", "--per_device_train_batch_size", "2", "--block_size", "32",
+                    "--max_train_steps", "3", "--eval_batches", "2", "--output_dir", str(tmp_path / "b")])
+    assert "perplexity=" in capsys.readouterr().out
