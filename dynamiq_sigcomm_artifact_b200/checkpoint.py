@@ -47,6 +47,10 @@ def load(path: str, trainer) -> dict:
     if state.get("version") != FORMAT_VERSION:
         raise ValueError(f"unsupported checkpoint version {state.get('version')}")
     trainer.model.load_state_dict(state["model"])
+    if getattr(trainer, "shadows", None):
+        from .ops.linear import enable_shadows
+
+        enable_shadows(trainer.model)  # refresh the bf16 working copies from the restored weights
     trainer.opt.load_state_dict(state["optimizer"])
     trainer.sched.load_state_dict(state["scheduler"])
     trainer.step_idx = int(state["step"])

@@ -36,6 +36,8 @@ std::tuple<at::Tensor, at::Tensor> fwht1024_tcgen05(at::Tensor x, int64_t seed, 
                                                     bool apply_signs, double scale, int64_t ctas);
 at::Tensor bins_to_bits(at::Tensor bins, int64_t nbits);
 at::Tensor bits_to_bins(at::Tensor words, int64_t nbits, int64_t n);
+at::Tensor swiglu_fwd(at::Tensor in);
+at::Tensor swiglu_bwd(at::Tensor dy, at::Tensor in);
 at::Tensor rope(at::Tensor x, at::Tensor cos, at::Tensor sin, bool backward);
 void adamw_step(at::Tensor table, at::Tensor numel, at::Tensor chunk_start, int64_t total_chunks, bool param_bf16,
                 bool grad_bf16, double lr, double beta1, double beta2, double eps, double weight_decay, int64_t step,
@@ -50,6 +52,8 @@ TORCH_LIBRARY(dq, m) {
   m.def("fwht1024_tcgen05(Tensor x, int seed, int step, int bucket, bool apply_signs, float scale, int ctas) -> (Tensor, Tensor)", &dq::fwht1024_tcgen05);
   m.def("bins_to_bits(Tensor bins, int nbits) -> Tensor", &dq::bins_to_bits);
   m.def("bits_to_bins(Tensor words, int nbits, int n) -> Tensor", &dq::bits_to_bins);
+  m.def("swiglu_fwd(Tensor x) -> Tensor", &dq::swiglu_fwd);
+  m.def("swiglu_bwd(Tensor dy, Tensor x) -> Tensor", &dq::swiglu_bwd);
   m.def("rope(Tensor x, Tensor cos, Tensor sin, bool backward) -> Tensor", &dq::rope);
   m.def("adamw_step(Tensor table, Tensor numel, Tensor chunk_start, int total_chunks, bool param_bf16, bool grad_bf16, "
         "float lr, float beta1, float beta2, float eps, float weight_decay, int step, float grad_scale) -> ()", &dq::adamw_step);

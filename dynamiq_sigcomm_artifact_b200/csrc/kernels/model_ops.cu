@@ -165,9 +165,12 @@ __global__ void rope_kernel(const T* __restrict__ x, const float* __restrict__ c
   }
 }
 
-// Multi-tensor AdamW (decoupled weight decay), fp32 state.  table[t] = {param, grad, m, v} device
-// addresses, numel[t], and chunk_start[t] = first chunk of tensor t (chunk = 4096 elements).
+// Multi-tensor AdamW (decoupled weight decay), fp32 state.  table[t] = {param, grad, m, v, shadow}
+// device addresses (shadow = 0 or a bf16 copy of the parameter that the kernel keeps in step, so that
+// no separate cast pass runs before the next forward), numel[t], and chunk_start[t] = first chunk of
+// tensor t (chunk = 4096 elements).
 constexpr int kAdamChunk = 4096;
+constexpr int kAdamCols = 5;
 template <typename P, typename G>
 __global__ void __launch_bounds__(256) adamw_kernel(const long long* __restrict__ table,
                                                     const long long* __restrict__ numel,
@@ -182,10 +185,11 @@ __global__ void __launch_bounds__(256) adamw_kernel(const long long* __restrict_
     else hi = mid - 1;
   }
   const int t = lo;
-  P* p = reinterpret_cast<P*>(table[4 * t]);
-  const G* g = reinterpret_cast<const G*>(table[4 * t + 1]);
-  float* m = reinterpret_cast<float*>(table[4 * t + 2]);
-  float* v = reinterpret_cast<float*>(table[4 * t + 3]);
+  P* p = reinterpret_cast<P*>(table[kAdamCols * t]);
+  const G* g = reinterpret_cast<const G*>(table[kAdamCols * t + 1]);
+  float* m = reinterpret_cast<float*>(table[kAdamCols * t + 2]);
+  float* v = reinterpret_cast<float*>(table[kAdamCols * t + 3]);
+  __nv_bfloat16* shadow = reinterpret_cast<__nv_bfloat16*>(table[kAdamCols * t + 4]);
   const long long n = numel[t];
   const long long base = static_cast<long long>(chunk - chunk_start[t]) * kAdamChunk;
   const float step_size = lr / bc1, inv_bc2_sqrt = rsqrtf(bc2);
@@ -202,6 +206,51 @@ __global__ void __launch_bounds__(256) adamw_kernel(const long long* __restrict_
     pi -= lr * wd * pi;
     pi -= step_size * mi / (sqrtf(vi) * inv_bc2_sqrt + eps);
     p[i] = from_f<P>(pi);
+    if (shadow != nullptr) shadow[i] = __float2bfloat16_rn(pi);
+  }
+}
+
+// SwiGLU: in [rows, 2 I] = (gate | up), out [rows, I] = silu(gate) * up; eight elements per thread.
+template <typename T>
+__global__ void __launch_bounds__(256) swiglu_fwd_kernel(const T* __restrict__ in, T* __restrict__ out, long long rows,
+                                                         int inner) {
+  const int groups = inner / 8;
+  const long long total = rows * groups;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / groups;
+    const int c = static_cast<int>(i % groups) * 8;
+    float g[8], u[8], o[8];
+    Vec8<T>::load(in + r * 2 * inner + c, g);
+    Vec8<T>::load(in + r * 2 * inner + inner + c, u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = g[k] / (1.f + __expf(-g[k])) * u[k];
+    Vec8<T>::store(out + r * inner + c, o);
+  }
+}
+
+// din = (dy * up * d silu(gate) | dy * silu(gate))
+template <typename T>
+__global__ void __launch_bounds__(256) swiglu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ in,
+                                                         T* __restrict__ din, long long rows, int inner) {
+  const int groups = inner / 8;
+  const long long total = rows * groups;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / groups;
+    const int c = static_cast<int>(i % groups) * 8;
+    float g[8], u[8], d[8], dg[8], du[8];
+    Vec8<T>::load(in + r * 2 * inner + c, g);
+    Vec8<T>::load(in + r * 2 * inner + inner + c, u);
+    Vec8<T>::load(dy + r * inner + c, d);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float sg = 1.f / (1.f + __expf(-g[k]));
+      du[k] = d[k] * g[k] * sg;
+      dg[k] = d[k] * u[k] * sg * (1.f + g[k] * (1.f - sg));
+    }
+    Vec8<T>::store(din + r * 2 * inner + c, dg);
+    Vec8<T>::store(din + r * 2 * inner + inner + c, du);
   }
 }
 
@@ -269,7 +318,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> norm_bwd(at::Tensor dy, at::Tenso
   auto stream = at::cuda::getCurrentCUDAStream();
   at::Tensor dw = at::empty({H}, fopt), db = at::empty({rms ? 0 : H}, fopt);
   if (H <= 2048) {
-    const int grid = std::max(1, std::min((rows + kNormWarps - 1) / kNormWarps, sm_count()));
+    const int grid = std::max(1, std::min((rows + kNormWarps - 1) / kNormWarps, 2 * sm_count()));
     const int nparts = grid * kNormWarps;
     at::Tensor dw_part = at::empty({nparts, H}, fopt), db_part = at::empty({rms ? 0 : nparts, H}, fopt);
     const int nchunk = (H + 255) / 256;
@@ -327,6 +376,45 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> norm_bwd(at::Tensor dy, at::Tenso
   return {dx, dw, db};
 }
 
+at::Tensor swiglu_fwd(at::Tensor in) {
+  TORCH_CHECK(in.is_cuda() && in.is_contiguous() && in.dim() >= 1 && in.size(-1) % 16 == 0,
+              "swiglu: contiguous CUDA tensor whose last dimension (2 I) is a multiple of 16");
+  TORCH_CHECK(in.scalar_type() == at::kBFloat16 || in.scalar_type() == at::kFloat, "swiglu: bf16 or fp32");
+  c10::cuda::CUDAGuard guard(in.device());
+  const int inner = static_cast<int>(in.size(-1) / 2);
+  const long long rows = in.numel() / (2 * inner);
+  auto shape = in.sizes().vec();
+  shape.back() = inner;
+  at::Tensor out = at::empty(shape, in.options());
+  const long long total = rows * (inner / 8);
+  const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>((total + 255) / 256, sm_count() * 16LL)));
+  auto stream = at::cuda::getCurrentCUDAStream();
+  if (in.scalar_type() == at::kBFloat16)
+    swiglu_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(in.data_ptr()), reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), rows, inner);
+  else
+    swiglu_fwd_kernel<float><<<grid, 256, 0, stream>>>(in.data_ptr<float>(), out.data_ptr<float>(), rows, inner);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
+}
+
+at::Tensor swiglu_bwd(at::Tensor dy, at::Tensor in) {
+  TORCH_CHECK(dy.is_cuda() && dy.is_contiguous() && in.is_contiguous() && dy.scalar_type() == in.scalar_type() &&
+                  dy.numel() * 2 == in.numel(), "swiglu_bwd: dy [.., I] and in [.., 2 I] must be contiguous and agree");
+  c10::cuda::CUDAGuard guard(in.device());
+  const int inner = static_cast<int>(in.size(-1) / 2);
+  const long long rows = in.numel() / (2 * inner);
+  at::Tensor din = at::empty_like(in);
+  const long long total = rows * (inner / 8);
+  const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>((total + 255) / 256, sm_count() * 16LL)));
+  auto stream = at::cuda::getCurrentCUDAStream();
+  if (in.scalar_type() == at::kBFloat16)
+    swiglu_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dy.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(in.data_ptr()), reinterpret_cast<__nv_bfloat16*>(din.data_ptr()), rows, inner);
+  else
+    swiglu_bwd_kernel<float><<<grid, 256, 0, stream>>>(dy.data_ptr<float>(), in.data_ptr<float>(), din.data_ptr<float>(), rows, inner);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return din;
+}
+
 at::Tensor rope(at::Tensor x, at::Tensor cos, at::Tensor sin, bool backward) {
   TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.dim() == 4, "rope: x must be contiguous [B, S, heads, D]");
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kFloat, "rope: bf16 or fp32");
@@ -350,11 +438,11 @@ at::Tensor rope(at::Tensor x, at::Tensor cos, at::Tensor sin, bool backward) {
   return y;
 }
 
-// table: int64 [T, 4] device tensor of addresses; numel: int64 [T] device; chunk_start: int32 [T] device.
+// table: int64 [T, 5] device tensor of addresses (param, grad, m, v, bf16 shadow or 0); numel: int64 [T] device; chunk_start: int32 [T] device.
 void adamw_step(at::Tensor table, at::Tensor numel, at::Tensor chunk_start, int64_t total_chunks, bool param_bf16,
                 bool grad_bf16, double lr, double beta1, double beta2, double eps, double weight_decay, int64_t step,
                 double grad_scale) {
-  TORCH_CHECK(table.is_cuda() && table.scalar_type() == at::kLong && table.dim() == 2 && table.size(1) == 4, "adamw: bad table");
+  TORCH_CHECK(table.is_cuda() && table.scalar_type() == at::kLong && table.dim() == 2 && table.size(1) == kAdamCols, "adamw: bad table");
   TORCH_CHECK(numel.is_cuda() && numel.scalar_type() == at::kLong && chunk_start.is_cuda() && chunk_start.scalar_type() == at::kInt, "adamw: bad metadata");
   if (total_chunks == 0) return;
   c10::cuda::CUDAGuard guard(table.device());

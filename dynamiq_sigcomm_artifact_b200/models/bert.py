@@ -9,6 +9,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops.layers import LayerNorm, fused_cross_entropy, padded_vocab_logits, shift_labels
+from ..ops.linear import MasterLinear
 from .common import GeluMLP, SelfAttention, init_linear
 
 
@@ -54,7 +55,7 @@ class BertMLM(nn.Module):
         self.typ = nn.Embedding(c.type_vocab, c.hidden)
         self.ln_emb = LayerNorm(c.hidden, c.eps)
         self.layers = nn.ModuleList(BertLayer(c) for _ in range(c.n_layer))
-        self.head_dense = nn.Linear(c.hidden, c.hidden)
+        self.head_dense = MasterLinear(c.hidden, c.hidden)
         self.head_ln = LayerNorm(c.hidden, c.eps)
         self.head_bias = nn.Parameter(torch.zeros(c.vocab))
         self.apply(init_linear)

@@ -15,11 +15,12 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops.layers import apply_rope
+from ..ops.layers import apply_rope, swiglu
+from ..ops.linear import MasterLinear
 
 
 def init_linear(m: nn.Module, std: float = 0.02) -> None:
-    if isinstance(m, nn.Linear):
+    if isinstance(m, (nn.Linear, MasterLinear)):
         nn.init.normal_(m.weight, mean=0.0, std=std)
         if m.bias is not None:
             nn.init.zeros_(m.bias)
@@ -36,8 +37,8 @@ class SelfAttention(nn.Module):
         self.n_heads, self.n_kv = n_heads, n_kv_heads or n_heads
         self.head_dim = hidden // n_heads
         self.causal, self.rope = causal, rope
-        self.qkv = nn.Linear(hidden, (self.n_heads + 2 * self.n_kv) * self.head_dim, bias=bias)
-        self.proj = nn.Linear(hidden, hidden, bias=bias)
+        self.qkv = MasterLinear(hidden, (self.n_heads + 2 * self.n_kv) * self.head_dim, bias=bias)
+        self.proj = MasterLinear(hidden, hidden, bias=bias)
 
     def forward(self, x: torch.Tensor, cos=None, sin=None) -> torch.Tensor:
         B, S, _ = x.shape
@@ -56,8 +57,8 @@ class SelfAttention(nn.Module):
 class GeluMLP(nn.Module):
     def __init__(self, hidden: int, inner: int, approximate: str = "tanh"):
         super().__init__()
-        self.fc = nn.Linear(hidden, inner)
-        self.proj = nn.Linear(inner, hidden)
+        self.fc = MasterLinear(hidden, inner)
+        self.proj = MasterLinear(inner, hidden)
         self.approximate = approximate
 
     def forward(self, x):
@@ -67,12 +68,11 @@ class GeluMLP(nn.Module):
 class SwiGLU(nn.Module):
     def __init__(self, hidden: int, inner: int):
         super().__init__()
-        self.gate_up = nn.Linear(hidden, 2 * inner, bias=False)
-        self.down = nn.Linear(inner, hidden, bias=False)
+        self.gate_up = MasterLinear(hidden, 2 * inner, bias=False)
+        self.down = MasterLinear(inner, hidden, bias=False)
 
     def forward(self, x):
-        g, u = self.gate_up(x).chunk(2, dim=-1)
-        return self.down(F.silu(g) * u)
+        return self.down(swiglu(self.gate_up(x)))
 
 
 def count_params(m: nn.Module) -> int:

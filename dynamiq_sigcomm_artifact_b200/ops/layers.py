@@ -7,7 +7,7 @@ GPU) they fall back to the equivalent PyTorch expression.
 """
 from __future__ import annotations
 
-from typing import Iterable, List
+from typing import Iterable, List, Optional
 
 import torch
 import torch.nn as nn
@@ -97,6 +97,28 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
     return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).to(x.dtype)
 
 
+class _SwiGLUFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        ctx.save_for_backward(x)
+        counters.add("swiglu_fwd")
+        return require().swiglu_fwd(x)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        counters.add("swiglu_bwd")
+        return require().swiglu_bwd(dy.contiguous(), x)
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up for gate_up = (gate | up) along the last dimension; one kernel each way."""
+    if gate_up.is_cuda and gate_up.shape[-1] % 16 == 0:
+        return _SwiGLUFn.apply(gate_up.contiguous())
+    g, u = gate_up.chunk(2, dim=-1)
+    return F.silu(g) * u
+
+
 class _CrossEntropyFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, logits, labels, vocab: int, ignore_index: int):
@@ -162,15 +184,18 @@ class FusedAdamW(torch.optim.Optimizer):
     CHUNK = 4096
 
     def __init__(self, params: Iterable, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
-                 weight_decay: float = 0.01):
+                 weight_decay: float = 0.01, shadows: Optional[dict] = None):
+        """`shadows` maps a parameter to a bf16 tensor of the same shape that the kernel keeps equal
+        to the updated parameter (see ops/linear.py)."""
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
         self._tables = {}
         self._step = 0
+        self._shadows = dict(shadows or {})
 
     def _table(self, gi: int, group) -> list:
         """Per (param dtype, grad dtype) metadata; rebuilt when a gradient buffer moves."""
         ps: List[torch.Tensor] = [p for p in group["params"] if p.grad is not None]
-        key = tuple((p.data_ptr(), p.grad.data_ptr()) for p in ps)
+        key = tuple((p.data_ptr(), p.grad.data_ptr(), self._shadow_ptr(p)) for p in ps)
         cached = self._tables.get(gi)
         if cached is not None and cached[0] == key:
             return cached[1]
@@ -189,7 +214,8 @@ class FusedAdamW(torch.optim.Optimizer):
             rows, numel, starts, c = [], [], [], 0
             for p in plist:
                 st = self.state[p]
-                rows.append([p.data_ptr(), p.grad.data_ptr(), st["exp_avg"].data_ptr(), st["exp_avg_sq"].data_ptr()])
+                rows.append([p.data_ptr(), p.grad.data_ptr(), st["exp_avg"].data_ptr(), st["exp_avg_sq"].data_ptr(),
+                             self._shadow_ptr(p)])
                 numel.append(p.numel())
                 starts.append(c)
                 c += (p.numel() + self.CHUNK - 1) // self.CHUNK
@@ -199,6 +225,14 @@ class FusedAdamW(torch.optim.Optimizer):
                         pd == torch.bfloat16, gd == torch.bfloat16, plist))
         self._tables[gi] = (key, out)
         return out
+
+    def _shadow_ptr(self, p) -> int:
+        sh = self._shadows.get(p)
+        if sh is None:
+            return 0
+        if sh.dtype != torch.bfloat16 or sh.shape != p.shape or not sh.is_contiguous():
+            raise ValueError("a shadow must be a contiguous bf16 tensor of the parameter's shape")
+        return sh.data_ptr()
 
     @torch.no_grad()
     def step(self, closure=None, grad_scale: float = 1.0):
@@ -230,6 +264,8 @@ class FusedAdamW(torch.optim.Optimizer):
                     pf.addcdiv_(st["exp_avg"], (st["exp_avg_sq"] / bc2).sqrt_().add_(group["eps"]),
                                 value=-group["lr"] / bc1)
                     p.copy_(pf)
+                    if p in self._shadows:
+                        self._shadows[p].copy_(pf)
         return loss
 
     def state_dict(self):

@@ -1,0 +1,66 @@
+"""Linear layer with fp32 master weights and a resident bf16 working copy.
+
+Under ``torch.autocast`` every ``nn.Linear`` re-casts its fp32 weight to bf16 on every forward
+(one read of 4 and one write of 2 bytes per parameter per step, and one kernel launch per layer).
+``MasterLinear`` keeps the bf16 copy alive instead: the fused AdamW kernel writes it together
+with the fp32 parameter (``FusedAdamW(shadows=...)``), the forward and the input-gradient GEMM
+read it, and the weight-gradient GEMM writes fp32 directly (bf16 x bf16 -> fp32 output), so no
+cast kernel runs on the weight path at all.  The parameter seen by DDP, the hooks, the optimizer
+state and checkpoints is still the fp32 ``weight``.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+class _ShadowLinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, shadow, bias):
+        ctx.save_for_backward(x, shadow)
+        ctx.has_bias = bias is not None
+        return F.linear(x, shadow, None if bias is None else bias.to(x.dtype))
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, shadow = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = (dy2 @ shadow).reshape(x.shape) if ctx.needs_input_grad[0] else None
+        dw = torch.mm(dy2.t(), x2, out_dtype=torch.float32) if ctx.needs_input_grad[1] else None
+        db = dy2.sum(dim=0, dtype=torch.float32) if ctx.has_bias and ctx.needs_input_grad[3] else None
+        return dx, dw, None, db
+
+
+class MasterLinear(nn.Module):
+    """y = x W^T + b with W fp32 (the parameter) and a bf16 working copy used on bf16 CUDA inputs."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.weight = nn.Parameter(torch.empty(out_features, in_features))
+        self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
+        nn.init.kaiming_uniform_(self.weight, a=math.sqrt(5))
+        self.shadow = None  # bf16 copy, created by enable_shadows()
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.shadow is not None and x.is_cuda and x.dtype == torch.bfloat16:
+            return _ShadowLinearFn.apply(x, self.weight, self.shadow, self.bias)
+        return F.linear(x, self.weight, self.bias)
+
+
+def enable_shadows(model: nn.Module) -> Dict[nn.Parameter, torch.Tensor]:
+    """Create (or refresh) the bf16 copy of every MasterLinear weight; returns {weight: copy}."""
+    out: Dict[nn.Parameter, torch.Tensor] = {}
+    for m in model.modules():
+        if isinstance(m, MasterLinear):
+            if m.shadow is None or m.shadow.device != m.weight.device:
+                m.shadow = torch.empty_like(m.weight, dtype=torch.bfloat16)
+            with torch.no_grad():
+                m.shadow.copy_(m.weight)
+            out[m.weight] = m.shadow
+    return out

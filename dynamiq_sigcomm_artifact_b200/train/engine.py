@@ -25,6 +25,7 @@ from .. import hooks
 from ..config import DynamiqConfig
 from ..models import build_model, mask_tokens
 from ..ops.layers import FusedAdamW
+from ..ops.linear import enable_shadows
 
 
 @dataclass
@@ -57,10 +58,12 @@ class Trainer:
         self.device = device
         torch.manual_seed(cfg.seed)  # identical initial weights on every rank
         self.model = build_model(cfg.model).to(device)
+        # bf16 working copies of the linear weights, kept in step by the optimizer kernel
+        self.shadows = enable_shadows(self.model) if (device.type == "cuda" and cfg.dtype == "bf16") else {}
         self.state = None
         if self.world > 1:
             self.ddp = DDP(self.model, device_ids=[device.index] if device.type == "cuda" else None,
-                           bucket_cap_mb=cfg.bucket_cap_mb, gradient_as_bucket_view=True)
+                           bucket_cap_mb=cfg.bucket_cap_mb, gradient_as_bucket_view=True, broadcast_buffers=False)
             dcfg = DynamiqConfig.from_env(method=cfg.method, seed=cfg.seed, topology=cfg.topology,
                                           comm_ctas=cfg.comm_ctas, warmup_steps=cfg.warmup_steps,
                                           measure_comm_error=cfg.measure_comm_error)
@@ -70,7 +73,7 @@ class Trainer:
             self.ddp = None
             self.net = self.model
             self._flatten_grads()
-        self.opt = FusedAdamW(self.model.parameters(), lr=cfg.lr, weight_decay=cfg.weight_decay)
+        self.opt = FusedAdamW(self.model.parameters(), lr=cfg.lr, weight_decay=cfg.weight_decay, shadows=self.shadows)
         self.sched = torch.optim.lr_scheduler.LinearLR(self.opt, start_factor=1.0, end_factor=0.0,
                                                        total_iters=cfg.total_steps)
         self.step_idx = 0

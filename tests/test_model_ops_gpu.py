@@ -136,3 +136,50 @@ def test_padded_vocab_head_matches_plain_head():
     assert abs(float(loss) - float(ref)) < 1e-4
     assert torch.allclose(x.grad, x2.grad, atol=1e-4, rtol=1e-3)
     assert torch.allclose(w.grad, w2.grad, atol=1e-4, rtol=1e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_forward_backward(dtype):
+    from dynamiq_sigcomm_artifact_b200.ops.layers import swiglu
+
+    torch.manual_seed(4)
+    x = torch.randn(3, 17, 256, device="cuda").to(dtype).requires_grad_(True)
+    dy = torch.randn(3, 17, 128, device="cuda").to(dtype)
+    y = swiglu(x)
+    y.backward(dy)
+    xf = x.detach().float().requires_grad_(True)
+    g, u = xf.chunk(2, dim=-1)
+    ref = F.silu(g) * u
+    ref.backward(dy.float())
+    tol = 3e-2 if dtype == torch.bfloat16 else 1e-5
+    assert torch.allclose(y.float(), ref, atol=tol, rtol=tol)
+    assert torch.allclose(x.grad.float(), xf.grad, atol=tol, rtol=tol)
+
+
+def test_master_linear_matches_autocast_linear_and_optimizer_keeps_shadow():
+    from dynamiq_sigcomm_artifact_b200.ops.layers import FusedAdamW
+    from dynamiq_sigcomm_artifact_b200.ops.linear import MasterLinear, enable_shadows
+
+    torch.manual_seed(5)
+    lin = MasterLinear(64, 48).cuda()
+    ref = torch.nn.Linear(64, 48).cuda()
+    with torch.no_grad():
+        ref.weight.copy_(lin.weight)
+        ref.bias.copy_(lin.bias)
+    shadows = enable_shadows(lin)
+    x = torch.randn(5, 7, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    x2 = x.detach().clone().requires_grad_(True)
+    y = lin(x)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y2 = ref(x2)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    y2.backward(dy)
+    assert torch.allclose(y.float(), y2.float(), atol=2e-2, rtol=2e-2)
+    assert lin.weight.grad.dtype == torch.float32
+    assert torch.allclose(lin.weight.grad, ref.weight.grad, atol=3e-2, rtol=3e-2)
+    assert torch.allclose(lin.bias.grad, ref.bias.grad, atol=3e-2, rtol=3e-2)
+    assert torch.allclose(x.grad.float(), x2.grad.float(), atol=3e-2, rtol=3e-2)
+    opt = FusedAdamW(lin.parameters(), lr=1e-2, shadows=shadows)
+    opt.step()
+    assert torch.equal(lin.shadow, lin.weight.to(torch.bfloat16))
