@@ -46,7 +46,9 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--method", default="dynamiQ_aee_5bit")
     ap.add_argument("--topology", default=None)
     ap.add_argument("--comm-ctas", type=int, default=64)
-    ap.add_argument("--bucket-cap-mb", type=int, default=25)
+    ap.add_argument("--comm-threads", type=int, default=256)
+    ap.add_argument("--bucket-cap-mb", type=int, default=0, help="0: 25 MB (GPT-2, BERT) or 100 MB (Llama 1.2B)")
+    ap.add_argument("--rotation", default="simt", choices=["simt", "tc"])
     return ap.parse_args()
 
 
@@ -77,8 +79,12 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     mb, seq, task, desc = MODELS[args.model]
+    if args.bucket_cap_mb <= 0:
+        args.bucket_cap_mb = 100 if args.model == "llama-1.2b" else 25
+    os.environ.setdefault("DQ_ROTATION", args.rotation)
     cfg = TrainConfig(model=args.model, method=args.method, micro_batch=mb, seq_len=seq, task=task,
-                      bucket_cap_mb=args.bucket_cap_mb, topology=args.topology, comm_ctas=args.comm_ctas)
+                      bucket_cap_mb=args.bucket_cap_mb, topology=args.topology, comm_ctas=args.comm_ctas,
+                      comm_threads=args.comm_threads)
     tr = Trainer(cfg)
     dev = tr.device
     host_batches = [tr.synthetic_batch(pinned=True) for _ in range(4)]

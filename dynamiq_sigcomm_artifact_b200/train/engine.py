@@ -43,8 +43,10 @@ class TrainConfig:
     task: str = "causal"  # causal | mlm
     topology: Optional[str] = None
     comm_ctas: int = 64
+    comm_threads: int = 256
     warmup_steps: int = 2
     measure_comm_error: bool = False
+    cuda_graphs: bool = True  # capture each transformer block's forward and backward as CUDA graphs
 
 
 class Trainer:
@@ -60,12 +62,15 @@ class Trainer:
         self.model = build_model(cfg.model).to(device)
         # bf16 working copies of the linear weights, kept in step by the optimizer kernel
         self.shadows = enable_shadows(self.model) if (device.type == "cuda" and cfg.dtype == "bf16") else {}
+        self.graphed = False
+        if cfg.cuda_graphs and device.type == "cuda" and cfg.dtype == "bf16":
+            self.graphed = self._graph_blocks()
         self.state = None
         if self.world > 1:
             self.ddp = DDP(self.model, device_ids=[device.index] if device.type == "cuda" else None,
                            bucket_cap_mb=cfg.bucket_cap_mb, gradient_as_bucket_view=True, broadcast_buffers=False)
             dcfg = DynamiqConfig.from_env(method=cfg.method, seed=cfg.seed, topology=cfg.topology,
-                                          comm_ctas=cfg.comm_ctas, warmup_steps=cfg.warmup_steps,
+                                          comm_ctas=cfg.comm_ctas, comm_threads=cfg.comm_threads, warmup_steps=cfg.warmup_steps,
                                           measure_comm_error=cfg.measure_comm_error)
             self.state = hooks.register(self.ddp, cfg.method, config=dcfg)
             self.net = self.ddp
@@ -81,6 +86,48 @@ class Trainer:
         self._gen = torch.Generator(device=device).manual_seed(cfg.seed + 17 * self.rank + 1) \
             if device.type == "cuda" else torch.Generator().manual_seed(cfg.seed + 17 * self.rank + 1)
         self.autocast_dtype = {"bf16": torch.bfloat16, "fp32": None}[cfg.dtype]
+
+    def _graph_blocks(self) -> bool:
+        """Capture every transformer block (forward and backward) as CUDA graphs: a step then issues
+        two graph launches per block instead of ~100 eager kernels, which takes the host off the
+        critical path.  Shapes are fixed by (micro_batch, seq_len); evaluation runs eagerly.  DDP's
+        parameter hooks still fire block by block, so bucket collectives keep overlapping backward."""
+        m, cfg = self.model, self.cfg
+        blocks = getattr(m, "blocks", None) or getattr(m, "layers", None)
+        if blocks is None:
+            return False
+        c = m.config
+        hidden = getattr(c, "d_model", None) or getattr(c, "hidden")
+        x = torch.randn(cfg.micro_batch, cfg.seq_len, hidden, device=self.device, dtype=torch.bfloat16,
+                        requires_grad=True)
+        if hasattr(m, "_tables"):
+            cos, sin = m._tables(cfg.seq_len, self.device)
+            sample = tuple((x.detach().clone().requires_grad_(True), cos, sin) for _ in blocks)
+        else:
+            sample = tuple((x.detach().clone().requires_grad_(True),) for _ in blocks)
+        import warnings
+
+        from ..utils import counters
+
+        # kernels of this package launched by one forward + backward of a block (replays repeat them)
+        before = counters.total()
+        with torch.autocast("cuda", dtype=torch.bfloat16, cache_enabled=False):
+            blocks[0](*sample[0]).float().sum().backward()
+        self._launches_per_graphed_step = (counters.total() - before) * len(blocks)
+        # parameters were created on the default stream and the capture runs on a side stream
+        warnings.filterwarnings("ignore", message="The AccumulateGrad node's stream does not match")
+        try:
+            with torch.autocast("cuda", dtype=torch.bfloat16, cache_enabled=False):
+                graphed = torch.cuda.make_graphed_callables(tuple(blocks), sample, num_warmup_iters=3)
+        except Exception as e:  # fall back to eager execution, loudly
+            print(f"[dynamiq] CUDA graph capture of the blocks failed ({type(e).__name__}: {e}); running eagerly",
+                  flush=True)
+            return False
+        for i, g in enumerate(graphed):
+            blocks[i] = g
+        for p in m.parameters():  # capture warm-up ran backward passes: drop their gradients
+            p.grad = None
+        return True
 
     def _flatten_grads(self) -> None:
         """Single-process runs: all gradients live in one flat buffer, zeroed by one memset."""
@@ -109,6 +156,10 @@ class Trainer:
         else:
             loss = self.net(input_ids, labels)
         loss.backward()
+        if self.graphed:
+            from ..utils import counters
+
+            counters.add("graphed_blocks", self._launches_per_graphed_step)
         self.opt.step()
         self.sched.step()
         if self.ddp is None:
