@@ -19,12 +19,14 @@ void fused_allreduce(at::Tensor bucket, at::Tensor steps, std::vector<int64_t> m
                      int64_t status_ptr, int64_t tail_ws_ptr, int64_t rank, int64_t world, int64_t bits, int64_t ctas,
                      int64_t threads, int64_t blocks_per_shard, int64_t slot_stride, int64_t scales_off,
                      int64_t flag_base, int64_t epoch, int64_t seed, int64_t step, int64_t bucket_id,
-                     double post_scale, int64_t timeout_ns, bool no_transmit, bool tensor_rotation);
+                     double post_scale, int64_t timeout_ns, bool no_transmit, int64_t codec, double sc_lattice_max, double sc_c1, double sc_c2,
+                     c10::optional<at::Tensor> sc_lut);
 void fused_allreduce_local(std::vector<at::Tensor> buckets, at::Tensor steps, std::vector<at::Tensor> mailboxes,
                            std::vector<at::Tensor> flags, at::Tensor status, at::Tensor tail_ws, int64_t nslots,
                            int64_t bits, int64_t ctas, int64_t threads, int64_t blocks_per_shard, int64_t slot_stride,
                            int64_t scales_off, int64_t flag_base, int64_t epoch, int64_t seed, int64_t step,
-                           int64_t bucket_id, double post_scale, int64_t timeout_ns, bool no_transmit, bool tensor_rotation);
+                           int64_t bucket_id, double post_scale, int64_t timeout_ns, bool no_transmit, int64_t codec, double sc_lattice_max, double sc_c1, double sc_c2,
+                     c10::optional<at::Tensor> sc_lut);
 std::tuple<at::Tensor, at::Tensor, at::Tensor> norm_fwd(at::Tensor x, at::Tensor w, c10::optional<at::Tensor> b,
                                                         double eps, bool rms);
 std::tuple<at::Tensor, at::Tensor, at::Tensor> norm_bwd(at::Tensor dy, at::Tensor x, at::Tensor w, at::Tensor mean,
@@ -38,6 +40,8 @@ at::Tensor bins_to_bits(at::Tensor bins, int64_t nbits);
 at::Tensor bits_to_bins(at::Tensor words, int64_t nbits, int64_t n);
 at::Tensor swiglu_fwd(at::Tensor in);
 at::Tensor swiglu_bwd(at::Tensor dy, at::Tensor in);
+std::tuple<at::Tensor, at::Tensor> superchunk_center(at::Tensor x, int64_t world);
+void superchunk_add_mean(at::Tensor resid, at::Tensor mean, at::Tensor out);
 at::Tensor rope(at::Tensor x, at::Tensor cos, at::Tensor sin, bool backward);
 void adamw_step(at::Tensor table, at::Tensor numel, at::Tensor chunk_start, int64_t total_chunks, bool param_bf16,
                 bool grad_bf16, double lr, double beta1, double beta2, double eps, double weight_decay, int64_t step,
@@ -54,6 +58,8 @@ TORCH_LIBRARY(dq, m) {
   m.def("bits_to_bins(Tensor words, int nbits, int n) -> Tensor", &dq::bits_to_bins);
   m.def("swiglu_fwd(Tensor x) -> Tensor", &dq::swiglu_fwd);
   m.def("swiglu_bwd(Tensor dy, Tensor x) -> Tensor", &dq::swiglu_bwd);
+  m.def("superchunk_center(Tensor x, int world) -> (Tensor, Tensor)", &dq::superchunk_center);
+  m.def("superchunk_add_mean(Tensor resid, Tensor mean, Tensor(a!) out) -> ()", &dq::superchunk_add_mean);
   m.def("rope(Tensor x, Tensor cos, Tensor sin, bool backward) -> Tensor", &dq::rope);
   m.def("adamw_step(Tensor table, Tensor numel, Tensor chunk_start, int total_chunks, bool param_bf16, bool grad_bf16, "
         "float lr, float beta1, float beta2, float eps, float weight_decay, int step, float grad_scale) -> ()", &dq::adamw_step);
@@ -67,12 +73,12 @@ TORCH_LIBRARY(dq, m) {
       "fused_allreduce(Tensor(a!) bucket, Tensor steps, int[] mail_ptrs, int[] flag_ptrs, int mailbox_bytes, "
       "int flag_words, int nslots, int status_ptr, int tail_ws_ptr, int rank, int world, int bits, int ctas, "
       "int threads, int blocks_per_shard, int slot_stride, int scales_off, int flag_base, int epoch, int seed, "
-      "int step, int bucket_id, float post_scale, int timeout_ns, bool no_transmit, bool tensor_rotation) -> ()",
+      "int step, int bucket_id, float post_scale, int timeout_ns, bool no_transmit, int codec, float sc_lattice_max, float sc_c1, float sc_c2, Tensor? sc_lut) -> ()",
       &dq::fused_allreduce);
   m.def(
       "fused_allreduce_local(Tensor[] buckets, Tensor steps, Tensor[] mailboxes, Tensor[] flags, Tensor status, "
       "Tensor tail_ws, int nslots, int bits, int ctas, int threads, int blocks_per_shard, int slot_stride, "
       "int scales_off, int flag_base, int epoch, int seed, int step, int bucket_id, float post_scale, "
-      "int timeout_ns, bool no_transmit, bool tensor_rotation) -> ()",
+      "int timeout_ns, bool no_transmit, int codec, float sc_lattice_max, float sc_c1, float sc_c2, Tensor? sc_lut) -> ()",
       &dq::fused_allreduce_local);
 }

@@ -1,0 +1,177 @@
+// Warp-level hierarchical "scaling quantisation" codec (the reference's superchunk format).
+//
+// A warp owns a block of 1024 values = 4 superchunks of 256 = 16 chunks of 16.  Lane l holds the 32
+// consecutive values [32 l, 32 l + 32): two whole chunks of superchunk l / 8, so chunk maxima need
+// no shuffles and the superchunk maximum is a 3-step butterfly inside an 8-lane group.
+//
+// Wire record of a superchunk (byte for byte the reference's layout, eden_utils.cpp:33-40,
+// scaling_quantization_algorithm.md:347-388): 16 x [2 b bytes of codes, little end first | 1 byte
+// round-up chunk scale] + 2 bytes bf16 scale unit = 16 (2 b + 1) + 2 bytes.  A block's four records are
+// contiguous (an 8-byte multiple), are assembled in the warp's shared-memory tile and move with 8-byte
+// accesses.
+//
+// Arithmetic restates parallel/codecs.py::SuperchunkCodec operation by operation (fp32, one rounding
+// per operation), which itself restates the reference kernels
+// (cuda_hierarchical_mee.cu:203-343 encode, :345-505 decode, :526-696 hop); partial sums stay fp32.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "philox.cuh"
+#include "rht_codec.cuh"
+
+namespace dq {
+
+struct ScParams {
+  float lattice_max;  // R for the linear lattice, lattice(R) for the logarithmic one
+  float c1, c2;       // (1 + e^2) / (2 e^2) and log2(1 + 2 e^2)
+  const float* lut;   // decode levels [2^b], device memory
+};
+
+template <int B>
+struct ScGeom {
+  static constexpr int kChunkBytes = 2 * B + 1;
+  static constexpr int kRecordBytes = 16 * kChunkBytes + 2;  // 82 / 146 / 274
+  static constexpr int kBlockBytes = 4 * kRecordBytes;       // 328 / 584 / 1096: multiples of 8
+};
+
+__device__ __forceinline__ float sc_sanitize(float x) { return (fabsf(x) <= 3.402823466e38f) ? x : 0.0f; }
+
+// lane-contiguous layout: reg k of lane l = element 32 l + k
+template <typename T>
+__device__ __forceinline__ void sc_load_block(const T* base, int valid, bool vec_ok, int lane, float (&v)[32]) {
+  if (valid == 1024 && vec_ok) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      float o[4];
+      Elem<T>::load4(base + 32 * lane + 4 * q, o);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) v[4 * q + k] = o[k];
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+      const int e = 32 * lane + k;
+      v[k] = e < valid ? Elem<T>::to_float(base[e]) : 0.0f;
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void sc_store_block(T* base, int valid, bool vec_ok, int lane, const float (&v)[32]) {
+  if (valid == 1024 && vec_ok) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      float o[4] = {v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]};
+      Elem<T>::store4(base + 32 * lane + 4 * q, o);
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+      const int e = 32 * lane + k;
+      if (e < valid) base[e] = Elem<T>::from_float(v[k]);
+    }
+  }
+}
+
+// Encode the block held in v into four records in `tile` (shared memory, >= kBlockBytes).
+template <int B, bool MEE>
+__device__ __forceinline__ void sc_encode_block(const float (&v)[32], uint8_t* tile, const ScParams& sp,
+                                                uint32_t first_call, uint32_t tag, uint32_t step, uint32_t k0,
+                                                uint32_t k1, int lane) {
+  constexpr int R = (1 << (B - 1)) - 1;
+  using G = ScGeom<B>;
+  float x[32], s[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float am = 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      x[16 * h + k] = sc_sanitize(v[16 * h + k]);
+      am = fmaxf(am, fabsf(x[16 * h + k]));
+    }
+    s[h] = fmaxf(__fadd_rn(__fdiv_rn(am, sp.lattice_max), 1e-7f), 1e-30f);
+  }
+  float S = fmaxf(s[0], s[1]);
+#pragma unroll
+  for (int o = 1; o < 8; o <<= 1) S = fmaxf(S, __shfl_xor_sync(0xFFFFFFFFu, S, o));
+  const __nv_bfloat16 unit_bf = __float2bfloat16_rn(fmaxf(__fdiv_rn(S, 255.0f), 1e-30f));
+  const float unit = fmaxf(__bfloat162float(unit_bf), 1e-30f);
+  uint8_t* rec = tile + (lane >> 3) * G::kRecordBytes;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const float q = fminf(fmaxf(ceilf(__fmul_rn(__fdiv_rn(s[h], S), 255.0f)), 1.0f), 255.0f);
+    const float dec = fmaxf(__fmul_rn(q, unit), 1e-30f);
+    U4 r = philox4x32<7>(first_call + 2u * static_cast<uint32_t>(lane) + h, 0u, tag, step, k0, k1);
+    const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+    uint32_t code[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      float y = __fdiv_rn(x[16 * h + k], dec);
+      if (MEE) {
+        const float mag = __fdiv_rn(log2f(__fadd_rn(__fdiv_rn(fabsf(y), sp.c1), 1.0f)), sp.c2);
+        y = y > 0.f ? mag : (y < 0.f ? -mag : 0.f);
+      }
+      const float u = __fmul_rn(__fadd_rn(static_cast<float>((rw[k >> 2] >> (8 * (k & 3))) & 0xFFu), 0.5f), 1.0f / 256.0f);
+      const float fl = floorf(y);
+      float c = fl + ((__fsub_rn(y, fl) > u) ? 1.0f : 0.0f);
+      c = fminf(fmaxf(c, static_cast<float>(-R)), static_cast<float>(R));
+      code[k] = static_cast<uint32_t>(static_cast<int>(c) + R);
+    }
+    uint8_t* ch = rec + (2 * (lane & 7) + h) * G::kChunkBytes;
+    constexpr int per = 8 / B;  // codes per byte, little end first
+#pragma unroll
+    for (int byte = 0; byte < 2 * B; ++byte) {
+      uint32_t val = 0;
+#pragma unroll
+      for (int j = 0; j < per; ++j) val |= code[byte * per + j] << (j * B);
+      ch[byte] = static_cast<uint8_t>(val);
+    }
+    ch[2 * B] = static_cast<uint8_t>(q);
+  }
+  if ((lane & 7) == 0) {
+    const unsigned short bits = __bfloat16_as_ushort(unit_bf);
+    rec[16 * G::kChunkBytes] = static_cast<uint8_t>(bits & 0xFF);
+    rec[16 * G::kChunkBytes + 1] = static_cast<uint8_t>(bits >> 8);
+  }
+}
+
+// Decode the four records in `tile`; ADD: v <- v + decoded (one rounding each), else v <- decoded.
+template <int B, bool MEE, bool ADD>
+__device__ __forceinline__ void sc_decode_block(float (&v)[32], const uint8_t* tile, const ScParams& sp, int lane) {
+  constexpr int R = (1 << (B - 1)) - 1;
+  using G = ScGeom<B>;
+  const uint8_t* rec = tile + (lane >> 3) * G::kRecordBytes;
+  const unsigned short ub = static_cast<unsigned short>(rec[16 * G::kChunkBytes]) |
+                            (static_cast<unsigned short>(rec[16 * G::kChunkBytes + 1]) << 8);
+  const float unit = fmaxf(__bfloat162float(__ushort_as_bfloat16(ub)), 1e-30f);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint8_t* ch = rec + (2 * (lane & 7) + h) * G::kChunkBytes;
+    const float dec = fmaxf(__fmul_rn(static_cast<float>(ch[2 * B]), unit), 1e-30f);
+    constexpr int per = 8 / B;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const uint32_t code = (static_cast<uint32_t>(ch[k / per]) >> ((k % per) * B)) & ((1u << B) - 1u);
+      const float level = MEE ? sp.lut[code] : static_cast<float>(static_cast<int>(code) - R);
+      const float val = __fmul_rn(level, dec);
+      v[16 * h + k] = ADD ? __fadd_rn(v[16 * h + k], val) : val;
+    }
+  }
+}
+
+// shared-memory tile <-> global record area, 8 bytes per lane per trip
+template <int B>
+__device__ __forceinline__ void sc_copy_out(uint8_t* dst, const uint8_t* tile, int lane) {
+  constexpr int n8 = ScGeom<B>::kBlockBytes / 8;
+  for (int i = lane; i < n8; i += 32)
+    reinterpret_cast<unsigned long long*>(dst)[i] = reinterpret_cast<const unsigned long long*>(tile)[i];
+}
+template <int B>
+__device__ __forceinline__ void sc_copy_in(uint8_t* tile, const uint8_t* src, int lane) {
+  constexpr int n8 = ScGeom<B>::kBlockBytes / 8;
+  for (int i = lane; i < n8; i += 32)
+    reinterpret_cast<unsigned long long*>(tile)[i] = __ldcg(reinterpret_cast<const unsigned long long*>(src) + i);
+}
+
+}  // namespace dq

@@ -28,31 +28,71 @@ namespace dq {
 static constexpr int kBlock = 1024;  // codec block, elements
 
 // defined in fused_allreduce_b{2..8}.cu
-template <int BITS, typename T, bool TC>
+template <int BITS, typename T, int CODEC>
 void launch_one(const ARParams* host_params, const ARParams* dev_params, int nranks, int ctas, int threads,
                 cudaStream_t stream);
 
-template <typename T, bool TC>
-static void launch_bits_tc(int bits, const ARParams* hp, const ARParams* dp, int nranks, int ctas, int threads,
-                           cudaStream_t stream) {
+template <typename T, int CODEC>
+static void launch_rht(int bits, const ARParams* hp, const ARParams* dp, int nranks, int ctas, int threads,
+                       cudaStream_t stream) {
   switch (bits) {
-    case 2: launch_one<2, T, TC>(hp, dp, nranks, ctas, threads, stream); break;
-    case 3: launch_one<3, T, TC>(hp, dp, nranks, ctas, threads, stream); break;
-    case 4: launch_one<4, T, TC>(hp, dp, nranks, ctas, threads, stream); break;
-    case 5: launch_one<5, T, TC>(hp, dp, nranks, ctas, threads, stream); break;
-    case 6: launch_one<6, T, TC>(hp, dp, nranks, ctas, threads, stream); break;
-    case 7: launch_one<7, T, TC>(hp, dp, nranks, ctas, threads, stream); break;
-    case 8: launch_one<8, T, TC>(hp, dp, nranks, ctas, threads, stream); break;
+    case 2: launch_one<2, T, CODEC>(hp, dp, nranks, ctas, threads, stream); break;
+    case 3: launch_one<3, T, CODEC>(hp, dp, nranks, ctas, threads, stream); break;
+    case 4: launch_one<4, T, CODEC>(hp, dp, nranks, ctas, threads, stream); break;
+    case 5: launch_one<5, T, CODEC>(hp, dp, nranks, ctas, threads, stream); break;
+    case 6: launch_one<6, T, CODEC>(hp, dp, nranks, ctas, threads, stream); break;
+    case 7: launch_one<7, T, CODEC>(hp, dp, nranks, ctas, threads, stream); break;
+    case 8: launch_one<8, T, CODEC>(hp, dp, nranks, ctas, threads, stream); break;
     default: TORCH_CHECK(false, "bits must be in 2..8, got ", bits);
   }
 }
 
-// hp->tensor_rotation (or dp's host copy, passed in `tensor`) selects tcgen05 or SIMT rotation
+template <typename T, int CODEC>
+static void launch_sc(int bits, const ARParams* hp, const ARParams* dp, int nranks, int ctas, int threads,
+                      cudaStream_t stream) {
+  switch (bits) {
+    case 2: launch_one<2, T, CODEC>(hp, dp, nranks, ctas, threads, stream); break;
+    case 4: launch_one<4, T, CODEC>(hp, dp, nranks, ctas, threads, stream); break;
+    case 8: launch_one<8, T, CODEC>(hp, dp, nranks, ctas, threads, stream); break;
+    default: TORCH_CHECK(false, "the superchunk codec has 2, 4 and 8 bit codes, got ", bits);
+  }
+}
+
+// `codec`: kCodecRht (SIMT rotation), kCodecRhtTc (tcgen05 rotation), kCodecScAee, kCodecScMee
 template <typename T>
 static void launch_bits(int bits, const ARParams* hp, const ARParams* dp, int nranks, int ctas, int threads,
-                        cudaStream_t stream, bool tensor) {
-  if (tensor) launch_bits_tc<T, true>(bits, hp, dp, nranks, ctas, threads, stream);
-  else launch_bits_tc<T, false>(bits, hp, dp, nranks, ctas, threads, stream);
+                        cudaStream_t stream, int codec) {
+  switch (codec) {
+    case kCodecRht: launch_rht<T, kCodecRht>(bits, hp, dp, nranks, ctas, threads, stream); break;
+    case kCodecRhtTc: launch_rht<T, kCodecRhtTc>(bits, hp, dp, nranks, ctas, threads, stream); break;
+    case kCodecScAee: launch_sc<T, kCodecScAee>(bits, hp, dp, nranks, ctas, threads, stream); break;
+    case kCodecScMee: launch_sc<T, kCodecScMee>(bits, hp, dp, nranks, ctas, threads, stream); break;
+    default: TORCH_CHECK(false, "unknown codec ", codec);
+  }
+}
+
+static unsigned block_bytes_of(int codec, int bits) {
+  if (codec == kCodecScAee || codec == kCodecScMee) return 4u * (16u * (2u * bits + 1u) + 2u);
+  return 128u * bits;
+}
+
+// superchunk codec constants; `lut` holds the 2^bits decode levels (device, fp32)
+static void fill_sc(ARParams& p, int64_t codec, int64_t bits, double lattice_max, double c1, double c2,
+                    const c10::optional<at::Tensor>& lut) {
+  p.codec = static_cast<int>(codec);
+  p.tensor_rotation = codec == kCodecRhtTc;
+  p.block_bytes = block_bytes_of(static_cast<int>(codec), static_cast<int>(bits));
+  p.sc_lattice_max = static_cast<float>(lattice_max);
+  p.sc_c1 = static_cast<float>(c1);
+  p.sc_c2 = static_cast<float>(c2);
+  p.sc_lut = nullptr;
+  if (codec == kCodecScMee) {
+    TORCH_CHECK(lut.has_value() && lut->is_cuda() && lut->scalar_type() == at::kFloat && lut->is_contiguous() &&
+                    lut->numel() >= (1 << bits),
+                "the MEE codec needs a CUDA fp32 table of 2^bits decode levels");
+    p.sc_lut = lut->data_ptr<float>();
+  }
+  if (codec == kCodecScAee || codec == kCodecScMee) TORCH_CHECK(lattice_max > 0, "lattice_max must be positive");
 }
 
 static void fill_common(ARParams& p, const at::Tensor& bucket, const at::Tensor& steps, int64_t rank, int64_t world,
@@ -95,9 +135,12 @@ static void fill_common(ARParams& p, const at::Tensor& bucket, const at::Tensor&
 
 static void check_layout(const ARParams& p, int bits, int64_t mailbox_bytes, int64_t nslots, int64_t flag_words,
                          int ctas) {
-  const unsigned long long need = static_cast<unsigned long long>(p.blocks_per_shard) * (128ull * bits);
+  (void)bits;
+  const unsigned long long need = static_cast<unsigned long long>(p.blocks_per_shard) * p.block_bytes;
+  const bool has_scales = p.codec == kCodecRht || p.codec == kCodecRhtTc;  // one fp32 scale per block after the codes
   TORCH_CHECK(p.scales_off >= need && (p.scales_off % 16) == 0, "scales overlap the codes of a slot");
-  TORCH_CHECK(p.slot_stride >= p.scales_off + 4ull * p.blocks_per_shard && (p.slot_stride % 16) == 0,
+  TORCH_CHECK(p.slot_stride >= p.scales_off + (has_scales ? 4ull * p.blocks_per_shard : 0ull) &&
+                  (p.slot_stride % 16) == 0,
               "slot stride too small");
   TORCH_CHECK(static_cast<unsigned long long>(nslots) * p.slot_stride <= static_cast<unsigned long long>(mailbox_bytes),
               "mailbox too small for ", nslots, " slots");
@@ -118,7 +161,8 @@ void fused_allreduce(at::Tensor bucket, at::Tensor steps, std::vector<int64_t> m
                      int64_t status_ptr, int64_t tail_ws_ptr, int64_t rank, int64_t world, int64_t bits, int64_t ctas,
                      int64_t threads, int64_t blocks_per_shard, int64_t slot_stride, int64_t scales_off,
                      int64_t flag_base, int64_t epoch, int64_t seed, int64_t step, int64_t bucket_id,
-                     double post_scale, int64_t timeout_ns, bool no_transmit, bool tensor_rotation) {
+                     double post_scale, int64_t timeout_ns, bool no_transmit, int64_t codec, double sc_lattice_max, double sc_c1, double sc_c2,
+                     c10::optional<at::Tensor> sc_lut) {
   c10::cuda::CUDAGuard guard(bucket.device());
   TORCH_CHECK(static_cast<int64_t>(mail_ptrs.size()) == world && static_cast<int64_t>(flag_ptrs.size()) == world,
               "need one mailbox and one flag pointer per rank");
@@ -126,6 +170,7 @@ void fused_allreduce(at::Tensor bucket, at::Tensor steps, std::vector<int64_t> m
   ARParams p{};
   fill_common(p, bucket, steps, rank, world, blocks_per_shard, slot_stride, scales_off, flag_base, epoch, seed, step,
               bucket_id, post_scale, timeout_ns, status_ptr, tail_ws_ptr, no_transmit);
+  fill_sc(p, codec, bits, sc_lattice_max, sc_c1, sc_c2, sc_lut);
   for (int r = 0; r < world; ++r) {
     p.mail[r] = reinterpret_cast<uint8_t*>(mail_ptrs[r]);
     p.flags[r] = reinterpret_cast<uint32_t*>(flag_ptrs[r]);
@@ -133,9 +178,9 @@ void fused_allreduce(at::Tensor bucket, at::Tensor steps, std::vector<int64_t> m
   check_layout(p, static_cast<int>(bits), mailbox_bytes, nslots, flag_words, static_cast<int>(ctas));
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   if (bucket.scalar_type() == at::kFloat)
-    launch_bits<float>(static_cast<int>(bits), &p, nullptr, 1, static_cast<int>(ctas), static_cast<int>(threads), stream, tensor_rotation);
+    launch_bits<float>(static_cast<int>(bits), &p, nullptr, 1, static_cast<int>(ctas), static_cast<int>(threads), stream, static_cast<int>(codec));
   else
-    launch_bits<__nv_bfloat16>(static_cast<int>(bits), &p, nullptr, 1, static_cast<int>(ctas), static_cast<int>(threads), stream, tensor_rotation);
+    launch_bits<__nv_bfloat16>(static_cast<int>(bits), &p, nullptr, 1, static_cast<int>(ctas), static_cast<int>(threads), stream, static_cast<int>(codec));
 }
 
 // All ranks of a collective in one launch on one GPU.  buckets[r], mailboxes[r] (uint8),
@@ -145,7 +190,8 @@ void fused_allreduce_local(std::vector<at::Tensor> buckets, at::Tensor steps, st
                            std::vector<at::Tensor> flags, at::Tensor status, at::Tensor tail_ws, int64_t nslots,
                            int64_t bits, int64_t ctas, int64_t threads, int64_t blocks_per_shard, int64_t slot_stride,
                            int64_t scales_off, int64_t flag_base, int64_t epoch, int64_t seed, int64_t step,
-                           int64_t bucket_id, double post_scale, int64_t timeout_ns, bool no_transmit, bool tensor_rotation) {
+                           int64_t bucket_id, double post_scale, int64_t timeout_ns, bool no_transmit, int64_t codec, double sc_lattice_max, double sc_c1, double sc_c2,
+                     c10::optional<at::Tensor> sc_lut) {
   const int64_t world = static_cast<int64_t>(buckets.size());
   TORCH_CHECK(world >= 1 && world <= kMaxWorld, "1..8 ranks");
   TORCH_CHECK(steps.dim() == 3 && steps.size(0) == world, "steps must be [world, nsteps, 8]");
@@ -168,6 +214,7 @@ void fused_allreduce_local(std::vector<at::Tensor> buckets, at::Tensor steps, st
                 flag_base, epoch, seed, step, bucket_id, post_scale, timeout_ns,
                 reinterpret_cast<int64_t>(status.data_ptr()),
                 reinterpret_cast<int64_t>(tail_ws.data_ptr<float>() + r * kBlock), no_transmit);
+    fill_sc(hp[r], codec, bits, sc_lattice_max, sc_c1, sc_c2, sc_lut);
     for (int64_t q = 0; q < world; ++q) {
       hp[r].mail[q] = static_cast<uint8_t*>(mailboxes[q].data_ptr());
       hp[r].flags[q] = reinterpret_cast<uint32_t*>(flags[q].data_ptr());
@@ -178,9 +225,9 @@ void fused_allreduce_local(std::vector<at::Tensor> buckets, at::Tensor steps, st
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   if (world == 1) {
     if (buckets[0].scalar_type() == at::kFloat)
-      launch_bits<float>(static_cast<int>(bits), hp.data(), nullptr, 1, static_cast<int>(ctas), static_cast<int>(threads), stream, tensor_rotation);
+      launch_bits<float>(static_cast<int>(bits), hp.data(), nullptr, 1, static_cast<int>(ctas), static_cast<int>(threads), stream, static_cast<int>(codec));
     else
-      launch_bits<__nv_bfloat16>(static_cast<int>(bits), hp.data(), nullptr, 1, static_cast<int>(ctas), static_cast<int>(threads), stream, tensor_rotation);
+      launch_bits<__nv_bfloat16>(static_cast<int>(bits), hp.data(), nullptr, 1, static_cast<int>(ctas), static_cast<int>(threads), stream, static_cast<int>(codec));
     return;
   }
   at::Tensor dev = at::empty({static_cast<int64_t>(world * sizeof(ARParams))},
@@ -189,9 +236,9 @@ void fused_allreduce_local(std::vector<at::Tensor> buckets, at::Tensor steps, st
   C10_CUDA_CHECK(cudaStreamSynchronize(stream));  // hp is pageable host memory
   const ARParams* dp = reinterpret_cast<const ARParams*>(dev.data_ptr());
   if (buckets[0].scalar_type() == at::kFloat)
-    launch_bits<float>(static_cast<int>(bits), nullptr, dp, static_cast<int>(world), static_cast<int>(ctas), static_cast<int>(threads), stream, tensor_rotation);
+    launch_bits<float>(static_cast<int>(bits), nullptr, dp, static_cast<int>(world), static_cast<int>(ctas), static_cast<int>(threads), stream, static_cast<int>(codec));
   else
-    launch_bits<__nv_bfloat16>(static_cast<int>(bits), nullptr, dp, static_cast<int>(world), static_cast<int>(ctas), static_cast<int>(threads), stream, tensor_rotation);
+    launch_bits<__nv_bfloat16>(static_cast<int>(bits), nullptr, dp, static_cast<int>(world), static_cast<int>(ctas), static_cast<int>(threads), stream, static_cast<int>(codec));
   C10_CUDA_CHECK(cudaStreamSynchronize(stream));  // keep `dev` alive until the kernel has read it
 }
 

@@ -12,6 +12,7 @@ constexpr uint32_t kTagStratified = 0x4000u;  // step tag flag: stratified round
 // local operand / result of a step: keep in sync with parallel/schedules.py
 enum : int { kLocalRaw = 0, kLocalWs = 1 };
 enum : int { kOutSend = 0, kOutStore = 1, kOutFinal = 2, kOutDecode = 3 };
+enum : int { kCodecRht = 0, kCodecRhtTc = 1, kCodecScAee = 2, kCodecScMee = 3 };
 
 // error codes left in status[0]; status[1] = (step << 16) | cta, status[2] = slot
 enum : uint32_t { kOk = 0, kErrWaitTimeout = 1, kErrBadProgram = 2, kErrCopyTimeout = 3, kErrMmaTimeout = 4 };
@@ -36,6 +37,10 @@ struct ARParams {
   uint32_t* status;                // 4 words, local
   int no_transmit;                 // debug: run the maths, skip remote payload stores
   int tensor_rotation;             // host-side selector: 1 = tcgen05 rotation, 0 = SIMT butterflies
+  int codec;                       // host-side selector: kCodecRht / kCodecScAee / kCodecScMee
+  unsigned int block_bytes;        // bytes of one encoded 1024-element block inside a message
+  float sc_lattice_max, sc_c1, sc_c2;  // superchunk codec constants
+  const float* sc_lut;             // superchunk codec decode levels [2^bits] (device memory)
   int steps[kMaxSteps][kStepInts];
 };
 

@@ -7,6 +7,7 @@
 
 #include "../common/rht_codec.cuh"
 #include "../common/rht_tc.cuh"
+#include "../common/sc_codec.cuh"
 #include "fused_allreduce.cuh"
 
 namespace dq {
@@ -89,8 +90,12 @@ __host__ __device__ constexpr size_t fused_smem_bytes(int threads) {
          32 * 4 + nwarps * 8 + 128;
 }
 
-template <int BITS, typename T, bool TC>
+template <int BITS, typename T, int CODEC>
 __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
+  constexpr bool TC = CODEC == kCodecRhtTc;
+  constexpr bool SC = CODEC == kCodecScAee || CODEC == kCodecScMee;
+  constexpr bool MEE = CODEC == kCodecScMee;
+  constexpr int SCB = (BITS == 2 || BITS == 4 || BITS == 8) ? BITS : 4;  // superchunk code width (2, 4, 8 only)
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
   const int cta = blockIdx.x, G = gridDim.x;
@@ -166,7 +171,9 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
   // prefetch state (warp-uniform): the item whose data is in flight or resident in `stage`
   RawItem pf = RawItem{-1, -1};
   uint32_t pf_parity = 0;
-  bool prefetch_ok = true;
+  bool prefetch_ok = !SC;  // the superchunk codec reads lane-contiguous runs straight from global memory
+  const ScParams scp{p.sc_lattice_max, p.sc_c1, p.sc_c2, p.sc_lut};
+  uint8_t* rec_tile = reinterpret_cast<uint8_t*>(tile);  // superchunk codec: the warp's record staging area
   auto issue_prefetch = [&](RawItem it) {
     pf = RawItem{-1, -1};
     if (!prefetch_ok || it.s < 0 || !vec_ok || it.blk == tail_block) return;
@@ -216,6 +223,58 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
       const long long e0 = static_cast<long long>(blk) * kBlock;
       const int valid = static_cast<int>(min(static_cast<long long>(kBlock), p.n - e0));
       float v[32];
+      if constexpr (SC) {
+        // ---- hierarchical superchunk codec: no rotation, records of 4 superchunks per block ----
+        constexpr unsigned kBB = ScGeom<SCB>::kBlockBytes;
+        const unsigned long long boff = static_cast<unsigned long long>(bs) * kBB;
+        const uint32_t first_call = static_cast<uint32_t>(blk) * 64u;  // Philox call index = element / 16
+        if (out != kOutDecode) {
+          if (local == kLocalRaw) sc_load_block<T>(bucket + e0, valid, vec_ok, lane, v);
+          else if (blk == tail_block) sc_load_block<float>(p.tail_ws, kBlock, true, lane, v);
+          else sc_load_block<T>(bucket + e0, kBlock, vec_ok, lane, v);
+          for (int r = 0; r < nrecv; ++r) {
+            const uint8_t* slot = my_mail + static_cast<unsigned long long>(recv_slot + r) * p.slot_stride;
+            sc_copy_in<SCB>(rec_tile, slot + boff, lane);
+            __syncwarp();
+            sc_decode_block<SCB, MEE, true>(v, rec_tile, scp, lane);
+            __syncwarp();
+          }
+        }
+        if (out == kOutStore) {
+          if (blk == tail_block) sc_store_block<float>(p.tail_ws, kBlock, true, lane, v);
+          else sc_store_block<T>(bucket + e0, kBlock, vec_ok, lane, v);
+        } else if (out == kOutSend) {
+          sc_encode_block<SCB, MEE>(v, rec_tile, scp, first_call, tag, p.step, p.seed_lo, p.seed_hi, lane);
+          __syncwarp();
+          if (!p.no_transmit)
+            sc_copy_out<SCB>(p.mail[dst] + static_cast<unsigned long long>(send_slot) * p.slot_stride + boff, rec_tile,
+                             lane);
+          __syncwarp();
+        } else {
+          if (out == kOutFinal) {
+            sc_encode_block<SCB, MEE>(v, rec_tile, scp, first_call, tag, p.step, p.seed_lo, p.seed_hi, lane);
+            __syncwarp();
+            if (!p.no_transmit) {
+              for (int peer = 0; peer < p.world; ++peer) {
+                if (peer == p.rank) continue;
+                sc_copy_out<SCB>(p.mail[peer] + static_cast<unsigned long long>(send_slot) * p.slot_stride + boff,
+                                 rec_tile, lane);
+              }
+            }
+          } else {
+            const uint8_t* slot = my_mail + static_cast<unsigned long long>(recv_slot) * p.slot_stride;
+            sc_copy_in<SCB>(rec_tile, slot + boff, lane);
+            __syncwarp();
+          }
+          sc_decode_block<SCB, MEE, false>(v, rec_tile, scp, lane);
+          __syncwarp();
+          const float wf = static_cast<float>(p.world);
+#pragma unroll
+          for (int k = 0; k < 32; ++k) v[k] = __fdiv_rn(v[k], wf);
+          sc_store_block<T>(bucket + e0, valid, vec_ok, lane, v);
+        }
+        continue;
+      }
       uint32_t w[BITS];
       float scale = 0.f;
 
@@ -343,28 +402,29 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
   }
 }
 
-template <int BITS, typename T, bool TC>
+template <int BITS, typename T, int CODEC>
 __global__ void __launch_bounds__(512, 1) fused_allreduce_kernel(const __grid_constant__ ARParams p) {
-  fused_allreduce_body<BITS, T, TC>(p);
+  fused_allreduce_body<BITS, T, CODEC>(p);
 }
 
 // Several ranks in one launch on one GPU (blockIdx.y = rank): the single-GPU form of the
 // collective used by the standalone codec ops and by tests.  Cooperative, so that CTAs that
 // wait on one another are co-resident.
-template <int BITS, typename T, bool TC>
+template <int BITS, typename T, int CODEC>
 __global__ void __launch_bounds__(512, 1) fused_allreduce_multi_kernel(const ARParams* __restrict__ plist) {
-  fused_allreduce_body<BITS, T, TC>(plist[blockIdx.y]);
+  fused_allreduce_body<BITS, T, CODEC>(plist[blockIdx.y]);
 }
 
-template <int BITS, typename T, bool TC>
+template <int BITS, typename T, int CODEC>
 void launch_one(const ARParams* host_params, const ARParams* dev_params, int nranks, int ctas, int threads,
                 cudaStream_t stream) {
+  constexpr bool TC = CODEC == kCodecRhtTc;
   TORCH_CHECK(!TC || threads == 128 || threads == 256 || threads == 512,
               "the tensor-core rotation needs 1, 2 or 4 whole warpgroups (128, 256 or 512 threads): TMEM columns are "
               "allocated in powers of two");
   const size_t smem = fused_smem_bytes<TC>(threads);
-  const void* fn = nranks == 1 ? reinterpret_cast<const void*>(&fused_allreduce_kernel<BITS, T, TC>)
-                               : reinterpret_cast<const void*>(&fused_allreduce_multi_kernel<BITS, T, TC>);
+  const void* fn = nranks == 1 ? reinterpret_cast<const void*>(&fused_allreduce_kernel<BITS, T, CODEC>)
+                               : reinterpret_cast<const void*>(&fused_allreduce_multi_kernel<BITS, T, CODEC>);
   // attribute and occupancy are queried once per (kernel, device, block size) and cached
   struct Cache {
     int dev = -1, threads = -1, capacity = 0;
@@ -394,9 +454,15 @@ void launch_one(const ARParams* host_params, const ARParams* dev_params, int nra
 
 
 #define DQ_INSTANTIATE_FUSED_ALLREDUCE(BITS)                                                                   \
-  template void launch_one<BITS, float, false>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);         \
-  template void launch_one<BITS, __nv_bfloat16, false>(const ARParams*, const ARParams*, int, int, int, cudaStream_t); \
-  template void launch_one<BITS, float, true>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);          \
-  template void launch_one<BITS, __nv_bfloat16, true>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);
+  template void launch_one<BITS, float, kCodecRht>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);           \
+  template void launch_one<BITS, __nv_bfloat16, kCodecRht>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);   \
+  template void launch_one<BITS, float, kCodecRhtTc>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);         \
+  template void launch_one<BITS, __nv_bfloat16, kCodecRhtTc>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);
+
+#define DQ_INSTANTIATE_FUSED_ALLREDUCE_SC(BITS)                                                                         \
+  template void launch_one<BITS, float, kCodecScAee>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);         \
+  template void launch_one<BITS, __nv_bfloat16, kCodecScAee>(const ARParams*, const ARParams*, int, int, int, cudaStream_t); \
+  template void launch_one<BITS, float, kCodecScMee>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);         \
+  template void launch_one<BITS, __nv_bfloat16, kCodecScMee>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);
 
 }  // namespace dq

@@ -344,7 +344,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> norm_bwd(at::Tensor dy, at::Tenso
 #undef DQ_ROWS_NC
 #undef DQ_ROWS
     C10_CUDA_KERNEL_LAUNCH_CHECK();
-    dim3 rb(32, 8);
+    dim3 rb(32, 32);
     reduce_parts2_kernel<<<(H + 31) / 32, rb, 0, stream>>>(dw_part.data_ptr<float>(), dw.data_ptr<float>(), nparts, H);
     if (!rms) reduce_parts2_kernel<<<(H + 31) / 32, rb, 0, stream>>>(db_part.data_ptr<float>(), db.data_ptr<float>(), nparts, H);
     C10_CUDA_KERNEL_LAUNCH_CHECK();

@@ -91,7 +91,7 @@ extern "C" int dq_rmsnorm_bwd_noalloc(const void* dy, const void* x, const float
   const int nchunk = (hidden + 255) / 256;
   if (is_bf16) launch_rows_nc<__nv_bfloat16>(nchunk, dy, x, w, rstd, dx, parts, rows, hidden, grid, stream);
   else launch_rows_nc<float>(nchunk, dy, x, w, rstd, dx, parts, rows, hidden, grid, stream);
-  dim3 rb(32, 8);
+  dim3 rb(32, 32);
   reduce_parts2_kernel<<<(hidden + 31) / 32, rb, 0, stream>>>(parts, dw, nparts, hidden);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {

@@ -136,24 +136,24 @@ __global__ void __launch_bounds__(kNormWarps * 32) norm_bwd_rows_kernel(
   }
 }
 
-// out[c] = sum over parts; 8 row-groups per CTA combined through shared memory in a fixed order
-static __global__ void __launch_bounds__(256) reduce_parts2_kernel(const float* __restrict__ part, float* __restrict__ out,
-                                                            int nparts, int H) {
-  __shared__ float sm[8][32];
+// out[c] = sum over parts; 32 row-groups per CTA (block 32 x 32) combined through shared memory in a
+// fixed order, so the result does not depend on scheduling
+static __global__ void __launch_bounds__(1024) reduce_parts2_kernel(const float* __restrict__ part,
+                                                                    float* __restrict__ out, int nparts, int H) {
+  __shared__ float sm[32][33];
   const int c = blockIdx.x * 32 + threadIdx.x, g = threadIdx.y;
   float s = 0.f;
   if (c < H)
-    for (int p = g; p < nparts; p += 8) s += part[static_cast<size_t>(p) * H + c];
+    for (int p = g; p < nparts; p += 32) s += part[static_cast<size_t>(p) * H + c];
   sm[g][threadIdx.x] = s;
   __syncthreads();
   if (g == 0 && c < H) {
     float t = 0.f;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) t += sm[k][threadIdx.x];
+    for (int k = 0; k < 32; ++k) t += sm[k][threadIdx.x];
     out[c] = t;
   }
 }
-
 
 }  // namespace normk
 }  // namespace dq

@@ -36,13 +36,24 @@ def _align(x: int, a: int) -> int:
     return (x + a - 1) // a * a
 
 
+CODECS = {"rht": 0, "rht_tc": 1, "sc_aee": 2, "sc_mee": 3}
+
+
+def block_bytes(bits: int, codec: str = "rht") -> int:
+    """Bytes of one encoded 1024-element block inside a message (scales of the rht codec excluded)."""
+    if codec.startswith("sc_"):
+        return 4 * (16 * (2 * bits + 1) + 2)
+    return 128 * bits
+
+
 @dataclasses.dataclass(frozen=True)
 class Layout:
-    """Geometry of one collective's slots for (numel, world, bits)."""
+    """Geometry of one collective's slots for (numel, world, bits, codec)."""
 
     numel: int
     world: int
     bits: int
+    codec: str = "rht"
 
     @property
     def nblocks(self) -> int:
@@ -54,11 +65,12 @@ class Layout:
 
     @property
     def scales_off(self) -> int:
-        return _align(self.blocks_per_shard * 128 * self.bits, 16)
+        return _align(self.blocks_per_shard * block_bytes(self.bits, self.codec), 16)
 
     @property
     def slot_stride(self) -> int:
-        return _align(self.scales_off + 4 * self.blocks_per_shard, 256)
+        scales = 0 if self.codec.startswith("sc_") else 4 * self.blocks_per_shard
+        return _align(self.scales_off + scales, 256)
 
 
 def program_tensor(rank: int, world: int, topology: str, correlated: bool = False) -> torch.Tensor:
@@ -71,6 +83,25 @@ def _rotation_flag(rotation: str) -> bool:
     if rotation not in ("simt", "tc"):
         raise ValueError("rotation must be 'simt' or 'tc'")
     return rotation == "tc"
+
+
+_SC_CACHE: Dict[tuple, tuple] = {}
+
+
+def codec_args(codec: str, bits: int, device) -> tuple:
+    """(codec id, lattice_max, c1, c2, lut) as the native operators take them."""
+    if codec in ("rht", "rht_tc"):
+        return CODECS[codec], 0.0, 0.0, 0.0, None
+    key = (codec, bits, str(device))
+    if key not in _SC_CACHE:
+        from .codecs import SuperchunkCodec, mee_lattice
+
+        c = SuperchunkCodec(bits, codec[3:])
+        lut = None
+        if codec == "sc_mee":
+            lut = mee_lattice(torch.arange(1 << bits, dtype=torch.float32) - c.R, c.eps).to(device).contiguous()
+        _SC_CACHE[key] = (CODECS[codec], float(c.lattice_max), float(c.c1), float(c.c2), lut)
+    return _SC_CACHE[key]
 
 
 STATUS_MESSAGES = {1: "timed out waiting for a peer's flag", 2: "malformed step program",
@@ -112,7 +143,7 @@ class FusedAllreduce:
             self.buf.close()
         self.max_numel = int(max_numel)
         self.nslots = sch.n_slots(self.world, "ring")  # same count for every topology
-        worst = Layout(self.max_numel, self.world, 8)
+        worst = Layout(self.max_numel, self.world, 8, "sc_aee")  # the largest message: 8-bit superchunk records
         self.set_bytes = _align(self.nslots * worst.slot_stride, 4096)
         self.flag_words_per_set = self.nslots * self.ctas
         self.off_flags = 2 * self.set_bytes
@@ -135,12 +166,17 @@ class FusedAllreduce:
 
     # -- the collective --------------------------------------------------------------------
     def allreduce_(self, bucket: torch.Tensor, bits: int, topology: str = "ring", seed: int = 0, step: int = 0,
-                   bucket_id: int = 0, no_transmit: bool = False, correlated: bool = False) -> torch.Tensor:
-        """In-place mean all-reduce of a flat fp32/bf16 CUDA tensor on the current stream."""
+                   bucket_id: int = 0, no_transmit: bool = False, correlated: bool = False,
+                   codec: Optional[str] = None) -> torch.Tensor:
+        """In-place mean all-reduce of a flat fp32/bf16 CUDA tensor on the current stream.
+
+        `codec`: None (the engine's rotation codec), "sc_aee" or "sc_mee" (the hierarchical
+        superchunk codec with 2 / 4 / 8-bit codes)."""
         if self.world == 1:
             return bucket
+        codec = codec or ("rht_tc" if self.tensor_rotation else "rht")
         self.ensure_capacity(bucket.numel())
-        lay = Layout(bucket.numel(), self.world, bits)
+        lay = Layout(bucket.numel(), self.world, bits, codec)
         self.epoch += 1
         parity = self.epoch & 1
         mail = [p + parity * self.set_bytes for p in self.buf.ptrs]
@@ -150,7 +186,7 @@ class FusedAllreduce:
             self.buf.local_ptr + self.off_status, self.buf.local_ptr + self.off_tail, self.rank, self.world, bits,
             self.ctas, self.threads, lay.blocks_per_shard, lay.slot_stride, lay.scales_off,
             parity * self.flag_words_per_set, self.epoch, seed, step, bucket_id, 1.0 / self.world, self.timeout_ns,
-            no_transmit, self.tensor_rotation)
+            no_transmit, *codec_args(codec, bits, bucket.device))
         counters.add("fused_allreduce")
         return bucket
 
@@ -182,7 +218,7 @@ class LocalCluster:
         self.device = torch.device(device)
         self.timeout_ns = timeout_ms * 1_000_000
         self.nslots = sch.n_slots(world, "ring")
-        worst = Layout(max_numel, world, 8)
+        worst = Layout(max_numel, world, 8, "sc_aee")
         self.max_numel = max_numel
         self.mailbox_bytes = self.nslots * worst.slot_stride
         self.mail = [torch.zeros(self.mailbox_bytes, dtype=torch.uint8, device=self.device) for _ in range(world)]
@@ -193,8 +229,9 @@ class LocalCluster:
 
     def run(self, buckets: List[torch.Tensor], programs: torch.Tensor, bits: int, seed: int = 0, step: int = 0,
             bucket_id: int = 0, post_scale: Optional[float] = None, no_transmit: bool = False,
-            preset_flags: bool = False) -> None:
-        lay = Layout(buckets[0].numel(), self.world, bits)
+            preset_flags: bool = False, codec: Optional[str] = None) -> None:
+        codec = codec or ("rht_tc" if self.tensor_rotation else "rht")
+        lay = Layout(buckets[0].numel(), self.world, bits, codec)
         assert buckets[0].numel() <= self.max_numel
         self.epoch += 1
         if preset_flags:
@@ -204,7 +241,7 @@ class LocalCluster:
             buckets, programs, self.mail, self.flags, self.status, self.tail_ws, self.nslots, bits, self.ctas,
             self.threads, lay.blocks_per_shard, lay.slot_stride, lay.scales_off, 0, self.epoch, seed, step, bucket_id,
             (1.0 / self.world) if post_scale is None else post_scale, self.timeout_ns, no_transmit,
-            self.tensor_rotation)
+            *codec_args(codec, bits, buckets[0].device))
 
     def allreduce_(self, buckets: List[torch.Tensor], bits: int, topology: str = "ring", correlated: bool = False,
                    **kw) -> List[torch.Tensor]:
@@ -217,6 +254,11 @@ class LocalCluster:
         if msg is not None:
             self.status.zero_()
             raise CollectiveTimeout(msg)
+
+    def slot_bytes(self, rank: int, slot: int, lay: Layout, nblocks: int) -> torch.Tensor:
+        """The encoded blocks of one received message as raw bytes [nblocks * block_bytes]."""
+        base = slot * lay.slot_stride
+        return self.mail[rank][base: base + nblocks * block_bytes(lay.bits, lay.codec)]
 
     def slot(self, rank: int, slot: int, lay: Layout, nblocks: int) -> Tuple[torch.Tensor, torch.Tensor]:
         """(code words [nblocks, bits, 32] int32, scales [nblocks] fp32) of one received message."""

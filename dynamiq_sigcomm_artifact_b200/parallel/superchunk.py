@@ -12,8 +12,11 @@ Per bucket (testbed_evaluation/new_comm_hooks/comm_hooks.py:681-780, dynamic-bit
    codec of that width over the method's topology, scatter them back;
 5. add the mean of means back (K22, cuda_hadamard.cu:1351-1369).
 
-This implementation runs on the device-agnostic backend (``torch_backend.py``), so it works
-under gloo on CPU and under NCCL point-to-point on GPUs.
+On CUDA buckets steps 1, 4 and 5 are native: ``torch.ops.dq.superchunk_center`` /
+``superchunk_add_mean`` (csrc/kernels/superchunk_ops.cu) and, per group, the persistent fused
+collective kernel with its superchunk codec (``FusedAllreduce.allreduce_(codec="sc_aee" | "sc_mee")``,
+csrc/common/sc_codec.cuh) over peer-mapped NVLink memory.  On CPU tensors (gloo) the same steps run
+on the device-agnostic backend (``torch_backend.py``).
 """
 from __future__ import annotations
 
@@ -54,7 +57,19 @@ def superchunk_allreduce(state, bucket) -> torch.futures.Future:
         fut.set_result(buf)
         return fut
     step, index = int(state["batch_idx"]), bucket.index()
-    resid, stats = mean_center(buf, world)
+    native = buf.is_cuda
+    if native:
+        from .. import ops as _ops
+        from ..hooks import _engine
+        from ..utils import counters
+
+        dq = _ops.require()
+        eng = _engine(state)
+        flat, stats = dq.superchunk_center(buf.reshape(-1), world)
+        counters.add("superchunk_center")
+        resid = flat.view(-1, SUPERCHUNK)
+    else:
+        resid, stats = mean_center(buf, world)
     dist.all_reduce(stats, group=group)
     mean_of_means, energy = stats[:, 0], stats[:, 1]
     params = state["params"]
@@ -80,14 +95,22 @@ def superchunk_allreduce(state, bucket) -> torch.futures.Future:
         rows = resid.index_select(0, idx).reshape(-1)
         if spec.no_compress:
             rows = rows / world
+        elif native:
+            eng.ensure_capacity(rows.numel())
+            eng.allreduce_(rows, bits, spec.topology, cfg.seed, step, (index << 2) | gid,
+                           no_transmit=spec.compute_only, codec=f"sc_{spec.lattice}")
         else:
             codec = SuperchunkCodec(bits, spec.lattice, cfg.seed, step, (index << 2) | gid)
             rows = allreduce_torch(rows, codec, spec.topology, group, transmit=not spec.compute_only)
         resid.index_copy_(0, idx, rows.view(-1, SUPERCHUNK))
     if not bool(done.all()):  # rows of a dropped group keep their local share, as in the reference
         resid[~done] /= world
-    out = (resid + mean_of_means.unsqueeze(1)).reshape(-1)[:n]
-    buf.copy_(out.to(buf.dtype))
+    if native:
+        dq.superchunk_add_mean(resid.reshape(-1), mean_of_means.contiguous(), buf.reshape(-1))
+        counters.add("superchunk_add_mean")
+    else:
+        out = (resid + mean_of_means.unsqueeze(1)).reshape(-1)[:n]
+        buf.copy_(out.to(buf.dtype))
     if spec.dynamic_bitrate and bucket.is_last():
         ctl = params["bitrate"]
         ctl.end_of_step()
