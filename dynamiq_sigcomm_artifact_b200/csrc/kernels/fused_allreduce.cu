@@ -58,7 +58,18 @@ static void launch_sc(int bits, const ARParams* hp, const ARParams* dp, int nran
   }
 }
 
-// `codec`: kCodecRht (SIMT rotation), kCodecRhtTc (tcgen05 rotation), kCodecScAee, kCodecScMee
+template <typename T>
+static void launch_mx(int bits, const ARParams* hp, const ARParams* dp, int nranks, int ctas, int threads,
+                      cudaStream_t stream) {
+  switch (bits) {
+    case 4: launch_one<4, T, kCodecMx>(hp, dp, nranks, ctas, threads, stream); break;
+    case 6: launch_one<6, T, kCodecMx>(hp, dp, nranks, ctas, threads, stream); break;
+    case 8: launch_one<8, T, kCodecMx>(hp, dp, nranks, ctas, threads, stream); break;
+    default: TORCH_CHECK(false, "the block-float codec has 4, 6 and 8 bit codes, got ", bits);
+  }
+}
+
+// `codec`: kCodecRht (SIMT rotation), kCodecRhtTc (tcgen05 rotation), kCodecScAee, kCodecScMee, kCodecMx
 template <typename T>
 static void launch_bits(int bits, const ARParams* hp, const ARParams* dp, int nranks, int ctas, int threads,
                         cudaStream_t stream, int codec) {
@@ -67,12 +78,14 @@ static void launch_bits(int bits, const ARParams* hp, const ARParams* dp, int nr
     case kCodecRhtTc: launch_rht<T, kCodecRhtTc>(bits, hp, dp, nranks, ctas, threads, stream); break;
     case kCodecScAee: launch_sc<T, kCodecScAee>(bits, hp, dp, nranks, ctas, threads, stream); break;
     case kCodecScMee: launch_sc<T, kCodecScMee>(bits, hp, dp, nranks, ctas, threads, stream); break;
+    case kCodecMx: launch_mx<T>(bits, hp, dp, nranks, ctas, threads, stream); break;
     default: TORCH_CHECK(false, "unknown codec ", codec);
   }
 }
 
 static unsigned block_bytes_of(int codec, int bits) {
   if (codec == kCodecScAee || codec == kCodecScMee) return 4u * (16u * (2u * bits + 1u) + 2u);
+  if (codec == kCodecMx) return 128u * bits + 32u;
   return 128u * bits;
 }
 

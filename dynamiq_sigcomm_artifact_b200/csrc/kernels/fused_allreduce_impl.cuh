@@ -8,6 +8,7 @@
 #include "../common/rht_codec.cuh"
 #include "../common/rht_tc.cuh"
 #include "../common/sc_codec.cuh"
+#include "../common/mx_codec.cuh"
 #include "fused_allreduce.cuh"
 
 namespace dq {
@@ -93,9 +94,11 @@ __host__ __device__ constexpr size_t fused_smem_bytes(int threads) {
 template <int BITS, typename T, int CODEC>
 __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
   constexpr bool TC = CODEC == kCodecRhtTc;
-  constexpr bool SC = CODEC == kCodecScAee || CODEC == kCodecScMee;
+  constexpr bool MX = CODEC == kCodecMx;  // block-float codes (8 / 6 / 4 bit) with native conversions
+  constexpr bool SC = CODEC == kCodecScAee || CODEC == kCodecScMee || MX;  // lane-contiguous record codecs
   constexpr bool MEE = CODEC == kCodecScMee;
   constexpr int SCB = (BITS == 2 || BITS == 4 || BITS == 8) ? BITS : 4;  // superchunk code width (2, 4, 8 only)
+  constexpr int MXB = (BITS == 4 || BITS == 6 || BITS == 8) ? BITS : 8;  // block-float code width (4, 6, 8 only)
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
   const int cta = blockIdx.x, G = gridDim.x;
@@ -224,19 +227,33 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
       const int valid = static_cast<int>(min(static_cast<long long>(kBlock), p.n - e0));
       float v[32];
       if constexpr (SC) {
-        // ---- hierarchical superchunk codec: no rotation, records of 4 superchunks per block ----
-        constexpr unsigned kBB = ScGeom<SCB>::kBlockBytes;
+        // ---- record codecs (superchunk AEE / MEE, block-float): no rotation, one record area per block ----
+        constexpr unsigned kBB = MX ? MxGeom<MXB>::kBlockBytes : ScGeom<SCB>::kBlockBytes;
         const unsigned long long boff = static_cast<unsigned long long>(bs) * kBB;
         const uint32_t first_call = static_cast<uint32_t>(blk) * 64u;  // Philox call index = element / 16
+        auto rec_in = [&](const uint8_t* src) {
+          if constexpr (MX) mx_copy_in<MXB>(rec_tile, src, lane);
+          else sc_copy_in<SCB>(rec_tile, src, lane);
+          __syncwarp();
+        };
+        auto rec_out = [&](uint8_t* dstp) {
+          if constexpr (MX) mx_copy_out<MXB>(dstp, rec_tile, lane);
+          else sc_copy_out<SCB>(dstp, rec_tile, lane);
+        };
+        auto rec_encode = [&]() {
+          if constexpr (MX) mx_encode_block<MXB>(v, rec_tile, lane);
+          else sc_encode_block<SCB, MEE>(v, rec_tile, scp, first_call, tag, p.step, p.seed_lo, p.seed_hi, lane);
+          __syncwarp();
+        };
         if (out != kOutDecode) {
           if (local == kLocalRaw) sc_load_block<T>(bucket + e0, valid, vec_ok, lane, v);
           else if (blk == tail_block) sc_load_block<float>(p.tail_ws, kBlock, true, lane, v);
           else sc_load_block<T>(bucket + e0, kBlock, vec_ok, lane, v);
           for (int r = 0; r < nrecv; ++r) {
             const uint8_t* slot = my_mail + static_cast<unsigned long long>(recv_slot + r) * p.slot_stride;
-            sc_copy_in<SCB>(rec_tile, slot + boff, lane);
-            __syncwarp();
-            sc_decode_block<SCB, MEE, true>(v, rec_tile, scp, lane);
+            rec_in(slot + boff);
+            if constexpr (MX) mx_decode_block<MXB, true>(v, rec_tile, lane);
+            else sc_decode_block<SCB, MEE, true>(v, rec_tile, scp, lane);
             __syncwarp();
           }
         }
@@ -244,29 +261,23 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
           if (blk == tail_block) sc_store_block<float>(p.tail_ws, kBlock, true, lane, v);
           else sc_store_block<T>(bucket + e0, kBlock, vec_ok, lane, v);
         } else if (out == kOutSend) {
-          sc_encode_block<SCB, MEE>(v, rec_tile, scp, first_call, tag, p.step, p.seed_lo, p.seed_hi, lane);
-          __syncwarp();
-          if (!p.no_transmit)
-            sc_copy_out<SCB>(p.mail[dst] + static_cast<unsigned long long>(send_slot) * p.slot_stride + boff, rec_tile,
-                             lane);
+          rec_encode();
+          if (!p.no_transmit) rec_out(p.mail[dst] + static_cast<unsigned long long>(send_slot) * p.slot_stride + boff);
           __syncwarp();
         } else {
           if (out == kOutFinal) {
-            sc_encode_block<SCB, MEE>(v, rec_tile, scp, first_call, tag, p.step, p.seed_lo, p.seed_hi, lane);
-            __syncwarp();
+            rec_encode();
             if (!p.no_transmit) {
               for (int peer = 0; peer < p.world; ++peer) {
                 if (peer == p.rank) continue;
-                sc_copy_out<SCB>(p.mail[peer] + static_cast<unsigned long long>(send_slot) * p.slot_stride + boff,
-                                 rec_tile, lane);
+                rec_out(p.mail[peer] + static_cast<unsigned long long>(send_slot) * p.slot_stride + boff);
               }
             }
           } else {
-            const uint8_t* slot = my_mail + static_cast<unsigned long long>(recv_slot) * p.slot_stride;
-            sc_copy_in<SCB>(rec_tile, slot + boff, lane);
-            __syncwarp();
+            rec_in(my_mail + static_cast<unsigned long long>(recv_slot) * p.slot_stride + boff);
           }
-          sc_decode_block<SCB, MEE, false>(v, rec_tile, scp, lane);
+          if constexpr (MX) mx_decode_block<MXB, false>(v, rec_tile, lane);
+          else sc_decode_block<SCB, MEE, false>(v, rec_tile, scp, lane);
           __syncwarp();
           const float wf = static_cast<float>(p.world);
 #pragma unroll
@@ -458,6 +469,10 @@ void launch_one(const ARParams* host_params, const ARParams* dev_params, int nra
   template void launch_one<BITS, __nv_bfloat16, kCodecRht>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);   \
   template void launch_one<BITS, float, kCodecRhtTc>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);         \
   template void launch_one<BITS, __nv_bfloat16, kCodecRhtTc>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);
+
+#define DQ_INSTANTIATE_FUSED_ALLREDUCE_MX(BITS)                                                                         \
+  template void launch_one<BITS, float, kCodecMx>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);           \
+  template void launch_one<BITS, __nv_bfloat16, kCodecMx>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);
 
 #define DQ_INSTANTIATE_FUSED_ALLREDUCE_SC(BITS)                                                                         \
   template void launch_one<BITS, float, kCodecScAee>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);         \

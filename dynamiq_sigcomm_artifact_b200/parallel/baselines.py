@@ -48,8 +48,19 @@ def _block_float_hook(fmt_of):
         if fmt == "zero":  # traffic-free debug mode: every rank keeps its own share
             buf.div_(world)
             return _done(buf)
-        out = allreduce_torch(buf, BlockFloatCodec(fmt), state["spec"].topology, state["group"],
-                              transmit=not state["spec"].compute_only)
+        spec = state["spec"]
+        if buf.is_cuda and buf.dtype in (torch.float32, torch.bfloat16):
+            # fused kernel: native E4M3 / E3M2 / E2M1 conversions, peer stores over NVLink
+            from ..hooks import _engine
+
+            eng = _engine(state)
+            eng.ensure_capacity(buf.numel())
+            width = {"fp8": 8, "fp6": 6, "fp4": 4}[fmt]
+            eng.allreduce_(buf.reshape(-1), width, spec.topology, state["config"].seed, int(state["batch_idx"]),
+                           bucket.index(), no_transmit=spec.compute_only, codec="mx")
+            return _done(buf)
+        out = allreduce_torch(buf, BlockFloatCodec(fmt), spec.topology, state["group"],
+                              transmit=not spec.compute_only)
         buf.copy_(out.to(buf.dtype))
         return _done(buf)
 

@@ -136,20 +136,23 @@ _FORMATS = {  # name: (exponent bits, mantissa bits, largest finite magnitude)
 
 
 def _round_to_minifloat(x: torch.Tensor, ebits: int, mbits: int, vmax: float) -> torch.Tensor:
-    """Round-to-nearest-even onto the (ebits, mbits) grid with subnormals, saturating at vmax."""
+    """Round-to-nearest-even onto the (ebits, mbits) grid with subnormals, saturating at vmax
+    (what ``cvt.rn.satfinite`` does on the device).  Exponents come from ``frexp``: exact."""
     bias = (1 << (ebits - 1)) - 1
     ax = x.abs().clamp_max(vmax)
-    e = torch.floor(torch.log2(ax.clamp_min(1e-38))).clamp_min(1 - bias)
-    step = torch.pow(torch.tensor(2.0, device=x.device), e - mbits)
+    e = (torch.frexp(ax.clamp_min(1e-38)).exponent - 1).clamp_min(1 - bias)  # floor(log2 |x|), at least emin
+    step = torch.ldexp(torch.ones_like(ax), e - mbits)
     return torch.sign(x) * torch.round(ax / step) * step
 
 
 class BlockFloatCodec(TorchCodec):
-    """32-value blocks: one E8M0 scale byte + 32 minifloat codes (8, 6 or 4 bits each).
+    """MXFP8 (E4M3) / FP6 (E3M2) / FP4 (E2M1): 32-value blocks with one power-of-two scale byte.
 
-    Codes are stored as the index of the value in the format's sorted table, so any of the three
-    formats shares the same packing code; the wire size is exactly 8.25 / 6.25 / 4.25 bit per
-    element, the figures the reference's bandwidth emulation uses (comm_hooks.py:239-241).
+    Layout, shared with the fused kernel (csrc/common/mx_codec.cuh): per 1024 values, 32 lanes x 4 w
+    code bytes (the 32 codes of a lane as a little-endian stream of w-bit codes, a code being the
+    format's sign | exponent | mantissa bit pattern), then the 32 scale bytes (biased exponent of the
+    scale).  8.25 / 6.25 / 4.25 bit per value - the figures the reference's bandwidth emulation charges
+    (comm_hooks.py:239-241).
     """
 
     BLOCK = 32
@@ -158,7 +161,7 @@ class BlockFloatCodec(TorchCodec):
         self.fmt = fmt
         self.ebits, self.mbits, self.vmax = _FORMATS[fmt]
         self.width = 1 + self.ebits + self.mbits
-        self.align = 32 * 8  # keeps every message a whole number of bytes for 6-bit codes
+        self.align = 1024
         mags = [0.0]
         bias = (1 << (self.ebits - 1)) - 1
         for e in range(1 << self.ebits):
@@ -166,11 +169,14 @@ class BlockFloatCodec(TorchCodec):
                 val = (m / (1 << self.mbits)) * 2.0 ** (1 - bias) if e == 0 else (1 + m / (1 << self.mbits)) * 2.0 ** (e - bias)
                 if 0 < val <= self.vmax:
                     mags.append(val)
+        # sorted magnitudes: the index of a magnitude is its exponent | mantissa bit pattern
         self.table = torch.tensor(sorted(set(mags)), dtype=torch.float32)
 
+    def block_bytes(self) -> int:
+        return 128 * self.width + 32
+
     def message_bytes(self, numel: int) -> int:
-        nb = (numel + self.BLOCK - 1) // self.BLOCK
-        return nb + (nb * self.BLOCK * self.width + 7) // 8
+        return (numel + 1023) // 1024 * self.block_bytes()
 
     def _table(self, device):
         if self.table.device != device:
@@ -178,37 +184,38 @@ class BlockFloatCodec(TorchCodec):
         return self.table
 
     def encode(self, v, first, tag):
-        n = v.numel()
-        nb = (n + self.BLOCK - 1) // self.BLOCK
-        x = torch.zeros(nb * self.BLOCK, dtype=torch.float32, device=v.device)
+        n, w = v.numel(), self.width
+        nblk = (n + 1023) // 1024
+        x = torch.zeros(nblk * 1024, dtype=torch.float32, device=v.device)
         x[:n] = torch.nan_to_num(v.float(), nan=0.0, posinf=0.0, neginf=0.0)
-        x = x.reshape(nb, self.BLOCK)
-        amax = x.abs().amax(dim=1).clamp_min(1e-38)
-        e = torch.ceil(torch.log2(amax / self.vmax)).clamp_(-127, 127)  # power-of-two block scale
-        y = _round_to_minifloat(x / torch.pow(torch.tensor(2.0, device=v.device), e).unsqueeze(1), self.ebits,
-                                self.mbits, self.vmax)
+        x = x.reshape(nblk, 32, 32)  # [block, lane, value]
+        amax = x.abs().amax(dim=2)
+        r = amax / torch.tensor(self.vmax, dtype=torch.float32, device=v.device)
+        fr = torch.frexp(r.clamp_min(1e-38))
+        e = torch.where(fr.mantissa > 0.5, fr.exponent, fr.exponent - 1).clamp(-127, 127)  # ceil(log2 r), exact
+        e = torch.where(amax >= 1e-30, e, torch.full_like(e, -127))
+        y = _round_to_minifloat(torch.ldexp(x, -e.unsqueeze(2)), self.ebits, self.mbits, self.vmax)
         t = self._table(v.device)
-        idx = torch.bucketize(y.abs(), t).clamp_max(t.numel() - 1)
-        # bucketize returns the first entry >= |y|; |y| is on the grid, so that entry is |y| itself
-        code = (idx | ((y < 0).long() << (self.width - 1))).to(torch.int64).reshape(-1)
-        nbits = code.numel() * self.width
-        bits = ((code.unsqueeze(1) >> torch.arange(self.width, device=v.device)) & 1).to(torch.uint8).reshape(-1)
-        pad = (-nbits) % 8
-        if pad:
-            bits = torch.cat([bits, torch.zeros(pad, dtype=torch.uint8, device=v.device)])
+        idx = torch.bucketize(y.abs(), t).clamp_max(t.numel() - 1)  # |y| is on the grid: first entry >= |y| is |y|
+        code = (idx | ((y < 0) | ((y == 0) & torch.signbit(y))).long() << (w - 1)).to(torch.int64)
+        bits = ((code.unsqueeze(3) >> torch.arange(w, device=v.device)) & 1).to(torch.uint8)  # [blk, lane, value, w]
+        bits = bits.reshape(nblk, 32, 32 * w // 8, 8)
         weights = (1 << torch.arange(8, device=v.device)).to(torch.uint8)
-        payload = (bits.reshape(-1, 8) * weights).sum(dim=1).to(torch.uint8)
-        return torch.cat([(e + 127).to(torch.uint8), payload])
+        payload = (bits * weights).sum(dim=3).to(torch.uint8).reshape(nblk, 32 * 4 * w)
+        scales = (e + 127).to(torch.uint8)
+        return torch.cat([payload, scales], dim=1).reshape(-1)
 
     def decode(self, msg, numel):
-        nb = (numel + self.BLOCK - 1) // self.BLOCK
-        e = msg[:nb].float() - 127.0
-        payload = msg[nb:]
-        bits = ((payload.unsqueeze(1) >> torch.arange(8, device=msg.device)) & 1).reshape(-1)[: nb * self.BLOCK * self.width]
-        code = (bits.reshape(-1, self.width).long() << torch.arange(self.width, device=msg.device)).sum(dim=1)
-        sign = 1.0 - 2.0 * ((code >> (self.width - 1)) & 1).float()
-        mag = self._table(msg.device)[(code & ((1 << (self.width - 1)) - 1)).clamp_max(self.table.numel() - 1)]
-        y = (sign * mag).reshape(nb, self.BLOCK) * torch.pow(torch.tensor(2.0, device=msg.device), e).unsqueeze(1)
+        w = self.width
+        nblk = (numel + 1023) // 1024
+        m = msg.reshape(nblk, self.block_bytes())
+        payload = m[:, : 128 * w].reshape(nblk, 32, 4 * w)
+        e = m[:, 128 * w:].to(torch.int32) - 127
+        bits = ((payload.unsqueeze(3) >> torch.arange(8, device=msg.device)) & 1).reshape(nblk, 32, 32, w)
+        code = (bits.long() << torch.arange(w, device=msg.device)).sum(dim=3)
+        sign = 1.0 - 2.0 * ((code >> (w - 1)) & 1).float()
+        mag = self._table(msg.device)[(code & ((1 << (w - 1)) - 1)).clamp_max(self.table.numel() - 1)]
+        y = torch.ldexp(sign * mag, e.unsqueeze(2))
         return y.reshape(-1)[:numel]
 
 

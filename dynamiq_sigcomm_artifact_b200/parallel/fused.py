@@ -36,13 +36,15 @@ def _align(x: int, a: int) -> int:
     return (x + a - 1) // a * a
 
 
-CODECS = {"rht": 0, "rht_tc": 1, "sc_aee": 2, "sc_mee": 3}
+CODECS = {"rht": 0, "rht_tc": 1, "sc_aee": 2, "sc_mee": 3, "mx": 4}
 
 
 def block_bytes(bits: int, codec: str = "rht") -> int:
     """Bytes of one encoded 1024-element block inside a message (scales of the rht codec excluded)."""
     if codec.startswith("sc_"):
         return 4 * (16 * (2 * bits + 1) + 2)
+    if codec == "mx":
+        return 128 * bits + 32
     return 128 * bits
 
 
@@ -69,7 +71,7 @@ class Layout:
 
     @property
     def slot_stride(self) -> int:
-        scales = 0 if self.codec.startswith("sc_") else 4 * self.blocks_per_shard
+        scales = 4 * self.blocks_per_shard if self.codec in ("rht", "rht_tc") else 0
         return _align(self.scales_off + scales, 256)
 
 
@@ -90,7 +92,7 @@ _SC_CACHE: Dict[tuple, tuple] = {}
 
 def codec_args(codec: str, bits: int, device) -> tuple:
     """(codec id, lattice_max, c1, c2, lut) as the native operators take them."""
-    if codec in ("rht", "rht_tc"):
+    if codec in ("rht", "rht_tc", "mx"):
         return CODECS[codec], 0.0, 0.0, 0.0, None
     key = (codec, bits, str(device))
     if key not in _SC_CACHE:

@@ -65,7 +65,7 @@ def test_superchunk_scale_rounds_up_so_codes_never_clip():
 def test_block_float_formats(fmt, bits):
     torch.manual_seed(2)
     c = codecs.BlockFloatCodec(fmt)
-    x = torch.randn(32 * 8 * 5)
+    x = torch.randn(1024 * 5)
     msg = c.encode(x, 0, 0)
     assert msg.numel() * 8 / x.numel() == bits
     y = c.decode(msg, x.numel())

@@ -93,3 +93,37 @@ def test_mean_centre_kernels_match_torch(dtype):
     dq.superchunk_add_mean(resid, (stats[:, 0] * world).contiguous(), out)
     tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
     assert torch.allclose(out.cpu().float(), torch.nan_to_num(x.float()), atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("fmt,bits", [("fp8", 8), ("fp6", 6), ("fp4", 4)])
+def test_block_float_kernel_matches_cpu_codec(fmt, bits):
+    """Native cvt (E4M3 / E3M2 / E2M1) inside the fused kernel against the PyTorch-op codec on CPU."""
+    from dynamiq_sigcomm_artifact_b200.parallel.codecs import BlockFloatCodec
+    from dynamiq_sigcomm_artifact_b200.parallel.fused import Layout, LocalCluster
+
+    n = 5 * 1024
+    x = torch.from_numpy(heavy_tail_grad(n, 12))
+    x[3], x[40:72] = float("nan"), 0.0  # a sanitised value and an all-zero scaling block
+    ref = BlockFloatCodec(fmt)
+    want = ref.encode(x, 0, 0)
+    cl = LocalCluster(1, n, ctas=2, threads=128)
+    lay = Layout(n, 1, bits, "mx")
+    buf = x.clone().cuda()
+    _one_step(cl, buf, sch.Step(shard=0, out=sch.OUT_SEND, dst=0, send_slot=0, tag=sch.TAG_ENCODE), bits, "mx")
+    got = cl.slot_bytes(0, 0, lay, lay.nblocks).cpu()
+    assert got.numel() == want.numel() == ref.message_bytes(n)
+    assert torch.equal(got, want), f"{int((got != want).sum())} of {want.numel()} bytes differ"
+    out = torch.zeros(n, device="cuda")
+    _one_step(cl, out, sch.Step(shard=0, recv_slot=0, nrecv=1, out=sch.OUT_DECODE), bits, "mx", preset_flags=True)
+    assert torch.equal(out.cpu(), ref.decode(want, n))
+    # collective
+    world = 4
+    xs = [heavy_tail_grad(20 * 1024, 60 + r) for r in range(world)]
+    exact = torch.from_numpy(np.mean(np.stack(xs).astype(np.float64), 0))
+    cl4 = LocalCluster(world, 20 * 1024, ctas=3, threads=128)
+    bufs = [torch.from_numpy(a).cuda() for a in xs]
+    cl4.allreduce_(bufs, bits, "ring", codec="mx")
+    cl4.check()
+    assert all(torch.equal(bufs[0], b) for b in bufs)
+    err = float(((bufs[0].cpu().double() - exact) ** 2).sum() / (exact ** 2).sum())
+    assert err < {"fp8": 5e-3, "fp6": 2e-2, "fp4": 0.15}[fmt], err
