@@ -8,6 +8,7 @@
 // (testbed_evaluation/new_comm_hooks/comm_hooks.py:239-241); its numerics come from the simulation stack
 // (simulations_llm/new_comm_hooks/utils_aggregation.py:422-506).  PyTorch-op twin: codecs.BlockFloatCodec.
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -111,6 +112,54 @@ __device__ __forceinline__ void mx_decode_block(float (&v)[32], const uint8_t* t
     v[k] = ADD ? __fadd_rn(v[k], a) : a;
     v[k + 1] = ADD ? __fadd_rn(v[k + 1], b) : b;
   }
+}
+
+// Identity wire: the block as 1024 bf16 (B = 16) or fp32 (B = 32) values, lane-contiguous.  The custom
+// point-to-point all-reduce of uncompressed gradients (the reference's BFloat16 / Float32 "compressors"
+// on its ring, utils_aggregation.py:575-686, and bf16_add_kernel, ring_allreduce_backend.cu:581-587).
+template <int B>
+struct CastGeom {
+  static constexpr int kBlockBytes = 128 * B;  // 2048 / 4096
+};
+
+template <int B>
+__device__ __forceinline__ void cast_encode_block(const float (&v)[32], uint8_t* tile, int lane) {
+  if (B == 16) {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(tile) + 32 * lane;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      float o[4] = {sanitize(v[4 * q]), sanitize(v[4 * q + 1]), sanitize(v[4 * q + 2]), sanitize(v[4 * q + 3])};
+      Elem<__nv_bfloat16>::store4(dst + 4 * q, o);
+    }
+  } else {
+    float* dst = reinterpret_cast<float*>(tile) + 32 * lane;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      float o[4] = {sanitize(v[4 * q]), sanitize(v[4 * q + 1]), sanitize(v[4 * q + 2]), sanitize(v[4 * q + 3])};
+      Elem<float>::store4(dst + 4 * q, o);
+    }
+  }
+}
+
+template <int B, bool ADD>
+__device__ __forceinline__ void cast_decode_block(float (&v)[32], const uint8_t* tile, int lane) {
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    float o[4];
+    if (B == 16) Elem<__nv_bfloat16>::load4(reinterpret_cast<const __nv_bfloat16*>(tile) + 32 * lane + 4 * q, o);
+    else Elem<float>::load4(reinterpret_cast<const float*>(tile) + 32 * lane + 4 * q, o);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[4 * q + k] = ADD ? __fadd_rn(v[4 * q + k], o[k]) : o[k];
+  }
+}
+
+template <int NBYTES>
+__device__ __forceinline__ void bytes_copy_out(uint8_t* dst, const uint8_t* tile, int lane) {
+  for (int i = lane; i < NBYTES / 16; i += 32) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(tile)[i];
+}
+template <int NBYTES>
+__device__ __forceinline__ void bytes_copy_in(uint8_t* tile, const uint8_t* src, int lane) {
+  for (int i = lane; i < NBYTES / 16; i += 32) reinterpret_cast<uint4*>(tile)[i] = __ldcg(reinterpret_cast<const uint4*>(src) + i);
 }
 
 template <int B>

@@ -69,6 +69,16 @@ static void launch_mx(int bits, const ARParams* hp, const ARParams* dp, int nran
   }
 }
 
+template <typename T>
+static void launch_cast(int bits, const ARParams* hp, const ARParams* dp, int nranks, int ctas, int threads,
+                        cudaStream_t stream) {
+  switch (bits) {
+    case 16: launch_one<16, T, kCodecCast>(hp, dp, nranks, ctas, threads, stream); break;
+    case 32: launch_one<32, T, kCodecCast>(hp, dp, nranks, ctas, threads, stream); break;
+    default: TORCH_CHECK(false, "the identity wire carries bf16 (16) or fp32 (32) values, got ", bits);
+  }
+}
+
 // `codec`: kCodecRht (SIMT rotation), kCodecRhtTc (tcgen05 rotation), kCodecScAee, kCodecScMee, kCodecMx
 template <typename T>
 static void launch_bits(int bits, const ARParams* hp, const ARParams* dp, int nranks, int ctas, int threads,
@@ -79,6 +89,7 @@ static void launch_bits(int bits, const ARParams* hp, const ARParams* dp, int nr
     case kCodecScAee: launch_sc<T, kCodecScAee>(bits, hp, dp, nranks, ctas, threads, stream); break;
     case kCodecScMee: launch_sc<T, kCodecScMee>(bits, hp, dp, nranks, ctas, threads, stream); break;
     case kCodecMx: launch_mx<T>(bits, hp, dp, nranks, ctas, threads, stream); break;
+    case kCodecCast: launch_cast<T>(bits, hp, dp, nranks, ctas, threads, stream); break;
     default: TORCH_CHECK(false, "unknown codec ", codec);
   }
 }
@@ -86,6 +97,7 @@ static void launch_bits(int bits, const ARParams* hp, const ARParams* dp, int nr
 static unsigned block_bytes_of(int codec, int bits) {
   if (codec == kCodecScAee || codec == kCodecScMee) return 4u * (16u * (2u * bits + 1u) + 2u);
   if (codec == kCodecMx) return 128u * bits + 32u;
+  if (codec == kCodecCast) return 128u * bits;
   return 128u * bits;
 }
 

@@ -12,7 +12,7 @@ constexpr uint32_t kTagStratified = 0x4000u;  // step tag flag: stratified round
 // local operand / result of a step: keep in sync with parallel/schedules.py
 enum : int { kLocalRaw = 0, kLocalWs = 1 };
 enum : int { kOutSend = 0, kOutStore = 1, kOutFinal = 2, kOutDecode = 3 };
-enum : int { kCodecRht = 0, kCodecRhtTc = 1, kCodecScAee = 2, kCodecScMee = 3, kCodecMx = 4 };
+enum : int { kCodecRht = 0, kCodecRhtTc = 1, kCodecScAee = 2, kCodecScMee = 3, kCodecMx = 4, kCodecCast = 5 };
 
 // error codes left in status[0]; status[1] = (step << 16) | cta, status[2] = slot
 enum : uint32_t { kOk = 0, kErrWaitTimeout = 1, kErrBadProgram = 2, kErrCopyTimeout = 3, kErrMmaTimeout = 4 };

@@ -94,8 +94,10 @@ __host__ __device__ constexpr size_t fused_smem_bytes(int threads) {
 template <int BITS, typename T, int CODEC>
 __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
   constexpr bool TC = CODEC == kCodecRhtTc;
-  constexpr bool MX = CODEC == kCodecMx;  // block-float codes (8 / 6 / 4 bit) with native conversions
-  constexpr bool SC = CODEC == kCodecScAee || CODEC == kCodecScMee || MX;  // lane-contiguous record codecs
+  constexpr bool MX = CODEC == kCodecMx;      // block-float codes (8 / 6 / 4 bit) with native conversions
+  constexpr bool CAST = CODEC == kCodecCast;  // identity wire: bf16 (16) or fp32 (32) values
+  constexpr bool SC = CODEC == kCodecScAee || CODEC == kCodecScMee || MX || CAST;  // lane-contiguous record codecs
+  constexpr int CB = BITS == 32 ? 32 : 16;
   constexpr bool MEE = CODEC == kCodecScMee;
   constexpr int SCB = (BITS == 2 || BITS == 4 || BITS == 8) ? BITS : 4;  // superchunk code width (2, 4, 8 only)
   constexpr int MXB = (BITS == 4 || BITS == 6 || BITS == 8) ? BITS : 8;  // block-float code width (4, 6, 8 only)
@@ -228,20 +230,23 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
       float v[32];
       if constexpr (SC) {
         // ---- record codecs (superchunk AEE / MEE, block-float): no rotation, one record area per block ----
-        constexpr unsigned kBB = MX ? MxGeom<MXB>::kBlockBytes : ScGeom<SCB>::kBlockBytes;
+        constexpr unsigned kBB = CAST ? CastGeom<CB>::kBlockBytes : (MX ? MxGeom<MXB>::kBlockBytes : ScGeom<SCB>::kBlockBytes);
         const unsigned long long boff = static_cast<unsigned long long>(bs) * kBB;
         const uint32_t first_call = static_cast<uint32_t>(blk) * 64u;  // Philox call index = element / 16
         auto rec_in = [&](const uint8_t* src) {
-          if constexpr (MX) mx_copy_in<MXB>(rec_tile, src, lane);
+          if constexpr (CAST) bytes_copy_in<CastGeom<CB>::kBlockBytes>(rec_tile, src, lane);
+          else if constexpr (MX) mx_copy_in<MXB>(rec_tile, src, lane);
           else sc_copy_in<SCB>(rec_tile, src, lane);
           __syncwarp();
         };
         auto rec_out = [&](uint8_t* dstp) {
-          if constexpr (MX) mx_copy_out<MXB>(dstp, rec_tile, lane);
+          if constexpr (CAST) bytes_copy_out<CastGeom<CB>::kBlockBytes>(dstp, rec_tile, lane);
+          else if constexpr (MX) mx_copy_out<MXB>(dstp, rec_tile, lane);
           else sc_copy_out<SCB>(dstp, rec_tile, lane);
         };
         auto rec_encode = [&]() {
-          if constexpr (MX) mx_encode_block<MXB>(v, rec_tile, lane);
+          if constexpr (CAST) cast_encode_block<CB>(v, rec_tile, lane);
+          else if constexpr (MX) mx_encode_block<MXB>(v, rec_tile, lane);
           else sc_encode_block<SCB, MEE>(v, rec_tile, scp, first_call, tag, p.step, p.seed_lo, p.seed_hi, lane);
           __syncwarp();
         };
@@ -252,7 +257,8 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
           for (int r = 0; r < nrecv; ++r) {
             const uint8_t* slot = my_mail + static_cast<unsigned long long>(recv_slot + r) * p.slot_stride;
             rec_in(slot + boff);
-            if constexpr (MX) mx_decode_block<MXB, true>(v, rec_tile, lane);
+            if constexpr (CAST) cast_decode_block<CB, true>(v, rec_tile, lane);
+            else if constexpr (MX) mx_decode_block<MXB, true>(v, rec_tile, lane);
             else sc_decode_block<SCB, MEE, true>(v, rec_tile, scp, lane);
             __syncwarp();
           }
@@ -276,7 +282,8 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
           } else {
             rec_in(my_mail + static_cast<unsigned long long>(recv_slot) * p.slot_stride + boff);
           }
-          if constexpr (MX) mx_decode_block<MXB, false>(v, rec_tile, lane);
+          if constexpr (CAST) cast_decode_block<CB, false>(v, rec_tile, lane);
+          else if constexpr (MX) mx_decode_block<MXB, false>(v, rec_tile, lane);
           else sc_decode_block<SCB, MEE, false>(v, rec_tile, scp, lane);
           __syncwarp();
           const float wf = static_cast<float>(p.world);
@@ -284,16 +291,17 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
           for (int k = 0; k < 32; ++k) v[k] = __fdiv_rn(v[k], wf);
           sc_store_block<T>(bucket + e0, valid, vec_ok, lane, v);
         }
-        continue;
-      }
-      uint32_t w[BITS];
+      } else {
+      // ---- rotation codec ----
+      constexpr int RB = (BITS >= 2 && BITS <= 8) ? BITS : 8;  // code width of the rotation codec
+      uint32_t w[RB];
       float scale = 0.f;
 
       if (active && nrecv > 0) {  // first incoming message: issue its loads before the local work
         const uint8_t* slot = my_mail + static_cast<unsigned long long>(recv_slot) * p.slot_stride;
-        const uint32_t* codes = reinterpret_cast<const uint32_t*>(slot) + static_cast<size_t>(bs) * (BITS * 32);
+        const uint32_t* codes = reinterpret_cast<const uint32_t*>(slot) + static_cast<size_t>(bs) * (RB * 32);
 #pragma unroll
-        for (int j = 0; j < BITS; ++j) w[j] = ld_cg_u32(codes + j * 32 + lane);
+        for (int j = 0; j < RB; ++j) w[j] = ld_cg_u32(codes + j * 32 + lane);
         scale = __ldcg(reinterpret_cast<const float*>(slot + p.scales_off) + bs);
       }
 
@@ -330,14 +338,14 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
       }
 
       if (active && out != kOutDecode) {
-        if (nrecv > 0) dequantize_add_block<BITS>(w, scale, v);
+        if (nrecv > 0) dequantize_add_block<RB>(w, scale, v);
         for (int r = 1; r < nrecv; ++r) {
           const uint8_t* slot = my_mail + static_cast<unsigned long long>(recv_slot + r) * p.slot_stride;
-          const uint32_t* codes = reinterpret_cast<const uint32_t*>(slot) + static_cast<size_t>(bs) * (BITS * 32);
+          const uint32_t* codes = reinterpret_cast<const uint32_t*>(slot) + static_cast<size_t>(bs) * (RB * 32);
 #pragma unroll
-          for (int j = 0; j < BITS; ++j) w[j] = ld_cg_u32(codes + j * 32 + lane);
+          for (int j = 0; j < RB; ++j) w[j] = ld_cg_u32(codes + j * 32 + lane);
           scale = __ldcg(reinterpret_cast<const float*>(slot + p.scales_off) + bs);
-          dequantize_add_block<BITS>(w, scale, v);
+          dequantize_add_block<RB>(w, scale, v);
         }
       }
 
@@ -348,36 +356,36 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
         }
       } else if (out == kOutSend) {
         if (active) {
-          scale = have_rw ? quantize_block_rw<BITS>(v, w, rw, lane, p.rank, strat_world)
-                          : quantize_block<BITS>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi,
+          scale = have_rw ? quantize_block_rw<RB>(v, w, rw, lane, p.rank, strat_world)
+                          : quantize_block<RB>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi,
                                                  lane, p.rank, strat_world);
           if (!p.no_transmit) {
             uint8_t* slot = p.mail[dst] + static_cast<unsigned long long>(send_slot) * p.slot_stride;
-            uint32_t* codes = reinterpret_cast<uint32_t*>(slot) + static_cast<size_t>(bs) * (BITS * 32);
+            uint32_t* codes = reinterpret_cast<uint32_t*>(slot) + static_cast<size_t>(bs) * (RB * 32);
 #pragma unroll
-            for (int j = 0; j < BITS; ++j) codes[j * 32 + lane] = w[j];
+            for (int j = 0; j < RB; ++j) codes[j * 32 + lane] = w[j];
             if (lane == 0) reinterpret_cast<float*>(slot + p.scales_off)[bs] = scale;
           }
         }
       } else {
         if (active) {
           if (out == kOutFinal) {
-            scale = have_rw ? quantize_block_rw<BITS>(v, w, rw, lane)
-                            : quantize_block<BITS>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi,
+            scale = have_rw ? quantize_block_rw<RB>(v, w, rw, lane)
+                            : quantize_block<RB>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi,
                                                    lane);
             if (!p.no_transmit) {
               for (int peer = 0; peer < p.world; ++peer) {
                 if (peer == p.rank) continue;
                 uint8_t* slot = p.mail[peer] + static_cast<unsigned long long>(send_slot) * p.slot_stride;
-                uint32_t* codes = reinterpret_cast<uint32_t*>(slot) + static_cast<size_t>(bs) * (BITS * 32);
+                uint32_t* codes = reinterpret_cast<uint32_t*>(slot) + static_cast<size_t>(bs) * (RB * 32);
 #pragma unroll
-                for (int j = 0; j < BITS; ++j) codes[j * 32 + lane] = w[j];
+                for (int j = 0; j < RB; ++j) codes[j * 32 + lane] = w[j];
                 if (lane == 0) reinterpret_cast<float*>(slot + p.scales_off)[bs] = scale;
               }
             }
           }
           // kOutDecode: w / scale were loaded from the all-gather slot above
-          dequantize_block<BITS>(w, scale, v);
+          dequantize_block<RB>(w, scale, v);
         }
         if (rotate_out) {
           if (TC) rotate_inverse_tc(v, col_signs, p.finish_scale, tg, lane);
@@ -388,6 +396,7 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
           else store_block<T>(bucket + e0, valid, vec_ok, lane, v);
         }
       }
+      }  // rotation codec
     }
 
     if (out == kOutSend || out == kOutFinal) {
@@ -469,6 +478,10 @@ void launch_one(const ARParams* host_params, const ARParams* dev_params, int nra
   template void launch_one<BITS, __nv_bfloat16, kCodecRht>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);   \
   template void launch_one<BITS, float, kCodecRhtTc>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);         \
   template void launch_one<BITS, __nv_bfloat16, kCodecRhtTc>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);
+
+#define DQ_INSTANTIATE_FUSED_ALLREDUCE_CAST(BITS)                                                                       \
+  template void launch_one<BITS, float, kCodecCast>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);         \
+  template void launch_one<BITS, __nv_bfloat16, kCodecCast>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);
 
 #define DQ_INSTANTIATE_FUSED_ALLREDUCE_MX(BITS)                                                                         \
   template void launch_one<BITS, float, kCodecMx>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);           \

@@ -211,7 +211,34 @@ def _cast_hook(dtype: Optional[torch.dtype]) -> Callable:
     return hook
 
 
-bf16_hook = _cast_hook(torch.bfloat16)
+def bf16_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
+    """bf16 wire.  On CUDA: this framework's own point-to-point all-reduce (the fused kernel with the
+    identity codec, no library collective), as the reference's bf16 method is its own ring carrying
+    bf16 (testbed_evaluation/new_comm_hooks/comm_hooks.py:175-212).  ``DQ_BF16_LIBRARY=1`` or a CPU
+    bucket selects the library all-reduce with a bf16 cast instead."""
+    import os
+
+    state = _unwrap(state)
+    state._auto_advance(bucket.index())
+    buf = bucket.buffer()
+    world = _world(state)
+    use_p2p = (buf.is_cuda and world > 1 and buf.dtype in (torch.float32, torch.bfloat16)
+               and os.environ.get("DQ_BF16_LIBRARY", "0") not in ("1", "true")
+               and state["batch_idx"] >= state["config"].warmup_steps)
+    if not use_p2p:
+        return _library_mean(state, buf, torch.bfloat16)
+    spec, cfg = state["spec"], state["config"]
+    eng = _engine(state)
+    eng.ensure_capacity(buf.numel())
+    stream = state["comm_stream"]
+    stream.wait_stream(torch.cuda.current_stream())
+    fut = torch.futures.Future(devices=[buf.device])
+    with torch.cuda.stream(stream), tracing.nvtx_range(f"bucket{bucket.index()}.p2p_bf16_{spec.topology}"):
+        eng.allreduce_(buf.reshape(-1), 16, spec.topology, cfg.seed, int(state["batch_idx"]), bucket.index(),
+                       no_transmit=spec.compute_only, codec="cast")
+        buf.record_stream(stream)
+        fut.set_result(buf)
+    return fut
 fp16_hook = _cast_hook(torch.float16)
 fp32_hook = _cast_hook(None)
 

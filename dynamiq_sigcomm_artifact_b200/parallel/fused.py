@@ -36,7 +36,7 @@ def _align(x: int, a: int) -> int:
     return (x + a - 1) // a * a
 
 
-CODECS = {"rht": 0, "rht_tc": 1, "sc_aee": 2, "sc_mee": 3, "mx": 4}
+CODECS = {"rht": 0, "rht_tc": 1, "sc_aee": 2, "sc_mee": 3, "mx": 4, "cast": 5}
 
 
 def block_bytes(bits: int, codec: str = "rht") -> int:
@@ -92,7 +92,7 @@ _SC_CACHE: Dict[tuple, tuple] = {}
 
 def codec_args(codec: str, bits: int, device) -> tuple:
     """(codec id, lattice_max, c1, c2, lut) as the native operators take them."""
-    if codec in ("rht", "rht_tc", "mx"):
+    if codec in ("rht", "rht_tc", "mx", "cast"):
         return CODECS[codec], 0.0, 0.0, 0.0, None
     key = (codec, bits, str(device))
     if key not in _SC_CACHE:
@@ -145,7 +145,7 @@ class FusedAllreduce:
             self.buf.close()
         self.max_numel = int(max_numel)
         self.nslots = sch.n_slots(self.world, "ring")  # same count for every topology
-        worst = Layout(self.max_numel, self.world, 8, "sc_aee")  # the largest message: 8-bit superchunk records
+        worst = Layout(self.max_numel, self.world, 32, "cast")  # the largest message: the fp32 identity wire
         self.set_bytes = _align(self.nslots * worst.slot_stride, 4096)
         self.flag_words_per_set = self.nslots * self.ctas
         self.off_flags = 2 * self.set_bytes
@@ -220,7 +220,7 @@ class LocalCluster:
         self.device = torch.device(device)
         self.timeout_ns = timeout_ms * 1_000_000
         self.nslots = sch.n_slots(world, "ring")
-        worst = Layout(max_numel, world, 8, "sc_aee")
+        worst = Layout(max_numel, world, 32, "cast")
         self.max_numel = max_numel
         self.mailbox_bytes = self.nslots * worst.slot_stride
         self.mail = [torch.zeros(self.mailbox_bytes, dtype=torch.uint8, device=self.device) for _ in range(world)]

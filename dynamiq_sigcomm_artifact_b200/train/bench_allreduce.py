@@ -126,6 +126,18 @@ def run_collectives(args) -> None:
 
         ms = time_op(nccl16, lambda: work.copy_(base), args.iters, args.warmup)
         record("nccl_bf16", ms, 2 * (world - 1) / world * numel * 2, nmse_vs(exact, work))
+        # this framework's own point-to-point all-reduce of uncompressed values (identity codec)
+        for cbits, label in ((16, "p2p_bf16"), (32, "p2p_fp32")):
+            it0 = [0]
+
+            def p2p():
+                it0[0] += 1
+                eng.allreduce_(work, cbits, "direct", seed=args.seed, step=it0[0], bucket_id=0, codec="cast")
+
+            ms = time_op(p2p, lambda: work.copy_(base), args.iters, args.warmup)
+            eng.check()
+            lay = Layout(numel, world, cbits, "cast")
+            record(f"{label}_direct", ms, 2 * (world - 1) * lay.blocks_per_shard * 128 * cbits, nmse_vs(exact, work))
         for topo in topologies:
             if topo == "butterfly" and world & (world - 1):
                 continue

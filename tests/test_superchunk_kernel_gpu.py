@@ -127,3 +127,21 @@ def test_block_float_kernel_matches_cpu_codec(fmt, bits):
     assert all(torch.equal(bufs[0], b) for b in bufs)
     err = float(((bufs[0].cpu().double() - exact) ** 2).sum() / (exact ** 2).sum())
     assert err < {"fp8": 5e-3, "fp6": 2e-2, "fp4": 0.15}[fmt], err
+
+
+@pytest.mark.parametrize("bits,tol", [(16, 2e-5), (32, 1e-13)])
+def test_identity_wire_collective(bits, tol):
+    """Uncompressed point-to-point all-reduce through the fused kernel (bf16 or fp32 on the wire)."""
+    from dynamiq_sigcomm_artifact_b200.parallel.fused import LocalCluster
+
+    world, n = 4, 30 * 1024 + 40
+    xs = [heavy_tail_grad(n, 70 + r) for r in range(world)]
+    exact = torch.from_numpy(np.mean(np.stack(xs).astype(np.float64), 0))
+    cl = LocalCluster(world, n, ctas=3, threads=128)
+    for topology in sch.TOPOLOGIES:
+        bufs = [torch.from_numpy(a).cuda() for a in xs]
+        cl.allreduce_(bufs, bits, topology, codec="cast")
+        cl.check()
+        assert all(torch.equal(bufs[0], b) for b in bufs)
+        err = float(((bufs[0].cpu().double() - exact) ** 2).sum() / (exact ** 2).sum())
+        assert err < tol, (topology, err)
