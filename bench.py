@@ -47,6 +47,8 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--topology", default=None)
     ap.add_argument("--comm-ctas", type=int, default=64)
     ap.add_argument("--comm-threads", type=int, default=256)
+    ap.add_argument("--tail-ctas", type=int, default=148, help="grid of the step's last bucket")
+    ap.add_argument("--reducer", default="flat", choices=["flat", "ddp"])
     ap.add_argument("--bucket-cap-mb", type=int, default=0, help="0: 25 MB (GPT-2, BERT) or 100 MB (Llama 1.2B)")
     ap.add_argument("--rotation", default="simt", choices=["simt", "tc"])
     return ap.parse_args()
@@ -84,7 +86,7 @@ def main() -> None:
     os.environ.setdefault("DQ_ROTATION", args.rotation)
     cfg = TrainConfig(model=args.model, method=args.method, micro_batch=mb, seq_len=seq, task=task,
                       bucket_cap_mb=args.bucket_cap_mb, topology=args.topology, comm_ctas=args.comm_ctas,
-                      comm_threads=args.comm_threads)
+                      comm_threads=args.comm_threads, tail_ctas=args.tail_ctas, reducer=args.reducer)
     tr = Trainer(cfg)
     dev = tr.device
     host_batches = [tr.synthetic_batch(pinned=True) for _ in range(4)]
@@ -145,7 +147,7 @@ def main() -> None:
             "data": "synthetic uniform token ids, random-init weights", "impl": "ours",
             "config": {"model": args.model, "arch": desc, "global_batch": mb * world, "seq_len": seq,
                        "parallelism": f"dp{world}", "method": args.method if world > 1 else "none (1 GPU)",
-                       "bucket_cap_mb": args.bucket_cap_mb, "optimizer": "fused AdamW, fp32 master weights",
+                       "bucket_cap_mb": args.bucket_cap_mb, "reducer": args.reducer, "optimizer": "fused AdamW, fp32 master weights",
                        "l2": "per-step working set (weights+grads+optimizer state+activations) is several GB, >> 126 MB L2"},
             "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"),
                        "reasons": clocks.get("reasons", []), "samples": clocks.get("samples", 0)},

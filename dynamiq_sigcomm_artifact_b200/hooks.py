@@ -127,9 +127,17 @@ def _engine(state: HookState):
         state["engine"] = FusedAllreduce(group=state["group"], max_numel=cfg.max_bucket_mb * (1 << 20) // 4,
                                          ctas=cfg.comm_ctas, threads=cfg.comm_threads,
                                          timeout_ms=cfg.wait_timeout_ms, validate=cfg.validate_topology,
-                                         rotation=cfg.rotation)
+                                         rotation=cfg.rotation, max_ctas=max(cfg.comm_ctas, cfg.tail_ctas))
         state["comm_stream"] = torch.cuda.Stream(priority=-1)
     return state["engine"]
+
+
+def _grid(state: HookState, bucket) -> Optional[int]:
+    """The step's last bucket has no backward pass left to share the GPU with: give it the wide grid."""
+    cfg: DynamiqConfig = state["config"]
+    if cfg.tail_ctas > 0 and bucket.is_last():
+        return cfg.tail_ctas
+    return None
 
 
 def _bucket_bits(state: HookState, index: int, buf: torch.Tensor) -> int:
@@ -163,7 +171,7 @@ def _rht_allreduce(state: HookState, bucket) -> torch.futures.Future:
             fut = torch.futures.Future(devices=[buf.device])
             with torch.cuda.stream(stream), tracing.nvtx_range(f"bucket{index}.fused_{spec.topology}_{bits}bit"):
                 eng.allreduce_(buf, bits, spec.topology, cfg.seed, step, index, no_transmit=spec.compute_only,
-                               correlated=spec.correlated)
+                               correlated=spec.correlated, ctas=_grid(state, bucket))
                 buf.record_stream(stream)
                 if exact is not None:
                     _account_error(state, buf, exact)
@@ -235,7 +243,7 @@ def bf16_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tens
     fut = torch.futures.Future(devices=[buf.device])
     with torch.cuda.stream(stream), tracing.nvtx_range(f"bucket{bucket.index()}.p2p_bf16_{spec.topology}"):
         eng.allreduce_(buf.reshape(-1), 16, spec.topology, cfg.seed, int(state["batch_idx"]), bucket.index(),
-                       no_transmit=spec.compute_only, codec="cast")
+                       no_transmit=spec.compute_only, codec="cast", ctas=_grid(state, bucket))
         buf.record_stream(stream)
         fut.set_result(buf)
     return fut

@@ -8,6 +8,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..ops.embedding import TiedEmbedding
 from ..ops.layers import LayerNorm, fused_cross_entropy, padded_vocab_logits, shift_labels
 from ..ops.linear import MasterLinear
 from .common import GeluMLP, SelfAttention, init_linear
@@ -50,7 +51,7 @@ class BertMLM(nn.Module):
     def __init__(self, c: BertConfig = BertConfig()):
         super().__init__()
         self.config = c
-        self.tok = nn.Embedding(c.vocab, c.hidden)
+        self.tok = TiedEmbedding(c.vocab, c.hidden)
         self.pos = nn.Embedding(c.max_pos, c.hidden)
         self.typ = nn.Embedding(c.type_vocab, c.hidden)
         self.ln_emb = LayerNorm(c.hidden, c.eps)
@@ -72,7 +73,7 @@ class BertMLM(nn.Module):
         h = self.head_ln(F.gelu(self.head_dense(x)))
         if labels is None:
             return F.linear(h, self.tok.weight.to(h.dtype), self.head_bias.to(h.dtype))
-        logits = padded_vocab_logits(h, self.tok.weight, self.head_bias)
+        logits = self.tok.logits(h, self.head_bias)
         return fused_cross_entropy(logits, labels.reshape(-1), self.config.vocab)
 
 

@@ -8,7 +8,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops.layers import LayerNorm, fused_cross_entropy, padded_vocab_logits, shift_labels
+from ..ops.embedding import TiedEmbedding
+from ..ops.layers import LayerNorm, fused_cross_entropy, shift_labels
 from .common import GeluMLP, SelfAttention, init_linear
 
 
@@ -43,7 +44,7 @@ class GPT2(nn.Module):
     def __init__(self, c: GPT2Config = GPT2Config()):
         super().__init__()
         self.config = c
-        self.wte = nn.Embedding(c.vocab, c.d_model)
+        self.wte = TiedEmbedding(c.vocab, c.d_model)
         self.wpe = nn.Embedding(c.context, c.d_model)
         self.blocks = nn.ModuleList(GPT2Block(c) for _ in range(c.n_layer))
         self.ln_f = LayerNorm(c.d_model, c.eps)
@@ -63,5 +64,5 @@ class GPT2(nn.Module):
         h = self.ln_f(x)
         if labels is None:
             return F.linear(h, self.wte.weight)
-        logits = padded_vocab_logits(h, self.wte.weight)
+        logits = self.wte.logits(h)
         return fused_cross_entropy(logits, shift_labels(labels).reshape(-1), self.config.vocab)

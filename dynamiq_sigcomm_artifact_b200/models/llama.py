@@ -8,6 +8,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..ops.embedding import TiedEmbedding
 from ..ops.layers import fused_cross_entropy, padded_vocab_logits, shift_labels, RMSNorm, rope_tables
 from .common import SelfAttention, SwiGLU, init_linear
 
@@ -46,7 +47,7 @@ class Llama(nn.Module):
     def __init__(self, c: LlamaConfig = LlamaConfig()):
         super().__init__()
         self.config = c
-        self.embed = nn.Embedding(c.vocab, c.d_model)
+        self.embed = TiedEmbedding(c.vocab, c.d_model)
         self.blocks = nn.ModuleList(LlamaBlock(c) for _ in range(c.n_layer))
         self.norm = RMSNorm(c.d_model, c.eps)
         self.lm_head = None if c.tie_embeddings else nn.Linear(c.d_model, c.vocab, bias=False)
@@ -71,5 +72,5 @@ class Llama(nn.Module):
         h = self.norm(x)
         if labels is None:
             return F.linear(h, w)
-        logits = padded_vocab_logits(h, w)
+        logits = self.embed.logits(h) if self.lm_head is None else padded_vocab_logits(h, w)
         return fused_cross_entropy(logits, shift_labels(labels).reshape(-1), self.config.vocab)

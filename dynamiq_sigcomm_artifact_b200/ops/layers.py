@@ -27,6 +27,9 @@ class _NormFn(torch.autograd.Function):
         ctx.save_for_backward(xc, w, mean, rstd)
         ctx.rms = rms
         ctx.has_bias = b is not None
+        # gradient-arena views (parallel/reducer.py): written in place, autograd then sees None
+        ctx.wg = getattr(w, "_dq_grad", None)
+        ctx.bg = getattr(b, "_dq_grad", None) if b is not None else None
         return y
 
     @staticmethod
@@ -35,6 +38,12 @@ class _NormFn(torch.autograd.Function):
         x, w, mean, rstd = ctx.saved_tensors
         dx, dw, db = ops.norm_bwd(dy.contiguous(), x, w, mean, rstd, ctx.rms)
         counters.add("norm_bwd", 2 if ctx.rms else 3)
+        if ctx.wg is not None:
+            ctx.wg.copy_(dw)
+            dw = None
+        if ctx.has_bias and ctx.bg is not None:
+            ctx.bg.copy_(db)
+            db = None
         return dx, dw, (db if ctx.has_bias else None), None, None
 
 
@@ -192,8 +201,9 @@ class FusedAdamW(torch.optim.Optimizer):
         self._step = 0
         self._shadows = dict(shadows or {})
 
-    def _table(self, gi: int, group) -> list:
-        """Per (param dtype, grad dtype) metadata; rebuilt when a gradient buffer moves."""
+    def _table(self, gi, group) -> list:
+        """Per (param dtype, grad dtype) metadata; rebuilt when a gradient buffer moves.  `gi` is any
+        hashable key, `group["params"]` the parameters it covers."""
         ps: List[torch.Tensor] = [p for p in group["params"] if p.grad is not None]
         key = tuple((p.data_ptr(), p.grad.data_ptr(), self._shadow_ptr(p)) for p in ps)
         cached = self._tables.get(gi)
@@ -230,9 +240,58 @@ class FusedAdamW(torch.optim.Optimizer):
         sh = self._shadows.get(p)
         if sh is None:
             return 0
-        if sh.dtype != torch.bfloat16 or sh.shape != p.shape or not sh.is_contiguous():
-            raise ValueError("a shadow must be a contiguous bf16 tensor of the parameter's shape")
+        if sh.dtype != torch.bfloat16 or not sh.is_contiguous() or sh.numel() < p.numel() \
+                or sh.shape[1:] != p.shape[1:]:
+            raise ValueError("a shadow must be a contiguous bf16 tensor whose leading rows have the parameter's shape")
         return sh.data_ptr()
+
+    def advance(self) -> int:
+        """Start optimizer step t+1 for callers that update parameter subsets with :meth:`step_params`."""
+        self._step += 1
+        return self._step
+
+    @torch.no_grad()
+    def step_params(self, key, params: List[torch.Tensor], grad_scale: float = 1.0) -> None:
+        """AdamW update of `params` only (all from one param group), at the step count set by
+        :meth:`advance`.  `key` identifies the subset (its pointer table is cached under it).  Used by
+        the bucket reducer to update a bucket as soon as its gradients are reduced."""
+        if not params:
+            return
+        group = self._group_of(params[0])
+        b1, b2 = group["betas"]
+        if params[0].is_cuda:
+            ops = require()
+            for table, numel, starts, chunks, pbf, gbf, _ in self._table(("subset", key), {"params": params}):
+                ops.adamw_step(table, numel, starts, chunks, pbf, gbf, group["lr"], b1, b2, group["eps"],
+                               group["weight_decay"], self._step, grad_scale)
+                counters.add("adamw")
+        else:
+            self._step_cpu([p for p in params if p.grad is not None], group, grad_scale)
+
+    def _group_of(self, p) -> dict:
+        idx = getattr(self, "_pgroup", None)
+        if idx is None:
+            idx = self._pgroup = {id(q): g for g in self.param_groups for q in g["params"]}
+        return idx[id(p)]
+
+    def _step_cpu(self, params, group, grad_scale: float) -> None:
+        b1, b2 = group["betas"]
+        for p in params:
+            st = self.state[p]
+            if "exp_avg" not in st:
+                st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+                st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+            g = p.grad.float() * grad_scale
+            st["exp_avg"].mul_(b1).add_(g, alpha=1 - b1)
+            st["exp_avg_sq"].mul_(b2).addcmul_(g, g, value=1 - b2)
+            bc1, bc2 = 1 - b1 ** self._step, 1 - b2 ** self._step
+            pf = p.float()
+            pf.mul_(1 - group["lr"] * group["weight_decay"])
+            pf.addcdiv_(st["exp_avg"], (st["exp_avg_sq"] / bc2).sqrt_().add_(group["eps"]),
+                        value=-group["lr"] / bc1)
+            p.copy_(pf)
+            if p in self._shadows:
+                self._shadows[p].view(-1)[: p.numel()].view_as(p).copy_(pf)
 
     @torch.no_grad()
     def step(self, closure=None, grad_scale: float = 1.0):
@@ -250,22 +309,7 @@ class FusedAdamW(torch.optim.Optimizer):
                                    group["weight_decay"], self._step, grad_scale)
                     counters.add("adamw")
             else:
-                for p in params:
-                    st = self.state[p]
-                    if "exp_avg" not in st:
-                        st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
-                        st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
-                    g = p.grad.float() * grad_scale
-                    st["exp_avg"].mul_(b1).add_(g, alpha=1 - b1)
-                    st["exp_avg_sq"].mul_(b2).addcmul_(g, g, value=1 - b2)
-                    bc1, bc2 = 1 - b1 ** self._step, 1 - b2 ** self._step
-                    pf = p.float()
-                    pf.mul_(1 - group["lr"] * group["weight_decay"])
-                    pf.addcdiv_(st["exp_avg"], (st["exp_avg_sq"] / bc2).sqrt_().add_(group["eps"]),
-                                value=-group["lr"] / bc1)
-                    p.copy_(pf)
-                    if p in self._shadows:
-                        self._shadows[p].copy_(pf)
+                self._step_cpu(params, group, grad_scale)
         return loss
 
     def state_dict(self):

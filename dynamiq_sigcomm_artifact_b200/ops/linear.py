@@ -19,10 +19,16 @@ import torch.nn.functional as F
 
 
 class _ShadowLinearFn(torch.autograd.Function):
+    """Gradients of `weight` / `bias` go to ``weight._dq_grad`` / ``bias._dq_grad`` when a gradient arena
+    attached them (parallel/reducer.py): the GEMM then writes its fp32 output in place and autograd sees
+    ``None`` (no temporary, no accumulate kernel).  In that mode a backward pass overwrites."""
+
     @staticmethod
     def forward(ctx, x, weight, shadow, bias):
         ctx.save_for_backward(x, shadow)
         ctx.has_bias = bias is not None
+        ctx.wg = getattr(weight, "_dq_grad", None)
+        ctx.bg = getattr(bias, "_dq_grad", None) if bias is not None else None
         return F.linear(x, shadow, None if bias is None else bias.to(x.dtype))
 
     @staticmethod
@@ -31,8 +37,16 @@ class _ShadowLinearFn(torch.autograd.Function):
         dy2 = dy.reshape(-1, dy.shape[-1])
         x2 = x.reshape(-1, x.shape[-1])
         dx = (dy2 @ shadow).reshape(x.shape) if ctx.needs_input_grad[0] else None
-        dw = torch.mm(dy2.t(), x2, out_dtype=torch.float32) if ctx.needs_input_grad[1] else None
-        db = dy2.sum(dim=0, dtype=torch.float32) if ctx.has_bias and ctx.needs_input_grad[3] else None
+        dw = db = None
+        if ctx.wg is not None:
+            torch.mm(dy2.t(), x2, out_dtype=torch.float32, out=ctx.wg)
+        elif ctx.needs_input_grad[1]:
+            dw = torch.mm(dy2.t(), x2, out_dtype=torch.float32)
+        if ctx.has_bias:
+            if ctx.bg is not None:
+                torch.sum(dy2, dim=0, dtype=torch.float32, out=ctx.bg)
+            elif ctx.needs_input_grad[3]:
+                db = dy2.sum(dim=0, dtype=torch.float32)
         return dx, dw, None, db
 
 
@@ -48,16 +62,25 @@ class MasterLinear(nn.Module):
         self.shadow = None  # bf16 copy, created by enable_shadows()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if self.shadow is not None and x.is_cuda and x.dtype == torch.bfloat16:
-            return _ShadowLinearFn.apply(x, self.weight, self.shadow, self.bias)
+        if self.shadow is not None and x.is_cuda:
+            if x.dtype != torch.bfloat16 and torch.is_autocast_enabled("cuda") \
+                    and torch.get_autocast_dtype("cuda") == torch.bfloat16:
+                x = x.to(torch.bfloat16)
+            if x.dtype == torch.bfloat16:
+                return _ShadowLinearFn.apply(x, self.weight, self.shadow, self.bias)
         return F.linear(x, self.weight, self.bias)
 
 
 def enable_shadows(model: nn.Module) -> Dict[nn.Parameter, torch.Tensor]:
-    """Create (or refresh) the bf16 copy of every MasterLinear weight; returns {weight: copy}."""
+    """Create (or refresh) the bf16 copy of every MasterLinear / TiedEmbedding weight; returns {weight: copy}
+    (a TiedEmbedding's copy has extra zero rows after the parameter's)."""
+    from .embedding import TiedEmbedding
+
     out: Dict[nn.Parameter, torch.Tensor] = {}
     for m in model.modules():
-        if isinstance(m, MasterLinear):
+        if isinstance(m, TiedEmbedding):
+            out[m.weight] = m.enable_shadow()
+        elif isinstance(m, MasterLinear):
             if m.shadow is None or m.shadow.device != m.weight.device:
                 m.shadow = torch.empty_like(m.weight, dtype=torch.bfloat16)
             with torch.no_grad():

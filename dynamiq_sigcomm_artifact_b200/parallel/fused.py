@@ -123,12 +123,16 @@ class FusedAllreduce:
     """Compressed all-reduce (mean) over NVLink for the ranks of a process group."""
 
     def __init__(self, group=None, max_numel: int = 32 << 20, ctas: int = 64, threads: int = 256,
-                 timeout_ms: int = 2000, validate: bool = True, rotation: str = "simt"):
+                 timeout_ms: int = 2000, validate: bool = True, rotation: str = "simt", max_ctas: Optional[int] = None):
+        """`ctas` is the default grid of a collective; a call may ask for any grid up to `max_ctas`
+        (every rank must ask for the same one): a bucket that runs under backward wants a small grid,
+        the last bucket of a step has the GPU to itself."""
         self.ops = _ops.require()
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.ctas, self.threads = int(ctas), int(threads)
+        self.max_ctas = max(int(max_ctas or 0), self.ctas)
         self.timeout_ns = int(timeout_ms) * 1_000_000
         self.validate = validate
         self.tensor_rotation = _rotation_flag(rotation)
@@ -147,7 +151,7 @@ class FusedAllreduce:
         self.nslots = sch.n_slots(self.world, "ring")  # same count for every topology
         worst = Layout(self.max_numel, self.world, 32, "cast")  # the largest message: the fp32 identity wire
         self.set_bytes = _align(self.nslots * worst.slot_stride, 4096)
-        self.flag_words_per_set = self.nslots * self.ctas
+        self.flag_words_per_set = self.nslots * self.max_ctas
         self.off_flags = 2 * self.set_bytes
         self.off_status = self.off_flags + _align(2 * self.flag_words_per_set * 4, 4096)
         self.off_tail = self.off_status + 256
@@ -169,7 +173,7 @@ class FusedAllreduce:
     # -- the collective --------------------------------------------------------------------
     def allreduce_(self, bucket: torch.Tensor, bits: int, topology: str = "ring", seed: int = 0, step: int = 0,
                    bucket_id: int = 0, no_transmit: bool = False, correlated: bool = False,
-                   codec: Optional[str] = None) -> torch.Tensor:
+                   codec: Optional[str] = None, ctas: Optional[int] = None) -> torch.Tensor:
         """In-place mean all-reduce of a flat fp32/bf16 CUDA tensor on the current stream.
 
         `codec`: None (the engine's rotation codec), "sc_aee" or "sc_mee" (the hierarchical
@@ -179,6 +183,9 @@ class FusedAllreduce:
         codec = codec or ("rht_tc" if self.tensor_rotation else "rht")
         self.ensure_capacity(bucket.numel())
         lay = Layout(bucket.numel(), self.world, bits, codec)
+        grid = int(ctas or self.ctas)
+        if not 1 <= grid <= self.max_ctas:
+            raise ValueError(f"grid of {grid} CTAs outside 1..{self.max_ctas} (flags are allocated for max_ctas)")
         self.epoch += 1
         parity = self.epoch & 1
         mail = [p + parity * self.set_bytes for p in self.buf.ptrs]
@@ -186,7 +193,7 @@ class FusedAllreduce:
         self.ops.fused_allreduce(
             bucket, self.program(topology, correlated), mail, flags, self.set_bytes, 2 * self.flag_words_per_set, self.nslots,
             self.buf.local_ptr + self.off_status, self.buf.local_ptr + self.off_tail, self.rank, self.world, bits,
-            self.ctas, self.threads, lay.blocks_per_shard, lay.slot_stride, lay.scales_off,
+            grid, self.threads, lay.blocks_per_shard, lay.slot_stride, lay.scales_off,
             parity * self.flag_words_per_set, self.epoch, seed, step, bucket_id, 1.0 / self.world, self.timeout_ns,
             no_transmit, *codec_args(codec, bits, bucket.device))
         counters.add("fused_allreduce")

@@ -10,6 +10,12 @@ Reference counterpart: ``train()`` and its set-up in testbed_evaluation/train_ll
 is plain ``torch.nn.parallel.DistributedDataParallel`` with 25 MB buckets and
 ``gradient_as_bucket_view``; compute is bf16 autocast over fp32 master weights and fp32
 gradient buckets.
+
+Two gradient paths (``TrainConfig.reducer``): ``"flat"`` (default) is this package's bucket reducer
+(parallel/reducer.py: gradient arena written in place by the backward kernels, communication hook
+and the AdamW step of each bucket on a side stream under the rest of backward); ``"ddp"`` wraps the
+model in ``DistributedDataParallel`` and registers the same hook through ``register_comm_hook``, as
+a user with an existing DDP model would.
 """
 from __future__ import annotations
 
@@ -44,9 +50,11 @@ class TrainConfig:
     topology: Optional[str] = None
     comm_ctas: int = 64
     comm_threads: int = 256
+    tail_ctas: int = 148  # grid of the step's last bucket (nothing left to overlap)
     warmup_steps: int = 2
     measure_comm_error: bool = False
     cuda_graphs: bool = True  # capture each transformer block's forward and backward as CUDA graphs
+    reducer: str = "flat"  # "flat": gradient arena + bucket pipeline of this package; "ddp": torch DDP + comm hook
 
 
 class Trainer:
@@ -63,22 +71,50 @@ class Trainer:
         # bf16 working copies of the linear weights, kept in step by the optimizer kernel
         self.shadows = enable_shadows(self.model) if (device.type == "cuda" and cfg.dtype == "bf16") else {}
         self.graphed = False
-        if cfg.cuda_graphs and device.type == "cuda" and cfg.dtype == "bf16":
-            self.graphed = self._graph_blocks()
         self.state = None
-        if self.world > 1:
-            self.ddp = DDP(self.model, device_ids=[device.index] if device.type == "cuda" else None,
-                           bucket_cap_mb=cfg.bucket_cap_mb, gradient_as_bucket_view=True, broadcast_buffers=False)
-            dcfg = DynamiqConfig.from_env(method=cfg.method, seed=cfg.seed, topology=cfg.topology,
-                                          comm_ctas=cfg.comm_ctas, comm_threads=cfg.comm_threads, warmup_steps=cfg.warmup_steps,
-                                          measure_comm_error=cfg.measure_comm_error)
-            self.state = hooks.register(self.ddp, cfg.method, config=dcfg)
-            self.net = self.ddp
-        else:
-            self.ddp = None
-            self.net = self.model
-            self._flatten_grads()
+        self.ddp = None
+        self.reducer = None
+        self.net = self.model
         self.opt = FusedAdamW(self.model.parameters(), lr=cfg.lr, weight_decay=cfg.weight_decay, shadows=self.shadows)
+        if cfg.reducer not in ("flat", "ddp"):
+            raise ValueError(f"unknown reducer {cfg.reducer!r}")
+        dcfg = None
+        if self.world > 1:
+            dcfg = DynamiqConfig.from_env(method=cfg.method, seed=cfg.seed, topology=cfg.topology,
+                                          comm_ctas=cfg.comm_ctas, comm_threads=cfg.comm_threads, tail_ctas=cfg.tail_ctas,
+                                          warmup_steps=cfg.warmup_steps, measure_comm_error=cfg.measure_comm_error)
+        use_graphs = cfg.cuda_graphs and device.type == "cuda" and cfg.dtype == "bf16"
+        if cfg.reducer == "flat":
+            from ..parallel.reducer import BucketReducer
+
+            hook = state_list = None
+            if dcfg is not None:
+                state_list = hooks.build_comm_state(dcfg)
+                hook = hooks.select_comm_hook(cfg.method, dcfg.topology)
+                self.state = state_list[0]
+            # the arena has to exist before the blocks are captured: the graphs keep its addresses
+            self.reducer = BucketReducer(self.model, cfg.bucket_cap_mb, hook, state_list,
+                                         on_reduced=lambda bi, ps: self.opt.step_params(bi, ps),
+                                         direct=(device.type == "cuda" and cfg.dtype == "bf16"), install=False)
+            if self.world > 1:
+                self.reducer.broadcast_parameters(0)
+                if self.shadows:
+                    enable_shadows(self.model)
+            if use_graphs:
+                self.graphed = self._graph_blocks()
+            self.reducer.arena.zero_()
+            self.reducer.install_marks()
+            self.opt._opt_called = True  # the scheduler's "step() before optimizer.step()" check
+        else:
+            if use_graphs:
+                self.graphed = self._graph_blocks()
+            if self.world > 1:
+                self.ddp = DDP(self.model, device_ids=[device.index] if device.type == "cuda" else None,
+                               bucket_cap_mb=cfg.bucket_cap_mb, gradient_as_bucket_view=True, broadcast_buffers=False)
+                self.state = hooks.register(self.ddp, cfg.method, config=dcfg)
+                self.net = self.ddp
+            else:
+                self._flatten_grads()
         self.sched = torch.optim.lr_scheduler.LinearLR(self.opt, start_factor=1.0, end_factor=0.0,
                                                        total_iters=cfg.total_steps)
         self.step_idx = 0
@@ -118,15 +154,19 @@ class Trainer:
         warnings.filterwarnings("ignore", message="The AccumulateGrad node's stream does not match")
         try:
             with torch.autocast("cuda", dtype=torch.bfloat16, cache_enabled=False):
-                graphed = torch.cuda.make_graphed_callables(tuple(blocks), sample, num_warmup_iters=3)
+                # with a gradient arena the blocks write their parameter gradients in place and
+                # autograd sees none for them
+                graphed = torch.cuda.make_graphed_callables(tuple(blocks), sample, num_warmup_iters=3,
+                                                            allow_unused_input=self.reducer is not None)
         except Exception as e:  # fall back to eager execution, loudly
             print(f"[dynamiq] CUDA graph capture of the blocks failed ({type(e).__name__}: {e}); running eagerly",
                   flush=True)
             return False
         for i, g in enumerate(graphed):
             blocks[i] = g
-        for p in m.parameters():  # capture warm-up ran backward passes: drop their gradients
-            p.grad = None
+        if self.reducer is None:
+            for p in m.parameters():  # capture warm-up ran backward passes: drop their gradients
+                p.grad = None
         return True
 
     def _flatten_grads(self) -> None:
@@ -155,17 +195,24 @@ class Trainer:
                 loss = self.net(input_ids, labels)
         else:
             loss = self.net(input_ids, labels)
+        if self.reducer is not None:
+            self.opt.advance()
+            self.reducer.begin_step()
         loss.backward()
         if self.graphed:
             from ..utils import counters
 
             counters.add("graphed_blocks", self._launches_per_graphed_step)
-        self.opt.step()
-        self.sched.step()
-        if self.ddp is None:
-            self._flat_grad.zero_()
+        if self.reducer is not None:
+            self.reducer.finish()  # every bucket: hook, then its AdamW step, on the side stream
+            self.sched.step()
         else:
-            self.opt.zero_grad(set_to_none=False)
+            self.opt.step()
+            self.sched.step()
+            if self.ddp is None:
+                self._flat_grad.zero_()
+            else:
+                self.opt.zero_grad(set_to_none=False)
         self.step_idx += 1
         return loss.detach()
 
