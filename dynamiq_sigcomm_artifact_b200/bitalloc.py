@@ -132,6 +132,78 @@ class DynamicBitrateController:
         self.u, self.initialised, self.target = float(d["u"]), bool(d["initialised"]), float(d["target"])
 
 
+class DeviceBitrateController:
+    """The same controller with its state on the GPU: nothing is read back to the host.
+
+    ``state`` is four doubles on the device (u, initialised, last average width, last delta).  Every
+    bucket's widths come from ``torch.ops.dq.superchunk_widths`` (which also returns the scores it
+    used); after the step's last bucket the scores are sorted once and one small kernel walks the
+    bisection / adjustment with binary searches (csrc/kernels/bitalloc_ops.cu).  The update runs on the
+    stream it is called on and is published through ``ready`` (an event) for the next step's first bucket.
+    Widths come from thresholds on the score (8 from 8 up, 4 from 4 up, else 2), which is
+    :func:`qbits` without the round trip through ``log2``.
+    """
+
+    def __init__(self, target_bits: float, device, u: float = U_MAX, initialised: bool = False):
+        self.target = float(target_bits) - HEADROOM
+        self.device = torch.device(device)
+        self.state = torch.tensor([float(u), 1.0 if initialised else 0.0, 0.0, 0.0], dtype=torch.float64,
+                                  device=self.device)
+        self._scores: List[torch.Tensor] = []
+        self.ready = None  # torch.cuda.Event of the last update
+
+    def widths(self, stats: torch.Tensor) -> torch.Tensor:
+        """stats [nsc, 2] (all-reduced; energy in column 1) -> uint8 widths [nsc]; remembers the scores."""
+        from . import ops as _ops
+
+        if self.ready is not None:
+            torch.cuda.current_stream(self.device).wait_event(self.ready)
+        nsc = stats.shape[0]
+        scores = torch.empty(nsc, dtype=torch.float32, device=stats.device)
+        widths = torch.empty(nsc, dtype=torch.uint8, device=stats.device)
+        _ops.require().superchunk_widths(stats, self.state, scores, widths)
+        self._scores.append(scores)
+        return widths
+
+    def end_of_step(self) -> None:
+        from . import ops as _ops
+
+        if not self._scores:
+            return
+        s = torch.cat(self._scores) if len(self._scores) > 1 else self._scores[0]
+        self._scores = []
+        _ops.require().superchunk_bitrate_update(torch.sort(s).values, self.state, self.target)
+        self.ready = torch.cuda.Event()
+        self.ready.record(torch.cuda.current_stream(self.device))
+
+    def state_dict(self) -> dict:
+        u, init, avg, delta = self.state.tolist()  # synchronises; checkpoints only
+        return {"u": u, "initialised": bool(init), "target": self.target, "last_avg": avg, "last_delta": delta}
+
+    def load_state_dict(self, d: dict) -> None:
+        self.target = float(d.get("target", self.target))
+        self.state.copy_(torch.tensor([float(d["u"]), 1.0 if d.get("initialised", True) else 0.0,
+                                       float(d.get("last_avg", 0.0)), float(d.get("last_delta", 0.0))],
+                                      dtype=torch.float64))
+
+
+def threshold_widths(energy: torch.Tensor, thresholds: Dict[int, float]) -> torch.Tensor:
+    """uint8 width per superchunk for the threshold split, built on the device without reading a size back:
+    the group sizes follow from the element count alone (:func:`split_by_thresholds`)."""
+    n = energy.numel()
+    top = int(n * thresholds.get(8, 0.0))
+    bottom = int(n * thresholds.get(2, 0.0))
+    if top + bottom > n:
+        bottom = max(0, n - top)
+    order = torch.argsort(energy.float(), descending=True, stable=True)
+    widths = torch.full((n,), 4, dtype=torch.uint8, device=energy.device)
+    if top:
+        widths[order[:top]] = 8
+    if bottom:
+        widths[order[n - bottom:]] = 2
+    return widths
+
+
 class BucketBitPolicy:
     """Per-bucket width for the rotation codec: b-1 / b / b+1 by energy per element.
 

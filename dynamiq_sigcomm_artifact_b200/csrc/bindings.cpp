@@ -20,13 +20,13 @@ void fused_allreduce(at::Tensor bucket, at::Tensor steps, std::vector<int64_t> m
                      int64_t threads, int64_t blocks_per_shard, int64_t slot_stride, int64_t scales_off,
                      int64_t flag_base, int64_t epoch, int64_t seed, int64_t step, int64_t bucket_id,
                      double post_scale, int64_t timeout_ns, bool no_transmit, int64_t codec, double sc_lattice_max, double sc_c1, double sc_c2,
-                     c10::optional<at::Tensor> sc_lut);
+                     c10::optional<at::Tensor> sc_lut, c10::optional<at::Tensor> sc_plan);
 void fused_allreduce_local(std::vector<at::Tensor> buckets, at::Tensor steps, std::vector<at::Tensor> mailboxes,
                            std::vector<at::Tensor> flags, at::Tensor status, at::Tensor tail_ws, int64_t nslots,
                            int64_t bits, int64_t ctas, int64_t threads, int64_t blocks_per_shard, int64_t slot_stride,
                            int64_t scales_off, int64_t flag_base, int64_t epoch, int64_t seed, int64_t step,
                            int64_t bucket_id, double post_scale, int64_t timeout_ns, bool no_transmit, int64_t codec, double sc_lattice_max, double sc_c1, double sc_c2,
-                     c10::optional<at::Tensor> sc_lut);
+                     c10::optional<at::Tensor> sc_lut, c10::optional<at::Tensor> sc_plan);
 std::tuple<at::Tensor, at::Tensor, at::Tensor> norm_fwd(at::Tensor x, at::Tensor w, c10::optional<at::Tensor> b,
                                                         double eps, bool rms);
 std::tuple<at::Tensor, at::Tensor, at::Tensor> norm_bwd(at::Tensor dy, at::Tensor x, at::Tensor w, at::Tensor mean,
@@ -42,6 +42,9 @@ at::Tensor swiglu_fwd(at::Tensor in);
 at::Tensor swiglu_bwd(at::Tensor dy, at::Tensor in);
 std::tuple<at::Tensor, at::Tensor> superchunk_center(at::Tensor x, int64_t world);
 void superchunk_add_mean(at::Tensor resid, at::Tensor mean, at::Tensor out);
+void superchunk_widths(at::Tensor stats, at::Tensor state, at::Tensor s_out, at::Tensor widths);
+at::Tensor superchunk_plan(at::Tensor widths);
+void superchunk_bitrate_update(at::Tensor sorted_s, at::Tensor state, double target);
 at::Tensor rope(at::Tensor x, at::Tensor cos, at::Tensor sin, bool backward);
 void adamw_step(at::Tensor table, at::Tensor numel, at::Tensor chunk_start, int64_t total_chunks, bool param_bf16,
                 bool grad_bf16, double lr, double beta1, double beta2, double eps, double weight_decay, int64_t step,
@@ -60,6 +63,9 @@ TORCH_LIBRARY(dq, m) {
   m.def("swiglu_bwd(Tensor dy, Tensor x) -> Tensor", &dq::swiglu_bwd);
   m.def("superchunk_center(Tensor x, int world) -> (Tensor, Tensor)", &dq::superchunk_center);
   m.def("superchunk_add_mean(Tensor resid, Tensor mean, Tensor(a!) out) -> ()", &dq::superchunk_add_mean);
+  m.def("superchunk_widths(Tensor stats, Tensor state, Tensor(a!) s_out, Tensor(b!) widths) -> ()", &dq::superchunk_widths);
+  m.def("superchunk_plan(Tensor widths) -> Tensor", &dq::superchunk_plan);
+  m.def("superchunk_bitrate_update(Tensor sorted_s, Tensor(a!) state, float target) -> ()", &dq::superchunk_bitrate_update);
   m.def("rope(Tensor x, Tensor cos, Tensor sin, bool backward) -> Tensor", &dq::rope);
   m.def("adamw_step(Tensor table, Tensor numel, Tensor chunk_start, int total_chunks, bool param_bf16, bool grad_bf16, "
         "float lr, float beta1, float beta2, float eps, float weight_decay, int step, float grad_scale) -> ()", &dq::adamw_step);
@@ -73,12 +79,12 @@ TORCH_LIBRARY(dq, m) {
       "fused_allreduce(Tensor(a!) bucket, Tensor steps, int[] mail_ptrs, int[] flag_ptrs, int mailbox_bytes, "
       "int flag_words, int nslots, int status_ptr, int tail_ws_ptr, int rank, int world, int bits, int ctas, "
       "int threads, int blocks_per_shard, int slot_stride, int scales_off, int flag_base, int epoch, int seed, "
-      "int step, int bucket_id, float post_scale, int timeout_ns, bool no_transmit, int codec, float sc_lattice_max, float sc_c1, float sc_c2, Tensor? sc_lut) -> ()",
+      "int step, int bucket_id, float post_scale, int timeout_ns, bool no_transmit, int codec, float sc_lattice_max, float sc_c1, float sc_c2, Tensor? sc_lut, Tensor? sc_plan=None) -> ()",
       &dq::fused_allreduce);
   m.def(
       "fused_allreduce_local(Tensor[] buckets, Tensor steps, Tensor[] mailboxes, Tensor[] flags, Tensor status, "
       "Tensor tail_ws, int nslots, int bits, int ctas, int threads, int blocks_per_shard, int slot_stride, "
       "int scales_off, int flag_base, int epoch, int seed, int step, int bucket_id, float post_scale, "
-      "int timeout_ns, bool no_transmit, int codec, float sc_lattice_max, float sc_c1, float sc_c2, Tensor? sc_lut) -> ()",
+      "int timeout_ns, bool no_transmit, int codec, float sc_lattice_max, float sc_c1, float sc_c2, Tensor? sc_lut, Tensor? sc_plan=None) -> ()",
       &dq::fused_allreduce_local);
 }

@@ -174,4 +174,134 @@ __device__ __forceinline__ void sc_copy_in(uint8_t* tile, const uint8_t* src, in
     reinterpret_cast<unsigned long long*>(tile)[i] = __ldcg(reinterpret_cast<const unsigned long long*>(src) + i);
 }
 
+// ---- mixed widths: every superchunk of a block has its own code width (2, 4 or 8) -----------------
+//
+// Per block the host side supplies `wpack` (byte j = width of superchunk j) and the block's byte offset
+// inside the message (a prefix sum over the blocks' record bytes; any four records add up to a multiple of
+// 8 bytes because 82, 146 and 274 are all 2 mod 8).  The arithmetic per superchunk is the fixed-width
+// codec's, operation for operation, with the width as a run-time value: a record written here equals the
+// record the fixed-width codec of that width writes for the same block, tag and step.
+//
+// Constant table (fp32, device): [0..2] lattice_max, [4..6] c1, [8..10] c2 for widths 2, 4, 8 (index
+// log2(width) - 1); decode levels of width 2 at [16..20), width 4 at [20..36), width 8 at [36..292).
+constexpr int kScMixTableFloats = 292;
+
+__device__ __forceinline__ int sc_rec_bytes(int b) { return 16 * (2 * b + 1) + 2; }
+__device__ __forceinline__ int sc_mix_block_bytes(uint32_t wpack) {
+  return sc_rec_bytes(wpack & 0xFF) + sc_rec_bytes((wpack >> 8) & 0xFF) + sc_rec_bytes((wpack >> 16) & 0xFF) +
+         sc_rec_bytes((wpack >> 24) & 0xFF);
+}
+__device__ __forceinline__ int sc_mix_slot(int b) { return b == 2 ? 0 : (b == 4 ? 1 : 2); }
+__device__ __forceinline__ int sc_mix_lut_base(int b) { return b == 2 ? 16 : (b == 4 ? 20 : 36); }
+
+__device__ __forceinline__ int sc_mix_rec_base(uint32_t wpack, int g) {
+  int base = 0;
+#pragma unroll
+  for (int i = 0; i < 3; ++i)
+    if (i < g) base += sc_rec_bytes((wpack >> (8 * i)) & 0xFF);
+  return base;
+}
+
+template <bool MEE>
+__device__ __forceinline__ void sc_encode_block_mix(const float (&v)[32], uint8_t* tile, const float* table,
+                                                    uint32_t wpack, uint32_t first_call, uint32_t tag, uint32_t step,
+                                                    uint32_t k0, uint32_t k1, int lane) {
+  const int g = lane >> 3;
+  const int B = static_cast<int>((wpack >> (8 * g)) & 0xFF);
+  const int R = (1 << (B - 1)) - 1;
+  const int ti = sc_mix_slot(B);
+  const float lattice_max = __ldg(table + ti), c1 = __ldg(table + 4 + ti), c2 = __ldg(table + 8 + ti);
+  const int chunk_bytes = 2 * B + 1;
+  float x[32], s[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float am = 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      x[16 * h + k] = sc_sanitize(v[16 * h + k]);
+      am = fmaxf(am, fabsf(x[16 * h + k]));
+    }
+    s[h] = fmaxf(__fadd_rn(__fdiv_rn(am, lattice_max), 1e-7f), 1e-30f);
+  }
+  float S = fmaxf(s[0], s[1]);
+#pragma unroll
+  for (int o = 1; o < 8; o <<= 1) S = fmaxf(S, __shfl_xor_sync(0xFFFFFFFFu, S, o));
+  const __nv_bfloat16 unit_bf = __float2bfloat16_rn(fmaxf(__fdiv_rn(S, 255.0f), 1e-30f));
+  const float unit = fmaxf(__bfloat162float(unit_bf), 1e-30f);
+  uint8_t* rec = tile + sc_mix_rec_base(wpack, g);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const float q = fminf(fmaxf(ceilf(__fmul_rn(__fdiv_rn(s[h], S), 255.0f)), 1.0f), 255.0f);
+    const float dec = fmaxf(__fmul_rn(q, unit), 1e-30f);
+    U4 r = philox4x32<7>(first_call + 2u * static_cast<uint32_t>(lane) + h, 0u, tag, step, k0, k1);
+    const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+    unsigned long long acc[2] = {0ull, 0ull};
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      float y = __fdiv_rn(x[16 * h + k], dec);
+      if (MEE) {
+        const float mag = __fdiv_rn(log2f(__fadd_rn(__fdiv_rn(fabsf(y), c1), 1.0f)), c2);
+        y = y > 0.f ? mag : (y < 0.f ? -mag : 0.f);
+      }
+      const float u = __fmul_rn(__fadd_rn(static_cast<float>((rw[k >> 2] >> (8 * (k & 3))) & 0xFFu), 0.5f), 1.0f / 256.0f);
+      const float fl = floorf(y);
+      float c = fl + ((__fsub_rn(y, fl) > u) ? 1.0f : 0.0f);
+      c = fminf(fmaxf(c, static_cast<float>(-R)), static_cast<float>(R));
+      acc[k >> 3] |= static_cast<unsigned long long>(static_cast<uint32_t>(static_cast<int>(c) + R)) << ((k & 7) * B);
+    }
+    uint8_t* ch = rec + (2 * (lane & 7) + h) * chunk_bytes;
+    for (int byte = 0; byte < B; ++byte) {  // codes 0..7 fill B bytes, codes 8..15 the next B, little end first
+      ch[byte] = static_cast<uint8_t>(acc[0] >> (8 * byte));
+      ch[B + byte] = static_cast<uint8_t>(acc[1] >> (8 * byte));
+    }
+    ch[2 * B] = static_cast<uint8_t>(q);
+  }
+  if ((lane & 7) == 0) {
+    const unsigned short bits = __bfloat16_as_ushort(unit_bf);
+    rec[16 * chunk_bytes] = static_cast<uint8_t>(bits & 0xFF);
+    rec[16 * chunk_bytes + 1] = static_cast<uint8_t>(bits >> 8);
+  }
+}
+
+template <bool MEE, bool ADD>
+__device__ __forceinline__ void sc_decode_block_mix(float (&v)[32], const uint8_t* tile, const float* table,
+                                                    uint32_t wpack, int lane) {
+  const int g = lane >> 3;
+  const int B = static_cast<int>((wpack >> (8 * g)) & 0xFF);
+  const int R = (1 << (B - 1)) - 1;
+  const uint32_t mask = (1u << B) - 1u;
+  const int chunk_bytes = 2 * B + 1;
+  const float* lut = table + sc_mix_lut_base(B);
+  const uint8_t* rec = tile + sc_mix_rec_base(wpack, g);
+  const unsigned short ub = static_cast<unsigned short>(rec[16 * chunk_bytes]) |
+                            (static_cast<unsigned short>(rec[16 * chunk_bytes + 1]) << 8);
+  const float unit = fmaxf(__bfloat162float(__ushort_as_bfloat16(ub)), 1e-30f);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint8_t* ch = rec + (2 * (lane & 7) + h) * chunk_bytes;
+    const float dec = fmaxf(__fmul_rn(static_cast<float>(ch[2 * B]), unit), 1e-30f);
+    unsigned long long acc[2] = {0ull, 0ull};
+    for (int byte = 0; byte < B; ++byte) {
+      acc[0] |= static_cast<unsigned long long>(ch[byte]) << (8 * byte);
+      acc[1] |= static_cast<unsigned long long>(ch[B + byte]) << (8 * byte);
+    }
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const uint32_t code = static_cast<uint32_t>(acc[k >> 3] >> ((k & 7) * B)) & mask;
+      const float level = MEE ? __ldg(lut + code) : static_cast<float>(static_cast<int>(code) - R);
+      const float val = __fmul_rn(level, dec);
+      v[16 * h + k] = ADD ? __fadd_rn(v[16 * h + k], val) : val;
+    }
+  }
+}
+
+__device__ __forceinline__ void sc_copy_out_n(uint8_t* dst, const uint8_t* tile, int n8, int lane) {
+  for (int i = lane; i < n8; i += 32)
+    reinterpret_cast<unsigned long long*>(dst)[i] = reinterpret_cast<const unsigned long long*>(tile)[i];
+}
+__device__ __forceinline__ void sc_copy_in_n(uint8_t* tile, const uint8_t* src, int n8, int lane) {
+  for (int i = lane; i < n8; i += 32)
+    reinterpret_cast<unsigned long long*>(tile)[i] = __ldcg(reinterpret_cast<const unsigned long long*>(src) + i);
+}
+
 }  // namespace dq

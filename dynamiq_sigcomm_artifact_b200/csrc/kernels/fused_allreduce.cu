@@ -90,12 +90,15 @@ static void launch_bits(int bits, const ARParams* hp, const ARParams* dp, int nr
     case kCodecScMee: launch_sc<T, kCodecScMee>(bits, hp, dp, nranks, ctas, threads, stream); break;
     case kCodecMx: launch_mx<T>(bits, hp, dp, nranks, ctas, threads, stream); break;
     case kCodecCast: launch_cast<T>(bits, hp, dp, nranks, ctas, threads, stream); break;
+    case kCodecScMixAee: launch_one<8, T, kCodecScMixAee>(hp, dp, nranks, ctas, threads, stream); break;
+    case kCodecScMixMee: launch_one<8, T, kCodecScMixMee>(hp, dp, nranks, ctas, threads, stream); break;
     default: TORCH_CHECK(false, "unknown codec ", codec);
   }
 }
 
 static unsigned block_bytes_of(int codec, int bits) {
   if (codec == kCodecScAee || codec == kCodecScMee) return 4u * (16u * (2u * bits + 1u) + 2u);
+  if (codec == kCodecScMixAee || codec == kCodecScMixMee) return 4u * 274u;  // the widest block: four 8-bit records
   if (codec == kCodecMx) return 128u * bits + 32u;
   if (codec == kCodecCast) return 128u * bits;
   return 128u * bits;
@@ -103,7 +106,7 @@ static unsigned block_bytes_of(int codec, int bits) {
 
 // superchunk codec constants; `lut` holds the 2^bits decode levels (device, fp32)
 static void fill_sc(ARParams& p, int64_t codec, int64_t bits, double lattice_max, double c1, double c2,
-                    const c10::optional<at::Tensor>& lut) {
+                    const c10::optional<at::Tensor>& lut, const c10::optional<at::Tensor>& plan) {
   p.codec = static_cast<int>(codec);
   p.tensor_rotation = codec == kCodecRhtTc;
   p.block_bytes = block_bytes_of(static_cast<int>(codec), static_cast<int>(bits));
@@ -118,6 +121,17 @@ static void fill_sc(ARParams& p, int64_t codec, int64_t bits, double lattice_max
     p.sc_lut = lut->data_ptr<float>();
   }
   if (codec == kCodecScAee || codec == kCodecScMee) TORCH_CHECK(lattice_max > 0, "lattice_max must be positive");
+  p.sc_plan = nullptr;
+  if (codec == kCodecScMixAee || codec == kCodecScMixMee) {
+    TORCH_CHECK(lut.has_value() && lut->is_cuda() && lut->scalar_type() == at::kFloat && lut->is_contiguous() &&
+                    lut->numel() >= 292,
+                "the mixed-width codec needs its CUDA fp32 constant table (292 values)");
+    TORCH_CHECK(plan.has_value() && plan->is_cuda() && plan->scalar_type() == at::kInt && plan->is_contiguous() &&
+                    plan->numel() >= 2 * static_cast<int64_t>(p.nblocks) + 1,
+                "the mixed-width codec needs an int32 CUDA plan of nblocks + 1 offsets and nblocks packed widths");
+    p.sc_lut = lut->data_ptr<float>();
+    p.sc_plan = reinterpret_cast<const uint32_t*>(plan->data_ptr<int>());
+  }
 }
 
 static void fill_common(ARParams& p, const at::Tensor& bucket, const at::Tensor& steps, int64_t rank, int64_t world,
@@ -187,7 +201,7 @@ void fused_allreduce(at::Tensor bucket, at::Tensor steps, std::vector<int64_t> m
                      int64_t threads, int64_t blocks_per_shard, int64_t slot_stride, int64_t scales_off,
                      int64_t flag_base, int64_t epoch, int64_t seed, int64_t step, int64_t bucket_id,
                      double post_scale, int64_t timeout_ns, bool no_transmit, int64_t codec, double sc_lattice_max, double sc_c1, double sc_c2,
-                     c10::optional<at::Tensor> sc_lut) {
+                     c10::optional<at::Tensor> sc_lut, c10::optional<at::Tensor> sc_plan) {
   c10::cuda::CUDAGuard guard(bucket.device());
   TORCH_CHECK(static_cast<int64_t>(mail_ptrs.size()) == world && static_cast<int64_t>(flag_ptrs.size()) == world,
               "need one mailbox and one flag pointer per rank");
@@ -195,7 +209,7 @@ void fused_allreduce(at::Tensor bucket, at::Tensor steps, std::vector<int64_t> m
   ARParams p{};
   fill_common(p, bucket, steps, rank, world, blocks_per_shard, slot_stride, scales_off, flag_base, epoch, seed, step,
               bucket_id, post_scale, timeout_ns, status_ptr, tail_ws_ptr, no_transmit);
-  fill_sc(p, codec, bits, sc_lattice_max, sc_c1, sc_c2, sc_lut);
+  fill_sc(p, codec, bits, sc_lattice_max, sc_c1, sc_c2, sc_lut, sc_plan);
   for (int r = 0; r < world; ++r) {
     p.mail[r] = reinterpret_cast<uint8_t*>(mail_ptrs[r]);
     p.flags[r] = reinterpret_cast<uint32_t*>(flag_ptrs[r]);
@@ -216,7 +230,7 @@ void fused_allreduce_local(std::vector<at::Tensor> buckets, at::Tensor steps, st
                            int64_t bits, int64_t ctas, int64_t threads, int64_t blocks_per_shard, int64_t slot_stride,
                            int64_t scales_off, int64_t flag_base, int64_t epoch, int64_t seed, int64_t step,
                            int64_t bucket_id, double post_scale, int64_t timeout_ns, bool no_transmit, int64_t codec, double sc_lattice_max, double sc_c1, double sc_c2,
-                     c10::optional<at::Tensor> sc_lut) {
+                     c10::optional<at::Tensor> sc_lut, c10::optional<at::Tensor> sc_plan) {
   const int64_t world = static_cast<int64_t>(buckets.size());
   TORCH_CHECK(world >= 1 && world <= kMaxWorld, "1..8 ranks");
   TORCH_CHECK(steps.dim() == 3 && steps.size(0) == world, "steps must be [world, nsteps, 8]");
@@ -239,7 +253,7 @@ void fused_allreduce_local(std::vector<at::Tensor> buckets, at::Tensor steps, st
                 flag_base, epoch, seed, step, bucket_id, post_scale, timeout_ns,
                 reinterpret_cast<int64_t>(status.data_ptr()),
                 reinterpret_cast<int64_t>(tail_ws.data_ptr<float>() + r * kBlock), no_transmit);
-    fill_sc(hp[r], codec, bits, sc_lattice_max, sc_c1, sc_c2, sc_lut);
+    fill_sc(hp[r], codec, bits, sc_lattice_max, sc_c1, sc_c2, sc_lut, sc_plan);
     for (int64_t q = 0; q < world; ++q) {
       hp[r].mail[q] = static_cast<uint8_t*>(mailboxes[q].data_ptr());
       hp[r].flags[q] = reinterpret_cast<uint32_t*>(flags[q].data_ptr());

@@ -12,7 +12,10 @@ constexpr uint32_t kTagStratified = 0x4000u;  // step tag flag: stratified round
 // local operand / result of a step: keep in sync with parallel/schedules.py
 enum : int { kLocalRaw = 0, kLocalWs = 1 };
 enum : int { kOutSend = 0, kOutStore = 1, kOutFinal = 2, kOutDecode = 3 };
-enum : int { kCodecRht = 0, kCodecRhtTc = 1, kCodecScAee = 2, kCodecScMee = 3, kCodecMx = 4, kCodecCast = 5 };
+enum : int {
+  kCodecRht = 0, kCodecRhtTc = 1, kCodecScAee = 2, kCodecScMee = 3, kCodecMx = 4, kCodecCast = 5,
+  kCodecScMixAee = 6, kCodecScMixMee = 7  // superchunk records whose width (2 / 4 / 8) varies per superchunk
+};
 
 // error codes left in status[0]; status[1] = (step << 16) | cta, status[2] = slot
 enum : uint32_t { kOk = 0, kErrWaitTimeout = 1, kErrBadProgram = 2, kErrCopyTimeout = 3, kErrMmaTimeout = 4 };
@@ -40,7 +43,10 @@ struct ARParams {
   int codec;                       // host-side selector: kCodecRht / kCodecScAee / kCodecScMee
   unsigned int block_bytes;        // bytes of one encoded 1024-element block inside a message
   float sc_lattice_max, sc_c1, sc_c2;  // superchunk codec constants
-  const float* sc_lut;             // superchunk codec decode levels [2^bits] (device memory)
+  const float* sc_lut;             // superchunk codec decode levels [2^bits] (device memory); mixed widths: the
+                                   // constant table of sc_codec.cuh (kScMixTableFloats)
+  const uint32_t* sc_plan;         // mixed widths: [nblocks + 1] message offsets of the blocks in 8-byte units (a prefix
+                                   // sum), then [nblocks] packed widths (byte j = width of superchunk j of the block)
   int steps[kMaxSteps][kStepInts];
 };
 

@@ -96,9 +96,10 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
   constexpr bool TC = CODEC == kCodecRhtTc;
   constexpr bool MX = CODEC == kCodecMx;      // block-float codes (8 / 6 / 4 bit) with native conversions
   constexpr bool CAST = CODEC == kCodecCast;  // identity wire: bf16 (16) or fp32 (32) values
-  constexpr bool SC = CODEC == kCodecScAee || CODEC == kCodecScMee || MX || CAST;  // lane-contiguous record codecs
+  constexpr bool MIX = CODEC == kCodecScMixAee || CODEC == kCodecScMixMee;  // superchunk records of per-superchunk width
+  constexpr bool SC = CODEC == kCodecScAee || CODEC == kCodecScMee || MX || CAST || MIX;  // lane-contiguous record codecs
   constexpr int CB = BITS == 32 ? 32 : 16;
-  constexpr bool MEE = CODEC == kCodecScMee;
+  constexpr bool MEE = CODEC == kCodecScMee || CODEC == kCodecScMixMee;
   constexpr int SCB = (BITS == 2 || BITS == 4 || BITS == 8) ? BITS : 4;  // superchunk code width (2, 4, 8 only)
   constexpr int MXB = (BITS == 4 || BITS == 6 || BITS == 8) ? BITS : 8;  // block-float code width (4, 6, 8 only)
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -231,21 +232,32 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
       if constexpr (SC) {
         // ---- record codecs (superchunk AEE / MEE, block-float): no rotation, one record area per block ----
         constexpr unsigned kBB = CAST ? CastGeom<CB>::kBlockBytes : (MX ? MxGeom<MXB>::kBlockBytes : ScGeom<SCB>::kBlockBytes);
-        const unsigned long long boff = static_cast<unsigned long long>(bs) * kBB;
+        unsigned long long boff = static_cast<unsigned long long>(bs) * kBB;
+        uint32_t wpack = 0;
+        int mix_n8 = 0;
+        if constexpr (MIX) {  // per-block offset and widths from the plan
+          const uint32_t o0 = __ldg(p.sc_plan + blk), o1 = __ldg(p.sc_plan + blk + 1);
+          boff = static_cast<unsigned long long>(o0 - __ldg(p.sc_plan + shard_lo)) * 8ull;
+          mix_n8 = static_cast<int>(o1 - o0);
+          wpack = __ldg(p.sc_plan + p.nblocks + 1 + blk);
+        }
         const uint32_t first_call = static_cast<uint32_t>(blk) * 64u;  // Philox call index = element / 16
         auto rec_in = [&](const uint8_t* src) {
-          if constexpr (CAST) bytes_copy_in<CastGeom<CB>::kBlockBytes>(rec_tile, src, lane);
+          if constexpr (MIX) sc_copy_in_n(rec_tile, src, mix_n8, lane);
+          else if constexpr (CAST) bytes_copy_in<CastGeom<CB>::kBlockBytes>(rec_tile, src, lane);
           else if constexpr (MX) mx_copy_in<MXB>(rec_tile, src, lane);
           else sc_copy_in<SCB>(rec_tile, src, lane);
           __syncwarp();
         };
         auto rec_out = [&](uint8_t* dstp) {
-          if constexpr (CAST) bytes_copy_out<CastGeom<CB>::kBlockBytes>(dstp, rec_tile, lane);
+          if constexpr (MIX) sc_copy_out_n(dstp, rec_tile, mix_n8, lane);
+          else if constexpr (CAST) bytes_copy_out<CastGeom<CB>::kBlockBytes>(dstp, rec_tile, lane);
           else if constexpr (MX) mx_copy_out<MXB>(dstp, rec_tile, lane);
           else sc_copy_out<SCB>(dstp, rec_tile, lane);
         };
         auto rec_encode = [&]() {
-          if constexpr (CAST) cast_encode_block<CB>(v, rec_tile, lane);
+          if constexpr (MIX) sc_encode_block_mix<MEE>(v, rec_tile, p.sc_lut, wpack, first_call, tag, p.step, p.seed_lo, p.seed_hi, lane);
+          else if constexpr (CAST) cast_encode_block<CB>(v, rec_tile, lane);
           else if constexpr (MX) mx_encode_block<MXB>(v, rec_tile, lane);
           else sc_encode_block<SCB, MEE>(v, rec_tile, scp, first_call, tag, p.step, p.seed_lo, p.seed_hi, lane);
           __syncwarp();
@@ -257,7 +269,8 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
           for (int r = 0; r < nrecv; ++r) {
             const uint8_t* slot = my_mail + static_cast<unsigned long long>(recv_slot + r) * p.slot_stride;
             rec_in(slot + boff);
-            if constexpr (CAST) cast_decode_block<CB, true>(v, rec_tile, lane);
+            if constexpr (MIX) sc_decode_block_mix<MEE, true>(v, rec_tile, p.sc_lut, wpack, lane);
+            else if constexpr (CAST) cast_decode_block<CB, true>(v, rec_tile, lane);
             else if constexpr (MX) mx_decode_block<MXB, true>(v, rec_tile, lane);
             else sc_decode_block<SCB, MEE, true>(v, rec_tile, scp, lane);
             __syncwarp();
@@ -282,7 +295,8 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
           } else {
             rec_in(my_mail + static_cast<unsigned long long>(recv_slot) * p.slot_stride + boff);
           }
-          if constexpr (CAST) cast_decode_block<CB, false>(v, rec_tile, lane);
+          if constexpr (MIX) sc_decode_block_mix<MEE, false>(v, rec_tile, p.sc_lut, wpack, lane);
+          else if constexpr (CAST) cast_decode_block<CB, false>(v, rec_tile, lane);
           else if constexpr (MX) mx_decode_block<MXB, false>(v, rec_tile, lane);
           else sc_decode_block<SCB, MEE, false>(v, rec_tile, scp, lane);
           __syncwarp();
@@ -492,5 +506,12 @@ void launch_one(const ARParams* host_params, const ARParams* dev_params, int nra
   template void launch_one<BITS, __nv_bfloat16, kCodecScAee>(const ARParams*, const ARParams*, int, int, int, cudaStream_t); \
   template void launch_one<BITS, float, kCodecScMee>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);         \
   template void launch_one<BITS, __nv_bfloat16, kCodecScMee>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);
+
+// mixed-width superchunk codec: the BITS parameter is a placeholder (8, the widest record)
+#define DQ_INSTANTIATE_FUSED_ALLREDUCE_SCMIX                                                                              \
+  template void launch_one<8, float, kCodecScMixAee>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);         \
+  template void launch_one<8, __nv_bfloat16, kCodecScMixAee>(const ARParams*, const ARParams*, int, int, int, cudaStream_t); \
+  template void launch_one<8, float, kCodecScMixMee>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);         \
+  template void launch_one<8, __nv_bfloat16, kCodecScMixMee>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);
 
 }  // namespace dq

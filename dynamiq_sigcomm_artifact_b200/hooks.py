@@ -63,6 +63,11 @@ class HookState(dict):
              "stats": {k: v for k, v in self["stats"].items() if k != "buckets"}}
         if self["bit_policy"] is not None:
             d["bit_policy"] = self["bit_policy"].state_dict()
+        ctl = self["params"].get("bitrate")
+        if ctl is not None and hasattr(ctl, "state_dict"):
+            sd = ctl.state_dict()
+            if sd.get("initialised"):
+                self["params"]["bitrate_u"] = sd["u"]
         for k in ("bitrate_u",):
             if k in self["params"]:
                 d[k] = self["params"][k]

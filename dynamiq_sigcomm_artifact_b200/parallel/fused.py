@@ -36,13 +36,15 @@ def _align(x: int, a: int) -> int:
     return (x + a - 1) // a * a
 
 
-CODECS = {"rht": 0, "rht_tc": 1, "sc_aee": 2, "sc_mee": 3, "mx": 4, "cast": 5}
+CODECS = {"rht": 0, "rht_tc": 1, "sc_aee": 2, "sc_mee": 3, "mx": 4, "cast": 5, "scmix_aee": 6, "scmix_mee": 7}
 
 
 def block_bytes(bits: int, codec: str = "rht") -> int:
     """Bytes of one encoded 1024-element block inside a message (scales of the rht codec excluded)."""
     if codec.startswith("sc_"):
         return 4 * (16 * (2 * bits + 1) + 2)
+    if codec.startswith("scmix_"):  # per-superchunk widths: slots are sized for the widest block
+        return 4 * (16 * (2 * 8 + 1) + 2)
     if codec == "mx":
         return 128 * bits + 32
     return 128 * bits
@@ -94,6 +96,11 @@ def codec_args(codec: str, bits: int, device) -> tuple:
     """(codec id, lattice_max, c1, c2, lut) as the native operators take them."""
     if codec in ("rht", "rht_tc", "mx", "cast"):
         return CODECS[codec], 0.0, 0.0, 0.0, None
+    if codec.startswith("scmix_"):
+        key = (codec, 0, str(device))
+        if key not in _SC_CACHE:
+            _SC_CACHE[key] = (CODECS[codec], 1.0, 0.0, 0.0, mix_table(codec[6:], device))
+        return _SC_CACHE[key]
     key = (codec, bits, str(device))
     if key not in _SC_CACHE:
         from .codecs import SuperchunkCodec, mee_lattice
@@ -104,6 +111,20 @@ def codec_args(codec: str, bits: int, device) -> tuple:
             lut = mee_lattice(torch.arange(1 << bits, dtype=torch.float32) - c.R, c.eps).to(device).contiguous()
         _SC_CACHE[key] = (CODECS[codec], float(c.lattice_max), float(c.c1), float(c.c2), lut)
     return _SC_CACHE[key]
+
+
+def mix_table(lattice: str, device) -> torch.Tensor:
+    """Constants of the mixed-width superchunk codec as the kernel reads them (csrc/common/sc_codec.cuh):
+    lattice_max / c1 / c2 for widths 2, 4, 8 at [0..2] / [4..6] / [8..10], decode levels at 16 / 20 / 36."""
+    from .codecs import SuperchunkCodec, mee_lattice
+
+    t = torch.zeros(292, dtype=torch.float32)
+    for i, (bits, base) in enumerate(((2, 16), (4, 20), (8, 36))):
+        c = SuperchunkCodec(bits, lattice)
+        t[i], t[4 + i], t[8 + i] = float(c.lattice_max), float(c.c1), float(c.c2)
+        codes = torch.arange(1 << bits, dtype=torch.float32) - c.R
+        t[base: base + (1 << bits)] = mee_lattice(codes, c.eps) if lattice == "mee" else codes
+    return t.to(device).contiguous()
 
 
 STATUS_MESSAGES = {1: "timed out waiting for a peer's flag", 2: "malformed step program",
@@ -173,11 +194,13 @@ class FusedAllreduce:
     # -- the collective --------------------------------------------------------------------
     def allreduce_(self, bucket: torch.Tensor, bits: int, topology: str = "ring", seed: int = 0, step: int = 0,
                    bucket_id: int = 0, no_transmit: bool = False, correlated: bool = False,
-                   codec: Optional[str] = None, ctas: Optional[int] = None) -> torch.Tensor:
+                   codec: Optional[str] = None, ctas: Optional[int] = None,
+                   plan: Optional[torch.Tensor] = None) -> torch.Tensor:
         """In-place mean all-reduce of a flat fp32/bf16 CUDA tensor on the current stream.
 
-        `codec`: None (the engine's rotation codec), "sc_aee" or "sc_mee" (the hierarchical
-        superchunk codec with 2 / 4 / 8-bit codes)."""
+        `codec`: None (the engine's rotation codec), "sc_aee" / "sc_mee" (the hierarchical superchunk
+        codec with 2 / 4 / 8-bit codes), "scmix_aee" / "scmix_mee" (the same with a width per superchunk,
+        given by `plan` from ``torch.ops.dq.superchunk_plan``; `bits` is ignored), "mx", "cast"."""
         if self.world == 1:
             return bucket
         codec = codec or ("rht_tc" if self.tensor_rotation else "rht")
@@ -195,7 +218,7 @@ class FusedAllreduce:
             self.buf.local_ptr + self.off_status, self.buf.local_ptr + self.off_tail, self.rank, self.world, bits,
             grid, self.threads, lay.blocks_per_shard, lay.slot_stride, lay.scales_off,
             parity * self.flag_words_per_set, self.epoch, seed, step, bucket_id, 1.0 / self.world, self.timeout_ns,
-            no_transmit, *codec_args(codec, bits, bucket.device))
+            no_transmit, *codec_args(codec, bits, bucket.device), plan)
         counters.add("fused_allreduce")
         return bucket
 
@@ -238,7 +261,7 @@ class LocalCluster:
 
     def run(self, buckets: List[torch.Tensor], programs: torch.Tensor, bits: int, seed: int = 0, step: int = 0,
             bucket_id: int = 0, post_scale: Optional[float] = None, no_transmit: bool = False,
-            preset_flags: bool = False, codec: Optional[str] = None) -> None:
+            preset_flags: bool = False, codec: Optional[str] = None, plan: Optional[torch.Tensor] = None) -> None:
         codec = codec or ("rht_tc" if self.tensor_rotation else "rht")
         lay = Layout(buckets[0].numel(), self.world, bits, codec)
         assert buckets[0].numel() <= self.max_numel
@@ -250,7 +273,7 @@ class LocalCluster:
             buckets, programs, self.mail, self.flags, self.status, self.tail_ws, self.nslots, bits, self.ctas,
             self.threads, lay.blocks_per_shard, lay.slot_stride, lay.scales_off, 0, self.epoch, seed, step, bucket_id,
             (1.0 / self.world) if post_scale is None else post_scale, self.timeout_ns, no_transmit,
-            *codec_args(codec, bits, buckets[0].device))
+            *codec_args(codec, bits, buckets[0].device), plan)
 
     def allreduce_(self, buckets: List[torch.Tensor], bits: int, topology: str = "ring", correlated: bool = False,
                    **kw) -> List[torch.Tensor]:

@@ -12,11 +12,16 @@ Per bucket (testbed_evaluation/new_comm_hooks/comm_hooks.py:681-780, dynamic-bit
    codec of that width over the method's topology, scatter them back;
 5. add the mean of means back (K22, cuda_hadamard.cu:1351-1369).
 
-On CUDA buckets steps 1, 4 and 5 are native: ``torch.ops.dq.superchunk_center`` /
-``superchunk_add_mean`` (csrc/kernels/superchunk_ops.cu) and, per group, the persistent fused
-collective kernel with its superchunk codec (``FusedAllreduce.allreduce_(codec="sc_aee" | "sc_mee")``,
-csrc/common/sc_codec.cuh) over peer-mapped NVLink memory.  On CPU tensors (gloo) the same steps run
-on the device-agnostic backend (``torch_backend.py``).
+On CUDA buckets everything is native and nothing is read back to the host: ``superchunk_center`` /
+``superchunk_add_mean`` (csrc/kernels/superchunk_ops.cu), the widths (``superchunk_widths`` for the
+dynamic-bitrate controller whose state lives on the device, an ``argsort`` with statically known group
+sizes for the threshold table), ``superchunk_plan`` (block offsets of the message), and ONE launch of
+the persistent fused collective kernel with the mixed-width superchunk codec
+(``FusedAllreduce.allreduce_(codec="scmix_aee" | "scmix_mee", plan=...)``, csrc/common/sc_codec.cuh): the
+rows stay in place instead of being gathered into three width groups and scattered back.  The
+three-group form remains for the debug variants that drop groups (``fixed`` on a mixed table,
+``no_compress``).  On CPU tensors (gloo) the same steps run on the device-agnostic backend
+(``torch_backend.py``).
 """
 from __future__ import annotations
 
@@ -58,6 +63,9 @@ def superchunk_allreduce(state, bucket) -> torch.futures.Future:
         return fut
     step, index = int(state["batch_idx"]), bucket.index()
     native = buf.is_cuda
+    dropped = spec.fixed and (spec.thresholds.get(8, 0.0) > 0 or spec.thresholds.get(2, 0.0) > 0)
+    if native and not spec.no_compress and not dropped:
+        return _native_mixed(state, bucket)
     if native:
         from .. import ops as _ops
         from ..hooks import _engine
@@ -117,4 +125,53 @@ def superchunk_allreduce(state, bucket) -> torch.futures.Future:
         params["bitrate_u"] = ctl.u
         params["bitrate_last_avg_bits"] = ctl.last_avg
     fut.set_result(buf)
+    return fut
+
+
+def _native_mixed(state, bucket) -> torch.futures.Future:
+    """CUDA path: centre -> all-reduce stats -> widths -> plan -> one mixed-width collective -> add mean,
+    on the hook's communication stream, without a device-to-host read."""
+    from .. import ops as _ops
+    from ..hooks import _engine, _grid
+    from ..utils import counters
+
+    spec, cfg, group = state["spec"], state["config"], state["group"]
+    world = dist.get_world_size(group)
+    buf = bucket.buffer()
+    step, index = int(state["batch_idx"]), bucket.index()
+    dq = _ops.require()
+    eng = _engine(state)
+    stream = state["comm_stream"]
+    stream.wait_stream(torch.cuda.current_stream(buf.device))
+    fut = torch.futures.Future(devices=[buf.device])
+    params = state["params"]
+    with torch.cuda.stream(stream):
+        flat, stats = dq.superchunk_center(buf.reshape(-1), world)
+        counters.add("superchunk_center")
+        dist.all_reduce(stats, group=group)
+        if spec.dynamic_bitrate:
+            ctl = params.get("bitrate")
+            if ctl is None:
+                ctl = params["bitrate"] = bitalloc.DeviceBitrateController(
+                    spec.bits, buf.device, u=float(params.get("bitrate_u", bitalloc.U_MAX)),
+                    initialised="bitrate_u" in params)
+            widths = ctl.widths(stats)
+            counters.add("superchunk_widths")
+        else:
+            widths = bitalloc.threshold_widths(stats[:, 1], spec.thresholds)
+        plan = dq.superchunk_plan(widths)
+        counters.add("superchunk_plan")
+        eng.ensure_capacity(flat.numel())
+        eng.allreduce_(flat, 8, spec.topology, cfg.seed, step, (index << 2) | 3, no_transmit=spec.compute_only,
+                       codec=f"scmix_{spec.lattice}", plan=plan, ctas=_grid(state, bucket))
+        dq.superchunk_add_mean(flat, stats[:, 0].contiguous(), buf.reshape(-1))
+        counters.add("superchunk_add_mean")
+        st = state["stats"]
+        st["collectives"] += 1
+        st["buckets"][index] = {"numel": buf.numel(), "mixed_widths": True}
+        if spec.dynamic_bitrate and bucket.is_last():
+            ctl.end_of_step()
+            counters.add("superchunk_bitrate_update")
+        buf.record_stream(stream)
+        fut.set_result(buf)
     return fut
