@@ -197,10 +197,11 @@ def threshold_widths(energy: torch.Tensor, thresholds: Dict[int, float]) -> torc
         bottom = max(0, n - top)
     order = torch.argsort(energy.float(), descending=True, stable=True)
     widths = torch.full((n,), 4, dtype=torch.uint8, device=energy.device)
+    # index_fill_ takes the value as a scalar argument: no host-to-device copy (and none of its stream syncs)
     if top:
-        widths[order[:top]] = 8
+        widths.index_fill_(0, order[:top], 8)
     if bottom:
-        widths[order[n - bottom:]] = 2
+        widths.index_fill_(0, order[n - bottom:], 2)
     return widths
 
 

@@ -90,6 +90,17 @@ def _signs(n: int, seed: int, device) -> torch.Tensor:
     return 1.0 - 2.0 * b.float()
 
 
+def _p2p_mean(state, x: torch.Tensor, wire_bits: int, spec, step: int, bucket_id: int) -> torch.Tensor:
+    """In-place mean of a flat fp32 CUDA tensor over the fused kernel's identity wire (bf16 or fp32)."""
+    from ..hooks import _engine
+
+    eng = _engine(state)
+    eng.ensure_capacity(x.numel())
+    eng.allreduce_(x, wire_bits, spec.topology, state["config"].seed, step, bucket_id,
+                   no_transmit=spec.compute_only, codec="cast")
+    return x
+
+
 def thc_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
     """THC: randomized Hadamard transform of power-of-two partitions, uniform stochastic
     quantisation to `quantization_levels` bins over +-T * max||g|| / sqrt(d), bins summed exactly,
@@ -121,7 +132,12 @@ def thc_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tenso
         u = (uniform_bytes(d, ((index & 0xFFFF) << 16) | part, step, cfg.seed, buf.device).float() + 0.5) / 256.0
         t = (y.clamp(-rng, rng) + rng) / (2 * rng) * (levels - 1)
         bins = torch.floor(t + u).clamp_(0, levels - 1)
-        total = allreduce_torch(bins, IntBinsCodec(), spec.topology, group, transmit=not spec.compute_only) * world
+        if bins.is_cuda:
+            # integer bins over this package's point-to-point kernel: bf16 carries sums up to 256 exactly
+            wire = 16 if world * (levels - 1) <= 256 else 32
+            total = _p2p_mean(state, bins, wire, spec, step, ((index & 0xFFF) << 4) | (part & 0xF)) * world
+        else:
+            total = allreduce_torch(bins, IntBinsCodec(), spec.topology, group, transmit=not spec.compute_only) * world
         mean = (total / (levels - 1) * (2 * rng) - world * rng) / world
         mean[0] = first[0] / world
         out = fwht_(mean) / math.sqrt(d) * s
@@ -162,7 +178,11 @@ def omnireduce_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torc
     out = torch.zeros_like(rows)
     if union.numel():
         dense = rows.index_select(0, union).reshape(-1)
-        red = allreduce_torch(dense, CastCodec(torch.bfloat16), spec.topology, group, transmit=not spec.compute_only)
+        if dense.is_cuda:
+            red = _p2p_mean(state, dense, 16, spec, int(state["batch_idx"]), index)
+        else:
+            red = allreduce_torch(dense, CastCodec(torch.bfloat16), spec.topology, group,
+                                  transmit=not spec.compute_only)
         out.index_copy_(0, union, red.view(-1, 256))
     real = union.numel() / nrows
     ratio = min(max(real / target, 0.6), 1 / 0.6)
