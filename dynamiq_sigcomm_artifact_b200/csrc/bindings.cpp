@@ -42,6 +42,7 @@ at::Tensor swiglu_fwd(at::Tensor in);
 at::Tensor swiglu_bwd(at::Tensor dy, at::Tensor in);
 std::tuple<at::Tensor, at::Tensor> superchunk_center(at::Tensor x, int64_t world);
 void superchunk_add_mean(at::Tensor resid, at::Tensor mean, at::Tensor out);
+void fwht_levels_(at::Tensor x, int64_t first, int64_t nlevels, double scale);
 void superchunk_widths(at::Tensor stats, at::Tensor state, at::Tensor s_out, at::Tensor widths);
 at::Tensor superchunk_plan(at::Tensor widths);
 void superchunk_bitrate_update(at::Tensor sorted_s, at::Tensor state, double target);
@@ -63,6 +64,7 @@ TORCH_LIBRARY(dq, m) {
   m.def("swiglu_bwd(Tensor dy, Tensor x) -> Tensor", &dq::swiglu_bwd);
   m.def("superchunk_center(Tensor x, int world) -> (Tensor, Tensor)", &dq::superchunk_center);
   m.def("superchunk_add_mean(Tensor resid, Tensor mean, Tensor(a!) out) -> ()", &dq::superchunk_add_mean);
+  m.def("fwht_levels_(Tensor(a!) x, int first, int nlevels, float scale) -> ()", &dq::fwht_levels_);
   m.def("superchunk_widths(Tensor stats, Tensor state, Tensor(a!) s_out, Tensor(b!) widths) -> ()", &dq::superchunk_widths);
   m.def("superchunk_plan(Tensor widths) -> Tensor", &dq::superchunk_plan);
   m.def("superchunk_bitrate_update(Tensor sorted_s, Tensor(a!) state, float target) -> ()", &dq::superchunk_bitrate_update);

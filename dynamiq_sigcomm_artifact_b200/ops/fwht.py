@@ -56,3 +56,41 @@ def ifwht1024(y: torch.Tensor, seed: int = 0, step: int = 0, bucket: int = 0, si
     n = x.numel()
     reps = (n + BLOCK - 1) // BLOCK
     return (x.reshape(-1) * s.repeat(reps)[:n]).reshape(y.shape)
+
+
+def fwht_pow2(x: torch.Tensor, normalize: bool = False) -> torch.Tensor:
+    """Walsh-Hadamard transform (Sylvester order) of a flat tensor whose length d is a power of two.
+
+    CUDA, d >= 4096: the tcgen05 kernel transforms the 1024-blocks (levels 0..9), then
+    ``fwht_levels_`` (csrc/kernels/fwht_strided.cu) applies the remaining log2(d) - 10 levels five at a
+    time, each pass streaming the array once.  Shorter CUDA tensors use ``fwht_levels_`` alone; CPU
+    tensors a PyTorch butterfly.  No host synchronisation.  ``normalize`` divides by sqrt(d)."""
+    d = x.numel()
+    if d & (d - 1):
+        raise ValueError(f"length must be a power of two, got {d}")
+    k = d.bit_length() - 1
+    scale = (1.0 / (2.0 ** (k / 2.0))) if normalize else 1.0
+    if not x.is_cuda:
+        v = x.reshape(-1).float().clone()
+        h = 1
+        while h < d:
+            w = v.view(d // (2 * h), 2, h)
+            a, b = w[:, 0, :].clone(), w[:, 1, :].clone()
+            w[:, 0, :], w[:, 1, :] = a + b, a - b
+            h *= 2
+        return (v * scale).reshape(x.shape)
+    ops = require()
+    if d >= TILE:
+        y = fwht1024(x.reshape(-1), signs=False, normalize=False, check=False).contiguous()
+        level = 10
+    else:
+        y = x.reshape(-1).float().clone()
+        level = 0
+    if level == k:
+        return (y * scale).reshape(x.shape) if scale != 1.0 else y.reshape(x.shape)
+    while level < k:
+        step = min(5, k - level)
+        ops.fwht_levels_(y, level, step, scale if level + step == k else 1.0)
+        counters.add("fwht_levels")
+        level += step
+    return y.reshape(x.shape)

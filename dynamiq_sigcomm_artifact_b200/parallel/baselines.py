@@ -90,6 +90,15 @@ def _signs(n: int, seed: int, device) -> torch.Tensor:
     return 1.0 - 2.0 * b.float()
 
 
+def _rotate(x: torch.Tensor) -> torch.Tensor:
+    """Orthonormal Walsh-Hadamard transform of a power-of-two vector (native kernels on CUDA)."""
+    if x.is_cuda:
+        from ..ops.fwht import fwht_pow2
+
+        return fwht_pow2(x, normalize=True)
+    return fwht_(x) / math.sqrt(x.numel())
+
+
 def _p2p_mean(state, x: torch.Tensor, wire_bits: int, spec, step: int, bucket_id: int) -> torch.Tensor:
     """In-place mean of a flat fp32 CUDA tensor over the fused kernel's identity wire (bf16 or fp32)."""
     from ..hooks import _engine
@@ -122,14 +131,20 @@ def thc_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tenso
         d = max(64, 1 << (m - 1).bit_length())
         x = torch.zeros(d, dtype=torch.float32, device=buf.device)
         x[:m] = flat[pos: pos + m].float()
-        s = _signs(d, cfg.seed + 7919 * part, buf.device)
-        y = fwht_(x * s) / math.sqrt(d)
+        cache = state["params"].setdefault("thc_signs", {})
+        s = cache.get((index, part, d))
+        if s is None:  # fixed per (bucket, partition): kept as int8
+            s = cache[(index, part, d)] = _signs(d, cfg.seed + 7919 * part, buf.device).to(torch.int8)
+        y = _rotate(x * s)
         norm = x.norm().reshape(1)
         dist.all_reduce(norm, op=dist.ReduceOp.MAX, group=group)
         first = y[:1].clone()
         dist.all_reduce(first, group=group)
         rng = (THC_T * norm / math.sqrt(d)).clamp_min(1e-30)
-        u = (uniform_bytes(d, ((index & 0xFFFF) << 16) | part, step, cfg.seed, buf.device).float() + 0.5) / 256.0
+        if buf.is_cuda:  # rounding offsets are private to a rank: the device generator is enough
+            u = torch.rand(d, device=buf.device)
+        else:
+            u = (uniform_bytes(d, ((index & 0xFFFF) << 16) | part, step, cfg.seed, buf.device).float() + 0.5) / 256.0
         t = (y.clamp(-rng, rng) + rng) / (2 * rng) * (levels - 1)
         bins = torch.floor(t + u).clamp_(0, levels - 1)
         if bins.is_cuda:
@@ -140,7 +155,7 @@ def thc_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tenso
             total = allreduce_torch(bins, IntBinsCodec(), spec.topology, group, transmit=not spec.compute_only) * world
         mean = (total / (levels - 1) * (2 * rng) - world * rng) / world
         mean[0] = first[0] / world
-        out = fwht_(mean) / math.sqrt(d) * s
+        out = _rotate(mean) * s
         flat[pos: pos + m] = out[:m].to(buf.dtype)
         pos += m
         part += 1

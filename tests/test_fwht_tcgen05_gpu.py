@@ -46,3 +46,19 @@ def test_fwht_roundtrip_and_padding():
     assert y.shape == x.shape and back.shape == x.shape
     cpu = fwht1024(full.cpu(), seed=5)
     assert torch.allclose(yf.cpu(), cpu, atol=2e-4)
+
+
+@pytest.mark.parametrize("log2d", [6, 9, 10, 12, 13, 17, 20])
+def test_whole_vector_transform_matches_butterflies(log2d):
+    """Tensor-core 1024-blocks + strided upper levels = the plain butterfly transform of the whole vector."""
+    from dynamiq_sigcomm_artifact_b200.ops.fwht import fwht_pow2
+
+    d = 1 << log2d
+    g = torch.Generator().manual_seed(log2d)
+    x = torch.randn(d, generator=g)
+    want = fwht_pow2(x.double().float(), normalize=True)  # CPU butterflies
+    got = fwht_pow2(x.cuda(), normalize=True).cpu()
+    assert float((got - want).abs().max()) < 2e-5 * max(1.0, float(want.abs().max()))
+    # orthonormal and an involution
+    back = fwht_pow2(got.cuda(), normalize=True).cpu()
+    assert float((back - x).abs().max()) < 5e-5
