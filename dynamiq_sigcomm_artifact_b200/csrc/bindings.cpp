@@ -38,6 +38,7 @@ std::tuple<at::Tensor, at::Tensor> fwht1024_tcgen05(at::Tensor x, int64_t seed, 
                                                     bool apply_signs, double scale, int64_t ctas);
 at::Tensor bins_to_bits(at::Tensor bins, int64_t nbits);
 at::Tensor bits_to_bins(at::Tensor words, int64_t nbits, int64_t n);
+at::Tensor colsum(at::Tensor x, c10::optional<at::Tensor> out);
 at::Tensor swiglu_fwd(at::Tensor in);
 at::Tensor swiglu_bwd(at::Tensor dy, at::Tensor in);
 std::tuple<at::Tensor, at::Tensor> superchunk_center(at::Tensor x, int64_t world);
@@ -60,6 +61,7 @@ TORCH_LIBRARY(dq, m) {
   m.def("fwht1024_tcgen05(Tensor x, int seed, int step, int bucket, bool apply_signs, float scale, int ctas) -> (Tensor, Tensor)", &dq::fwht1024_tcgen05);
   m.def("bins_to_bits(Tensor bins, int nbits) -> Tensor", &dq::bins_to_bits);
   m.def("bits_to_bins(Tensor words, int nbits, int n) -> Tensor", &dq::bits_to_bins);
+  m.def("colsum(Tensor x, Tensor(a!)? out=None) -> Tensor(a!)", &dq::colsum);
   m.def("swiglu_fwd(Tensor x) -> Tensor", &dq::swiglu_fwd);
   m.def("swiglu_bwd(Tensor dy, Tensor x) -> Tensor", &dq::swiglu_bwd);
   m.def("superchunk_center(Tensor x, int world) -> (Tensor, Tensor)", &dq::superchunk_center);

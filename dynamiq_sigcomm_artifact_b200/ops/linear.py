@@ -42,11 +42,19 @@ class _ShadowLinearFn(torch.autograd.Function):
             torch.mm(dy2.t(), x2, out_dtype=torch.float32, out=ctx.wg)
         elif ctx.needs_input_grad[1]:
             dw = torch.mm(dy2.t(), x2, out_dtype=torch.float32)
-        if ctx.has_bias:
-            if ctx.bg is not None:
-                torch.sum(dy2, dim=0, dtype=torch.float32, out=ctx.bg)
-            elif ctx.needs_input_grad[3]:
+        if ctx.has_bias and (ctx.bg is not None or ctx.needs_input_grad[3]):
+            if dy2.shape[1] % 4 == 0 and dy2.is_contiguous() and dy2.data_ptr() % 16 == 0:
+                from . import require  # native column sum (csrc/kernels/colsum.cu)
+                from ..utils import counters
+
+                db = require().colsum(dy2, ctx.bg)
+                counters.add("colsum", 2)
+            elif ctx.bg is not None:
+                db = torch.sum(dy2, dim=0, dtype=torch.float32, out=ctx.bg)
+            else:
                 db = dy2.sum(dim=0, dtype=torch.float32)
+            if ctx.bg is not None:
+                db = None
         return dx, dw, None, db
 
 

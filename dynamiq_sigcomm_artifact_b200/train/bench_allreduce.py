@@ -195,10 +195,38 @@ def run_kernels(args) -> None:
                    "ctas": args.ctas, "threads": args.threads, "rotation": args.rotation}
             rows.append(row)
             print(json.dumps(row), flush=True)
-    # the tensor-core Hadamard kernel on its own: reads and writes every element once
     from ..ops import require
 
     dq = require()
+    # the other wire codecs of the same kernel: superchunk records with a width per superchunk (the
+    # reference's 5-bit threshold mixture), block-float fp8, the bf16 identity wire
+    nsc = (numel + 255) // 256
+    g = torch.Generator().manual_seed(args.seed)
+    wsel = torch.rand(nsc, generator=g)
+    widths = torch.where(wsel < 0.35, 8, torch.where(wsel < 0.80, 4, 2)).to(torch.uint8).to(dev)
+    plan = dq.superchunk_plan(widths)
+    wire_mix = float(plan[(nsc + 3) // 4].item()) * 8.0  # bytes of the whole mixed message
+    cl = LocalCluster(1, numel, ctas=args.ctas, threads=args.threads, device=dev)
+    work = torch.empty_like(x)
+    for codec, cbits, msg, kw in (("scmix_mee", 8, wire_mix, {"plan": plan}), ("mx", 8, numel * 1.03125, {}),
+                                  ("cast", 16, numel * 2.0, {})):
+        progs = {
+            "encode": (sch.Step(shard=0, out=sch.OUT_SEND, dst=0, send_slot=0, tag=sch.TAG_ENCODE), 4 * numel + msg),
+            "hop": (sch.Step(shard=0, recv_slot=0, nrecv=1, out=sch.OUT_SEND, dst=0, send_slot=1,
+                             tag=sch.TAG_ENCODE + 1), 4 * numel + 2 * msg),
+            "decode": (sch.Step(shard=0, recv_slot=0, nrecv=1, out=sch.OUT_DECODE), 4 * numel + msg),
+        }
+        for name, (step, nbytes) in progs.items():
+            prog = torch.tensor([[step.as_ints()]], dtype=torch.int32)
+            ms = time_op(lambda: cl.run([work], prog, cbits, seed=args.seed, preset_flags=True, codec=codec, **kw),
+                         lambda: work.copy_(x), args.iters, args.warmup)
+            cl.check()
+            row = {"kernel": f"{codec}_{name}", "bits": cbits, "numel": numel, "ms": ms, "gbs": nbytes / ms / 1e6,
+                   "gelem_s": numel / ms / 1e6, "hbm_fraction_of_measured": nbytes / ms / 1e6 / hbm,
+                   "ctas": args.ctas, "threads": args.threads}
+            rows.append(row)
+            print(json.dumps(row), flush=True)
+    # the tensor-core Hadamard kernel on its own: reads and writes every element once
     n4 = numel // 4096 * 4096
     xin = x[:n4].contiguous()
     ms = time_op(lambda: dq.fwht1024_tcgen05(xin, args.seed, 0, 0, True, 1.0 / 32.0, 0), lambda: None, args.iters,

@@ -85,6 +85,22 @@ def main(argv=None) -> None:
     timed("superchunk_center_64Mi", lambda: dq.superchunk_center(xs, 8), xs.numel() * 8 + xs.numel() // 32)
     bins = torch.randint(0, 16, (64 << 20,), dtype=torch.uint8, device=dev)
     timed("bins_to_bits_4bit_64Mi", lambda: dq.bins_to_bits(bins, 4), bins.numel() * 1.5)
+    # bit allocation of the superchunk codec: 64 Mi elements = 256 Ki superchunks
+    _, stats = dq.superchunk_center(xs, 8)
+    nsc = stats.shape[0]
+    state = torch.tensor([3.0, 1.0, 0.0, 0.0], dtype=torch.float64, device=dev)
+    scores = torch.empty(nsc, device=dev)
+    widths = torch.empty(nsc, dtype=torch.uint8, device=dev)
+    timed("superchunk_widths_256Ki", lambda: dq.superchunk_widths(stats, state, scores, widths), nsc * 13)
+    timed("superchunk_plan_256Ki", lambda: dq.superchunk_plan(widths), nsc * 3)
+    sorted_scores = torch.sort(scores).values
+    timed("superchunk_bitrate_update_256Ki", lambda: dq.superchunk_bitrate_update(sorted_scores, state, 4.375), nsc * 4)
+    # upper levels of a 2^23-point Walsh-Hadamard transform (THC partitions): levels 10..22 in three passes
+    v = torch.randn(1 << 23, device=dev)
+    timed("fwht_levels_2p23_five_levels", lambda: dq.fwht_levels_(v, 10, 5, 1.0), v.numel() * 8)
+    from ..ops.fwht import fwht_pow2
+
+    timed("fwht_pow2_2p23_whole_vector", lambda: fwht_pow2(v), v.numel() * 8 * 4)
 
 
 if __name__ == "__main__":

@@ -183,3 +183,21 @@ def test_master_linear_matches_autocast_linear_and_optimizer_keeps_shadow():
     opt = FusedAdamW(lin.parameters(), lr=1e-2, shadows=shadows)
     opt.step()
     assert torch.equal(lin.shadow, lin.weight.to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("rows,cols,dtype", [(8192, 768, torch.bfloat16), (300, 3072, torch.bfloat16),
+                                             (17, 132, torch.float32), (1, 4, torch.bfloat16)])
+def test_colsum_matches_torch(rows, cols, dtype):
+    from dynamiq_sigcomm_artifact_b200 import ops
+
+    dq = ops.require()
+    g = torch.Generator().manual_seed(rows + cols)
+    x = torch.randn(rows, cols, generator=g).to(dtype).cuda()
+    want = x.float().sum(dim=0)
+    got = dq.colsum(x, None)
+    assert got.dtype == torch.float32 and got.shape == (cols,)
+    assert torch.allclose(got, want, rtol=1e-4, atol=1e-3)
+    out = torch.full((cols,), 7.0, device="cuda")
+    ret = dq.colsum(x, out)
+    assert ret.data_ptr() == out.data_ptr() and torch.allclose(out, want, rtol=1e-4, atol=1e-3)
+    assert torch.equal(dq.colsum(x, None), got), "two runs must agree bit for bit"
