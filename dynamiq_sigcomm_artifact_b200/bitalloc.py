@@ -187,6 +187,63 @@ class DeviceBitrateController:
                                       dtype=torch.float64))
 
 
+KTH_INIT, KTH_SMALLER_INIT = 1.1562e-4, 2.6375e-06
+
+
+class MomentumThresholds:
+    """Widths from two energy thresholds that follow the step's quantiles with momentum.
+
+    A superchunk is sent at 8 bits if its energy exceeds ``kth``, at 2 bits if it is below
+    ``kth_smaller``, else at 4.  After the step's last bucket all energies of the step are sorted once
+    (descending) and ``kth <- 0.25 * E[int(n * t8)] + 0.75 * kth``, ``kth_smaller <- 0.25 * E[int(n * (t8 +
+    t4))] + 0.75 * kth_smaller`` (simulations_llm/new_comm_hooks/comm_hooks.py:326-370, initial values
+    :498-499).  No per-bucket sort and, on CUDA, no value ever read back: the thresholds are a device tensor.
+    """
+
+    def __init__(self, thresholds: Dict[int, float], device="cpu", kth: float = KTH_INIT,
+                 kth_smaller: float = KTH_SMALLER_INIT):
+        self.t8 = float(thresholds.get(8, 0.0))
+        self.t4 = float(thresholds.get(4, 0.0))
+        self.device = torch.device(device)
+        self.state = torch.tensor([kth, kth_smaller], dtype=torch.float32, device=self.device)
+        self._energies: List[torch.Tensor] = []
+        self.ready = None
+
+    def widths(self, energy: torch.Tensor) -> torch.Tensor:
+        if self.ready is not None and energy.is_cuda:
+            torch.cuda.current_stream(energy.device).wait_event(self.ready)
+        e = energy.float()
+        self._energies.append(e)
+        w = (e > self.state[0]).to(torch.uint8) * 4 + 4 - (e < self.state[1]).to(torch.uint8) * 2
+        return w.to(torch.uint8)
+
+    def groups(self, energy: torch.Tensor) -> Dict[int, torch.Tensor]:
+        """Row indices per width (the three-group form used on CPU tensors)."""
+        w = self.widths(energy)
+        return {b: torch.nonzero(w == b, as_tuple=False).reshape(-1) for b in (8, 4, 2)}
+
+    def end_of_step(self) -> None:
+        if not self._energies:
+            return
+        e = torch.cat(self._energies) if len(self._energies) > 1 else self._energies[0]
+        self._energies = []
+        n = e.numel()
+        srt = torch.sort(e, descending=True).values
+        i8 = min(n - 1, int(n * self.t8))
+        i4 = min(n - 1, int(n * (self.t8 + self.t4)))
+        self.state.mul_(0.75).add_(0.25 * torch.stack([srt[i8], srt[i4]]))
+        if e.is_cuda:
+            self.ready = torch.cuda.Event()
+            self.ready.record(torch.cuda.current_stream(e.device))
+
+    def state_dict(self) -> dict:
+        kth, small = self.state.tolist()
+        return {"kth": kth, "kth_smaller": small}
+
+    def load_state_dict(self, d: dict) -> None:
+        self.state.copy_(torch.tensor([float(d["kth"]), float(d["kth_smaller"])], dtype=torch.float32))
+
+
 def threshold_widths(energy: torch.Tensor, thresholds: Dict[int, float]) -> torch.Tensor:
     """uint8 width per superchunk for the threshold split, built on the device without reading a size back:
     the group sizes follow from the element count alone (:func:`split_by_thresholds`)."""

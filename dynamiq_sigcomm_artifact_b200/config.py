@@ -42,6 +42,7 @@ class MethodSpec:
     bits: int = 5  # nominal average code width
     fixed: bool = False  # superchunk: only the 4-bit group is communicated
     dynamic_bitrate: bool = False
+    momentum: bool = False  # superchunk: widths from two energy thresholds tracked with momentum across steps
     topology: str = "ring"  # ring | butterfly | direct
     correlated: bool = False  # stratified uniforms across ranks
     no_compress: bool = False  # run the selection logic but skip the collective (debug)
@@ -76,7 +77,8 @@ def parse_method(name: str, topology: Optional[str] = None) -> MethodSpec:
         return MethodSpec(hook="bf16", bits=16, **common)
     if "dynamiq" in low:
         bits = _bits_in(low, 5)
-        family = "superchunk" if ("superchunk" in low or "mee" in low or "bitrate" in low or "fixed" in low) else "rht"
+        family = "superchunk" if ("superchunk" in low or "mee" in low or "bitrate" in low or "fixed" in low
+                                  or "momentum" in low) else "rht"
         if "rht" in low:
             family = "rht"
         lattice = "aee" if "aee" in low else "mee"
@@ -86,6 +88,7 @@ def parse_method(name: str, topology: Optional[str] = None) -> MethodSpec:
         return MethodSpec(hook="dynamiq_bitrate" if "bitrate" in low else "dynamiq", family=family,
                           lattice=lattice, bits=bits, fixed=fixed, dynamic_bitrate="bitrate" in low,
                           correlated="correlated" in low, no_compress="no_compress" in low,
+                          momentum="momentum" in low,
                           thresholds=thresholds, **common)
     if "fp8" in low:
         return MethodSpec(hook="mxfp8", bits=8, **common)

@@ -89,6 +89,11 @@ def superchunk_allreduce(state, bucket) -> torch.futures.Future:
                 ctl.u, ctl.initialised = float(params["bitrate_u"]), True
         ctl.observe(energy)
         groups = bitalloc.split_by_bitrate(energy, ctl.u)
+    elif spec.momentum and not spec.fixed:
+        mom = params.get("momentum")
+        if mom is None:
+            mom = params["momentum"] = bitalloc.MomentumThresholds(spec.thresholds, energy.device)
+        groups = mom.groups(energy)
     else:
         groups = bitalloc.split_by_thresholds(energy, spec.thresholds, fixed=spec.fixed)
     st = state["stats"]
@@ -124,6 +129,8 @@ def superchunk_allreduce(state, bucket) -> torch.futures.Future:
         ctl.end_of_step()
         params["bitrate_u"] = ctl.u
         params["bitrate_last_avg_bits"] = ctl.last_avg
+    if "momentum" in params and bucket.is_last():
+        params["momentum"].end_of_step()
     fut.set_result(buf)
     return fut
 
@@ -157,6 +164,11 @@ def _native_mixed(state, bucket) -> torch.futures.Future:
                     initialised="bitrate_u" in params)
             widths = ctl.widths(stats)
             counters.add("superchunk_widths")
+        elif spec.momentum and not spec.fixed:
+            mom = params.get("momentum")
+            if mom is None:
+                mom = params["momentum"] = bitalloc.MomentumThresholds(spec.thresholds, buf.device)
+            widths = mom.widths(stats[:, 1])
         else:
             widths = bitalloc.threshold_widths(stats[:, 1], spec.thresholds)
         plan = dq.superchunk_plan(widths)
@@ -172,6 +184,8 @@ def _native_mixed(state, bucket) -> torch.futures.Future:
         if spec.dynamic_bitrate and bucket.is_last():
             ctl.end_of_step()
             counters.add("superchunk_bitrate_update")
+        if "momentum" in params and bucket.is_last():
+            params["momentum"].end_of_step()
         buf.record_stream(stream)
         fut.set_result(buf)
     return fut

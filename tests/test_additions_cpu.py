@@ -1,0 +1,56 @@
+"""Momentum thresholds, command-file poller, THC constants."""
+import os
+
+import torch
+
+from dynamiq_sigcomm_artifact_b200 import bitalloc
+from dynamiq_sigcomm_artifact_b200.config import parse_method
+from dynamiq_sigcomm_artifact_b200.launch.poller import CommandFilePoller
+from dynamiq_sigcomm_artifact_b200.parallel import thc_tables
+
+
+def test_momentum_thresholds_track_quantiles():
+    spec = parse_method("dynamiQ_mee_5bit_momentum")
+    assert spec.family == "superchunk" and spec.momentum and not spec.dynamic_bitrate
+    thr = {8: 0.2, 4: 0.6, 2: 0.2}
+    m = bitalloc.MomentumThresholds(thr)
+    g = torch.Generator().manual_seed(0)
+    frac = None
+    for _ in range(40):
+        e1, e2 = torch.exp(torch.randn(3000, generator=g) * 2 - 9), torch.exp(torch.randn(1000, generator=g) * 2 - 9)
+        w = torch.cat([m.widths(e1), m.widths(e2)])
+        assert set(w.tolist()) <= {2, 4, 8}
+        frac = [(w == b).float().mean().item() for b in (8, 4, 2)]
+        m.end_of_step()
+    assert abs(frac[0] - 0.2) < 0.05 and abs(frac[1] - 0.6) < 0.06 and abs(frac[2] - 0.2) < 0.05, frac
+    sd = m.state_dict()
+    m2 = bitalloc.MomentumThresholds(thr)
+    m2.load_state_dict(sd)
+    assert torch.equal(m2.state, m.state)
+    gr = m2.groups(torch.tensor([1.0, 1e-9, sd["kth"] * 0.5]))
+    assert gr[8].tolist() == [0] and gr[2].tolist() == [1] and gr[4].tolist() == [2]
+
+
+def test_command_file_poller_runs_new_lines_once(tmp_path):
+    path = tmp_path / "commands.txt"
+    path.write_text("echo one\ncd sub\n\necho two\nhalf written")
+    ran = []
+    p = CommandFilePoller(str(path), global_seed=7, poll_seconds=0.0,
+                          runner=lambda cmd, env, cwd: ran.append((cmd, env["GLOBAL_SEED"], os.path.basename(cwd))) or 0)
+    assert p.poll_once() and [r[0] for r in ran] == ["echo one", "echo two"]
+    assert ran[0][1] == "7" and ran[1][2] == "sub"
+    assert p.poll_once() and len(ran) == 2  # nothing new: the unfinished line waits for its newline
+    with open(path, "a") as f:
+        f.write("\nexit\necho never\n")
+    assert not p.poll_once()
+    assert [r[0] for r in ran] == ["echo one", "echo two", "half written"]
+    assert p.run(max_polls=1) == 3
+
+
+def test_thc_threshold_is_the_two_sided_normal_quantile():
+    assert abs(thc_tables.clip_threshold(2.0 ** -10) - thc_tables.THC_T) < 1e-9
+    assert abs(thc_tables.clipping_error(0.0) - 1.0) < 1e-9  # everything clipped to zero: E[x^2]
+    e31, e255 = thc_tables.expected_error(thc_tables.THC_T, 31), thc_tables.expected_error(thc_tables.THC_T, 255)
+    assert 0.0 < e255 < e31 < 0.02
+    t_best, e_best = thc_tables.best_threshold(31)
+    assert 2.0 < t_best < thc_tables.THC_T and e_best <= e31
