@@ -6,6 +6,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <cuda_bf16.h>
+#include <type_traits>
 #include <torch/extension.h>
 
 #include "norm_kernels.cuh"
@@ -193,18 +194,60 @@ __global__ void __launch_bounds__(256) adamw_kernel(const long long* __restrict_
   const long long n = numel[t];
   const long long base = static_cast<long long>(chunk - chunk_start[t]) * kAdamChunk;
   const float step_size = lr / bc1, inv_bc2_sqrt = rsqrtf(bc2);
+  auto update = [&](float gi, float& pi, float& mi, float& vi) {
+    gi *= grad_scale;
+    mi = beta1 * mi + (1.f - beta1) * gi;
+    vi = beta2 * vi + (1.f - beta2) * gi * gi;
+    pi -= lr * wd * pi;
+    pi -= step_size * mi / (sqrtf(vi) * inv_bc2_sqrt + eps);
+  };
+  if constexpr (std::is_same<P, float>::value && std::is_same<G, float>::value) {
+    // fp32 fast path: 16-byte streaming accesses (every array is touched exactly once per step, so none of it
+    // should displace the GEMM operands of the backward pass that runs beside this kernel), all loads of a
+    // thread's four groups in flight before the arithmetic
+    const bool aligned = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) |
+                           reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v)) & 15u) == 0 &&
+                         (reinterpret_cast<uintptr_t>(shadow) & 7u) == 0;
+    if (aligned && base + kAdamChunk <= n) {
+      constexpr int kGroups = kAdamChunk / 4 / 256;  // float4 groups per thread
+      float4 p4[kGroups], g4[kGroups], m4[kGroups], v4[kGroups];
+#pragma unroll
+      for (int j = 0; j < kGroups; ++j) {
+        const long long i = base + 4ll * (threadIdx.x + 256 * j);
+        g4[j] = __ldcs(reinterpret_cast<const float4*>(g + i));
+        p4[j] = __ldcs(reinterpret_cast<const float4*>(p + i));
+        m4[j] = __ldcs(reinterpret_cast<const float4*>(m + i));
+        v4[j] = __ldcs(reinterpret_cast<const float4*>(v + i));
+      }
+#pragma unroll
+      for (int j = 0; j < kGroups; ++j) {
+        const long long i = base + 4ll * (threadIdx.x + 256 * j);
+        update(g4[j].x, p4[j].x, m4[j].x, v4[j].x);
+        update(g4[j].y, p4[j].y, m4[j].y, v4[j].y);
+        update(g4[j].z, p4[j].z, m4[j].z, v4[j].z);
+        update(g4[j].w, p4[j].w, m4[j].w, v4[j].w);
+        __stcs(reinterpret_cast<float4*>(m + i), m4[j]);
+        __stcs(reinterpret_cast<float4*>(v + i), v4[j]);
+        __stcs(reinterpret_cast<float4*>(p + i), p4[j]);
+        if (shadow != nullptr) {
+          const __nv_bfloat162 lo = __floats2bfloat162_rn(p4[j].x, p4[j].y), hi = __floats2bfloat162_rn(p4[j].z, p4[j].w);
+          uint2 packed;
+          packed.x = *reinterpret_cast<const unsigned int*>(&lo);
+          packed.y = *reinterpret_cast<const unsigned int*>(&hi);
+          *reinterpret_cast<uint2*>(shadow + i) = packed;
+        }
+      }
+      return;
+    }
+  }
 #pragma unroll 4
   for (int k = threadIdx.x; k < kAdamChunk; k += 256) {
     const long long i = base + k;
     if (i >= n) break;
-    const float gi = to_f(g[i]) * grad_scale;
-    float pi = to_f(p[i]);
-    const float mi = beta1 * m[i] + (1.f - beta1) * gi;
-    const float vi = beta2 * v[i] + (1.f - beta2) * gi * gi;
+    float pi = to_f(p[i]), mi = m[i], vi = v[i];
+    update(to_f(g[i]), pi, mi, vi);
     m[i] = mi;
     v[i] = vi;
-    pi -= lr * wd * pi;
-    pi -= step_size * mi / (sqrtf(vi) * inv_bc2_sqrt + eps);
     p[i] = from_f<P>(pi);
     if (shadow != nullptr) shadow[i] = __float2bfloat16_rn(pi);
   }
