@@ -30,7 +30,8 @@ void fused_allreduce_local(std::vector<at::Tensor> buckets, at::Tensor steps, st
 std::tuple<at::Tensor, at::Tensor, at::Tensor> norm_fwd(at::Tensor x, at::Tensor w, c10::optional<at::Tensor> b,
                                                         double eps, bool rms);
 std::tuple<at::Tensor, at::Tensor, at::Tensor> norm_bwd(at::Tensor dy, at::Tensor x, at::Tensor w, at::Tensor mean,
-                                                        at::Tensor rstd, bool rms);
+                                                        at::Tensor rstd, bool rms, c10::optional<at::Tensor> dw_out,
+                                                        c10::optional<at::Tensor> db_out);
 std::tuple<at::Tensor, at::Tensor> ce_fwd(at::Tensor logits, at::Tensor labels, int64_t vocab, int64_t ignore_index);
 at::Tensor ce_bwd(at::Tensor logits, at::Tensor labels, at::Tensor lse, at::Tensor gout, at::Tensor n_valid,
                   int64_t vocab, int64_t ignore_index);
@@ -39,6 +40,7 @@ std::tuple<at::Tensor, at::Tensor> fwht1024_tcgen05(at::Tensor x, int64_t seed, 
 at::Tensor bins_to_bits(at::Tensor bins, int64_t nbits);
 at::Tensor bits_to_bins(at::Tensor words, int64_t nbits, int64_t n);
 at::Tensor colsum(at::Tensor x, c10::optional<at::Tensor> out);
+void scatter_add_rows(at::Tensor grad, at::Tensor ids, at::Tensor rows, double scale);
 at::Tensor swiglu_fwd(at::Tensor in);
 at::Tensor swiglu_bwd(at::Tensor dy, at::Tensor in);
 std::tuple<at::Tensor, at::Tensor> superchunk_center(at::Tensor x, int64_t world);
@@ -55,13 +57,14 @@ void adamw_step(at::Tensor table, at::Tensor numel, at::Tensor chunk_start, int6
 
 TORCH_LIBRARY(dq, m) {
   m.def("norm_fwd(Tensor x, Tensor w, Tensor? b, float eps, bool rms) -> (Tensor, Tensor, Tensor)", &dq::norm_fwd);
-  m.def("norm_bwd(Tensor dy, Tensor x, Tensor w, Tensor mean, Tensor rstd, bool rms) -> (Tensor, Tensor, Tensor)", &dq::norm_bwd);
+  m.def("norm_bwd(Tensor dy, Tensor x, Tensor w, Tensor mean, Tensor rstd, bool rms, Tensor(a!)? dw_out=None, Tensor(b!)? db_out=None) -> (Tensor, Tensor, Tensor)", &dq::norm_bwd);
   m.def("ce_fwd(Tensor logits, Tensor labels, int vocab, int ignore_index) -> (Tensor, Tensor)", &dq::ce_fwd);
   m.def("ce_bwd(Tensor(a!) logits, Tensor labels, Tensor lse, Tensor gout, Tensor n_valid, int vocab, int ignore_index) -> Tensor(a!)", &dq::ce_bwd);
   m.def("fwht1024_tcgen05(Tensor x, int seed, int step, int bucket, bool apply_signs, float scale, int ctas) -> (Tensor, Tensor)", &dq::fwht1024_tcgen05);
   m.def("bins_to_bits(Tensor bins, int nbits) -> Tensor", &dq::bins_to_bits);
   m.def("bits_to_bins(Tensor words, int nbits, int n) -> Tensor", &dq::bits_to_bins);
   m.def("colsum(Tensor x, Tensor(a!)? out=None) -> Tensor(a!)", &dq::colsum);
+  m.def("scatter_add_rows(Tensor(a!) grad, Tensor ids, Tensor rows, float scale) -> ()", &dq::scatter_add_rows);
   m.def("swiglu_fwd(Tensor x) -> Tensor", &dq::swiglu_fwd);
   m.def("swiglu_bwd(Tensor dy, Tensor x) -> Tensor", &dq::swiglu_bwd);
   m.def("superchunk_center(Tensor x, int world) -> (Tensor, Tensor)", &dq::superchunk_center);

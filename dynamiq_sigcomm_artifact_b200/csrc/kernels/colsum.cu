@@ -104,3 +104,60 @@ at::Tensor colsum(at::Tensor x, c10::optional<at::Tensor> out) {
 }
 
 }  // namespace dq
+
+// ---- deterministic row scatter-add: grad[ids[k], :] += scale * rows[k, :] ------------------------------------
+// `order` sorts the ids (stable); CTA k works only if position k starts a run of equal ids and then adds the
+// run's rows in sorted order, so every output row has one writer and a fixed summation order: ranks that hold
+// the same (ids, rows) produce the same bits.  Used for the embedding-lookup part of a tied embedding's
+// gradient, which is exchanged as token rows instead of a dense vocabulary-sized matrix.
+namespace dq {
+namespace {
+
+__global__ void __launch_bounds__(256) scatter_add_rows_kernel(float* __restrict__ grad, const long long* __restrict__ ids,
+                                                               const long long* __restrict__ order,
+                                                               const __nv_bfloat16* __restrict__ rows, long long n, int d,
+                                                               long long nrows_out, float scale) {
+  const long long k = blockIdx.x;
+  const long long id = ids[order[k]];
+  if (k > 0 && ids[order[k - 1]] == id) return;  // not the start of a run
+  if (id < 0 || id >= nrows_out) return;          // never write outside the matrix
+  for (int c = threadIdx.x * 4; c < d; c += 256 * 4) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (long long j = k; j < n && ids[order[j]] == id; ++j) {
+      float v[4];
+      load4(rows + order[j] * d + c, v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[i] += v[i];
+    }
+    float4* dst = reinterpret_cast<float4*>(grad + id * d + c);
+    float4 g = *dst;
+    g.x += scale * acc[0], g.y += scale * acc[1], g.z += scale * acc[2], g.w += scale * acc[3];
+    *dst = g;
+  }
+}
+
+}  // namespace
+
+// grad [V, d] fp32 (in place), ids [n] int64, rows [n, d] bf16
+void scatter_add_rows(at::Tensor grad, at::Tensor ids, at::Tensor rows, double scale) {
+  TORCH_CHECK(grad.is_cuda() && grad.scalar_type() == at::kFloat && grad.is_contiguous() && grad.dim() == 2,
+              "scatter_add_rows: grad must be a contiguous CUDA fp32 matrix");
+  TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous() && ids.dim() == 1,
+              "scatter_add_rows: ids must be a contiguous CUDA int64 vector");
+  TORCH_CHECK(rows.is_cuda() && rows.scalar_type() == at::kBFloat16 && rows.is_contiguous() && rows.dim() == 2 &&
+                  rows.size(0) == ids.size(0) && rows.size(1) == grad.size(1),
+              "scatter_add_rows: rows must be a contiguous CUDA bf16 [n, d] matrix");
+  const long long n = ids.numel();
+  const int d = static_cast<int>(grad.size(1));
+  TORCH_CHECK(d % 4 == 0, "scatter_add_rows: row length must be a multiple of 4");
+  if (n == 0) return;
+  c10::cuda::CUDAGuard guard(grad.device());
+  at::Tensor order = at::argsort(ids, /*stable=*/true, /*dim=*/0, /*descending=*/false);
+  scatter_add_rows_kernel<<<static_cast<unsigned>(n), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      grad.data_ptr<float>(), reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()),
+      reinterpret_cast<const long long*>(order.data_ptr<int64_t>()),
+      reinterpret_cast<const __nv_bfloat16*>(rows.data_ptr()), n, d, grad.size(0), static_cast<float>(scale));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+}  // namespace dq

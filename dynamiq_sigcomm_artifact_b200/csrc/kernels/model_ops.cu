@@ -349,8 +349,10 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> norm_fwd(at::Tensor x, at::Tensor
 }
 
 // returns (dx, dw, db); db is empty for RMSNorm
+// `dw_out` / `db_out` (fp32 [H], optional): where the weight / bias gradient is written instead of a new tensor
 std::tuple<at::Tensor, at::Tensor, at::Tensor> norm_bwd(at::Tensor dy, at::Tensor x, at::Tensor w, at::Tensor mean,
-                                                        at::Tensor rstd, bool rms) {
+                                                        at::Tensor rstd, bool rms, c10::optional<at::Tensor> dw_out,
+                                                        c10::optional<at::Tensor> db_out) {
   check_norm_inputs(x, w);
   TORCH_CHECK(dy.is_contiguous() && dy.scalar_type() == x.scalar_type() && dy.numel() == x.numel(), "norm_bwd: dy/x mismatch");
   c10::cuda::CUDAGuard guard(x.device());
@@ -359,7 +361,14 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> norm_bwd(at::Tensor dy, at::Tenso
   at::Tensor dx = at::empty_like(x);
   auto fopt = x.options().dtype(at::kFloat);
   auto stream = at::cuda::getCurrentCUDAStream();
-  at::Tensor dw = at::empty({H}, fopt), db = at::empty({rms ? 0 : H}, fopt);
+  auto usable = [&](const c10::optional<at::Tensor>& t) {
+    if (!t.has_value()) return false;
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == H,
+                "norm_bwd: an output gradient must be a contiguous CUDA fp32 tensor of H elements");
+    return true;
+  };
+  at::Tensor dw = usable(dw_out) ? *dw_out : at::empty({H}, fopt);
+  at::Tensor db = rms ? at::empty({0}, fopt) : (usable(db_out) ? *db_out : at::empty({H}, fopt));
   if (H <= 2048) {
     const int grid = std::max(1, std::min((rows + kNormWarps - 1) / kNormWarps, 2 * sm_count()));
     const int nparts = grid * kNormWarps;
@@ -388,8 +397,12 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> norm_bwd(at::Tensor dy, at::Tenso
 #undef DQ_ROWS
     C10_CUDA_KERNEL_LAUNCH_CHECK();
     dim3 rb(32, 32);
-    reduce_parts2_kernel<<<(H + 31) / 32, rb, 0, stream>>>(dw_part.data_ptr<float>(), dw.data_ptr<float>(), nparts, H);
-    if (!rms) reduce_parts2_kernel<<<(H + 31) / 32, rb, 0, stream>>>(db_part.data_ptr<float>(), db.data_ptr<float>(), nparts, H);
+    if (rms)
+      reduce_parts2_kernel<<<(H + 31) / 32, rb, 0, stream>>>(dw_part.data_ptr<float>(), dw.data_ptr<float>(), nparts, H);
+    else
+      reduce_parts2_pair_kernel<<<dim3((H + 31) / 32, 2), rb, 0, stream>>>(dw_part.data_ptr<float>(), dw.data_ptr<float>(),
+                                                                           db_part.data_ptr<float>(), db.data_ptr<float>(),
+                                                                           nparts, H);
     C10_CUDA_KERNEL_LAUNCH_CHECK();
     return {dx, dw, db};
   }

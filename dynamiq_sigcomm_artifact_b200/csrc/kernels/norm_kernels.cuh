@@ -155,5 +155,27 @@ static __global__ void __launch_bounds__(1024) reduce_parts2_kernel(const float*
   }
 }
 
+// the same reduction for two partial-sum arrays (weight and bias gradient) in one launch: blockIdx.y picks the pair
+static __global__ void __launch_bounds__(1024) reduce_parts2_pair_kernel(const float* __restrict__ part_a,
+                                                                         float* __restrict__ out_a,
+                                                                         const float* __restrict__ part_b,
+                                                                         float* __restrict__ out_b, int nparts, int H) {
+  __shared__ float sm[32][33];
+  const float* part = blockIdx.y == 0 ? part_a : part_b;
+  float* out = blockIdx.y == 0 ? out_a : out_b;
+  const int c = blockIdx.x * 32 + threadIdx.x, g = threadIdx.y;
+  float s = 0.f;
+  if (c < H)
+    for (int p = g; p < nparts; p += 32) s += part[static_cast<size_t>(p) * H + c];
+  sm[g][threadIdx.x] = s;
+  __syncthreads();
+  if (g == 0 && c < H) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) t += sm[k][threadIdx.x];
+    out[c] = t;
+  }
+}
+
 }  // namespace normk
 }  // namespace dq

@@ -31,11 +31,18 @@ class _LookupFn(torch.autograd.Function):
         ctx.save_for_backward(ids)
         ctx.rows = weight.shape[0]
         ctx.direct = getattr(weight, "_dq_grad_padded", None)
+        ctx.sparse = getattr(weight, "_dq_sparse", None)
         return F.embedding(ids, shadow)
 
     @staticmethod
     def backward(ctx, dy):
         (ids,) = ctx.saved_tensors
+        if ctx.sparse is not None:
+            # multi-rank runs: keep the token rows; the reducer exchanges them and adds every rank's rows
+            # after the dense (output-projection) part of the gradient has been reduced
+            ctx.sparse["ids"] = ids.reshape(-1)
+            ctx.sparse["rows"] = dy.reshape(-1, dy.shape[-1]).contiguous()
+            return None, None, None
         rows = dy.reshape(-1, dy.shape[-1]).float()
         if ctx.direct is not None:
             # the output projection's weight gradient was written earlier in this backward pass

@@ -36,13 +36,13 @@ class _NormFn(torch.autograd.Function):
     def backward(ctx, dy):
         ops = require()
         x, w, mean, rstd = ctx.saved_tensors
-        dx, dw, db = ops.norm_bwd(dy.contiguous(), x, w, mean, rstd, ctx.rms)
-        counters.add("norm_bwd", 2 if ctx.rms else 3)
+        # with gradient-arena views the reduction kernel writes the parameter gradients in place
+        dx, dw, db = ops.norm_bwd(dy.contiguous(), x, w, mean, rstd, ctx.rms, ctx.wg,
+                                  ctx.bg if ctx.has_bias else None)
+        counters.add("norm_bwd", 2)
         if ctx.wg is not None:
-            ctx.wg.copy_(dw)
             dw = None
         if ctx.has_bias and ctx.bg is not None:
-            ctx.bg.copy_(db)
             db = None
         return dx, dw, (db if ctx.has_bias else None), None, None
 

@@ -20,6 +20,14 @@ kernel for the gradient (16 bytes of HBM traffic), an optimizer pass that nothin
   fused AdamW step of exactly that bucket's parameters, both overlapping the rest of backward.
   Without gradient clipping nothing needs the whole gradient before the first update.
 
+* **Tied embedding across ranks** (``sparse_embedding``, on by default when there is more than one rank):
+  the dense part of a tied embedding's gradient (the output projection's weight gradient) exists at the very
+  start of backward, the lookup part only at its end but touches at most one row per token.  The parameter is
+  therefore bucketed with the head (reduced through the hook under the whole backward pass); the lookup part
+  travels as token rows (all-gather of ids and bf16 rows) and every rank adds all ranks' rows in the same
+  order after the dense part has been reduced, followed by that parameter's AdamW step.  What used to be the
+  step's exposed tail - the compressed collective of a vocabulary-sized bucket - is gone.
+
 In this mode one backward pass per step is assumed (a second one overwrites the in-place
 gradients); accumulate micro-batches with ``direct=False``.
 """
@@ -97,9 +105,12 @@ class BucketReducer:
 
     def __init__(self, model: nn.Module, bucket_cap_mb: float = 25.0, hook: Optional[Callable] = None,
                  hook_state=None, on_reduced: Optional[Callable[[int, List[nn.Parameter]], None]] = None,
-                 direct: bool = True, side_stream: bool = True, group=None, install: bool = True):
+                 direct: bool = True, side_stream: bool = True, group=None, install: bool = True,
+                 sparse_embedding: Optional[bool] = None):
         self.model, self.hook, self.hook_state, self.on_reduced = model, hook, hook_state, on_reduced
         self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self._sparse_wanted = sparse_embedding
         params = [p for p in model.parameters() if p.requires_grad]
         if not params:
             raise ValueError("model has no trainable parameters")
@@ -107,6 +118,15 @@ class BucketReducer:
         self.cuda = self.device.type == "cuda"
         self.direct = bool(direct and self.cuda)
         self.blocks = find_blocks(model)
+        # tied embeddings whose lookup gradient is exchanged as rows (needs the in-place gradient path)
+        want = (self.world > 1) if self._sparse_wanted is None else bool(self._sparse_wanted)
+        self.sparse_params: List[nn.Parameter] = []
+        if want and self.direct and self.blocks is not None:
+            from ..ops.embedding import TiedEmbedding
+
+            self.sparse_params = [m.weight for m in model.modules() if isinstance(m, TiedEmbedding)
+                                  and m.weight.requires_grad]
+        self._sparse_ids = {id(p) for p in self.sparse_params}
         self.groups = self._make_groups(params)
         self._layout(bucket_cap_mb)
         self.side = torch.cuda.Stream(self.device) if (self.cuda and side_stream) else None
@@ -133,6 +153,8 @@ class BucketReducer:
             if bi is not None:
                 per_block[bi].append(p)
                 seen_block = True
+            elif id(p) in self._sparse_ids:
+                post.insert(0, p)  # its dense gradient (output projection) is the first thing backward produces
             elif seen_block:
                 post.append(p)
             else:
@@ -204,6 +226,8 @@ class BucketReducer:
                 p._dq_grad = p.grad
                 if padded:
                     p._dq_grad_padded = self.arena[o: o + padded[0] * padded[1]].view(padded)
+            if id(p) in self._sparse_ids:
+                p._dq_sparse = {"ids": None, "rows": None}
         self.buckets = [FlatBucket(bi, self.arena[s:e], self.bucket_params[bi], bi == len(spans) - 1)
                         for bi, (s, e) in enumerate(spans)]
         self.n_direct = len(direct_ids)
@@ -230,7 +254,7 @@ class BucketReducer:
         self._handles = []
         for ps in self.bucket_params:
             for p in ps:
-                for a in ("_dq_grad", "_dq_grad_padded"):
+                for a in ("_dq_grad", "_dq_grad_padded", "_dq_sparse"):
                     if hasattr(p, a):
                         delattr(p, a)
 
@@ -266,15 +290,48 @@ class BucketReducer:
             if self._gap_index is not None and bucket.is_last():
                 self.arena.index_fill_(0, self._gap_index, 0.0)
             if self.on_reduced is not None:  # the consumer (optimizer) runs here, so the gradients are spent
-                self.on_reduced(bi, self.bucket_params[bi])
+                ready = [p for p in self.bucket_params[bi] if id(p) not in self._sparse_ids]
+                self.on_reduced(bi, ready)
                 for p in self.bucket_accum[bi]:
                     p.grad.zero_()
 
     def finish(self) -> None:
         """After ``loss.backward()``: flush what no marker reported and join the side stream."""
         self.group_ready(len(self.groups) - 1)
+        if self.sparse_params:
+            self._finish_sparse()
         if self.side is not None:
             torch.cuda.current_stream(self.device).wait_stream(self.side)
+
+    def _finish_sparse(self) -> None:
+        """Exchange the lookup rows of the tied embeddings, add every rank's rows (same order everywhere), then
+        hand the parameters to the consumer."""
+        from .. import ops as _ops
+        from ..utils import counters
+
+        dq = _ops.require()
+        stream = self.side if self.side is not None else torch.cuda.current_stream(self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream), torch.no_grad():
+            for p in self.sparse_params:
+                sp = p._dq_sparse
+                ids, rows = sp["ids"], sp["rows"]
+                if ids is None:
+                    raise RuntimeError("a tied embedding took no part in this backward pass")
+                if self.world > 1:
+                    all_ids = torch.empty(self.world * ids.numel(), dtype=ids.dtype, device=ids.device)
+                    all_rows = torch.empty(self.world * rows.shape[0], rows.shape[1], dtype=rows.dtype, device=rows.device)
+                    dist.all_gather_into_tensor(all_ids, ids.contiguous(), group=self.group)
+                    dist.all_gather_into_tensor(all_rows, rows, group=self.group)
+                else:
+                    all_ids, all_rows = ids.contiguous(), rows
+                dq.scatter_add_rows(p.grad, all_ids, all_rows, 1.0 / self.world)
+                counters.add("scatter_add_rows")
+                sp["ids"] = sp["rows"] = None
+                ids.record_stream(stream)
+                rows.record_stream(stream)
+            if self.on_reduced is not None:
+                self.on_reduced(-1, self.sparse_params)
 
     def zero_accumulated(self) -> None:
         """Without `on_reduced`: call after the optimizer step (in-place gradients need no zeroing)."""

@@ -55,6 +55,7 @@ class TrainConfig:
     measure_comm_error: bool = False
     cuda_graphs: bool = True  # capture each transformer block's forward and backward as CUDA graphs
     reducer: str = "flat"  # "flat": gradient arena + bucket pipeline of this package; "ddp": torch DDP + comm hook
+    sparse_embedding: Optional[bool] = None  # tied-embedding lookup gradient exchanged as token rows (None: when world > 1)
 
 
 class Trainer:
@@ -95,7 +96,8 @@ class Trainer:
             # the arena has to exist before the blocks are captured: the graphs keep its addresses
             self.reducer = BucketReducer(self.model, cfg.bucket_cap_mb, hook, state_list,
                                          on_reduced=lambda bi, ps: self.opt.step_params(bi, ps),
-                                         direct=(device.type == "cuda" and cfg.dtype == "bf16"), install=False)
+                                         direct=(device.type == "cuda" and cfg.dtype == "bf16"), install=False,
+                                         sparse_embedding=cfg.sparse_embedding)
             if self.world > 1:
                 self.reducer.broadcast_parameters(0)
                 if self.shadows:

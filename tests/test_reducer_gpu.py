@@ -67,3 +67,43 @@ def test_pipelined_trainer_matches_plain_trainer(name, graphs):
     # the bf16 working copies follow the fp32 parameters
     for p, sh in a.shadows.items():
         assert torch.equal(sh.view(-1)[: p.numel()].view_as(p), p.detach().to(torch.bfloat16))
+
+
+def test_scatter_add_rows_is_exact_and_deterministic():
+    from dynamiq_sigcomm_artifact_b200 import ops
+
+    dq = ops.require()
+    g = torch.Generator().manual_seed(1)
+    V, d, n = 1000, 256, 4096  # many duplicate ids
+    ids = torch.randint(0, V, (n,), generator=g).cuda()
+    rows = torch.randn(n, d, generator=g).to(torch.bfloat16).cuda()
+    base = torch.randn(V, d, generator=g).cuda()
+    want = base.double().index_add(0, ids, rows.double() * 0.25)
+    outs = []
+    for _ in range(2):
+        grad = base.clone()
+        dq.scatter_add_rows(grad, ids, rows, 0.25)
+        outs.append(grad)
+    assert torch.equal(outs[0], outs[1])
+    assert float((outs[0].double() - want).abs().max()) < 1e-4
+
+
+@pytest.mark.parametrize("name", ["gpt2-tiny", "llama-tiny"])
+def test_row_exchange_of_the_tied_embedding_matches_the_dense_path(name):
+    """Single process with the row exchange forced on (the all-gather is the identity): same training run."""
+    cfg = dict(model=name, micro_batch=2, seq_len=128, lr=1e-3, weight_decay=0.01)
+    a = Trainer(TrainConfig(reducer="flat", sparse_embedding=True, **cfg))
+    b = Trainer(TrainConfig(reducer="flat", sparse_embedding=False, **cfg))
+    b.model.load_state_dict(a.model.state_dict())
+    enable_shadows(b.model)
+    assert a.reducer.sparse_params and not b.reducer.sparse_params
+    names_a = [n for n, _ in a.model.named_parameters()]
+    first_bucket = {id(p) for p in a.reducer.bucket_params[0]}
+    assert id(a.reducer.sparse_params[0]) in first_bucket, "the tied weight is reduced with the head"
+    for s in range(6):
+        ids = _batch(a.model, 40 + s, 2, 128)
+        la, lb = float(a.train_step_device(ids)), float(b.train_step_device(ids))
+        assert abs(la - lb) < 2e-2 * max(1.0, abs(lb)), (s, la, lb)
+    torch.cuda.synchronize()
+    for (n, p), (_, q) in zip(a.model.named_parameters(), b.model.named_parameters()):
+        assert float((p - q).abs().mean()) < 2e-4, n
