@@ -49,6 +49,8 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--comm-threads", type=int, default=256)
     ap.add_argument("--tail-ctas", type=int, default=148, help="grid of the step's last bucket")
     ap.add_argument("--reducer", default="flat", choices=["flat", "ddp"])
+    ap.add_argument("--comm-prefetch", type=int, default=1, help="0: collective kernel without its staging buffer")
+    ap.add_argument("--sparse-embedding", type=int, default=-1, help="-1: automatic, 0 / 1: force off / on")
     ap.add_argument("--bucket-cap-mb", type=int, default=0, help="0: 25 MB (GPT-2, BERT) or 100 MB (Llama 1.2B)")
     ap.add_argument("--rotation", default="simt", choices=["simt", "tc"])
     return ap.parse_args()
@@ -86,7 +88,8 @@ def main() -> None:
     os.environ.setdefault("DQ_ROTATION", args.rotation)
     cfg = TrainConfig(model=args.model, method=args.method, micro_batch=mb, seq_len=seq, task=task,
                       bucket_cap_mb=args.bucket_cap_mb, topology=args.topology, comm_ctas=args.comm_ctas,
-                      comm_threads=args.comm_threads, tail_ctas=args.tail_ctas, reducer=args.reducer)
+                      comm_threads=args.comm_threads, tail_ctas=args.tail_ctas, reducer=args.reducer, comm_prefetch=bool(args.comm_prefetch),
+                      sparse_embedding=None if args.sparse_embedding < 0 else bool(args.sparse_embedding))
     tr = Trainer(cfg)
     dev = tr.device
     host_batches = [tr.synthetic_batch(pinned=True) for _ in range(4)]

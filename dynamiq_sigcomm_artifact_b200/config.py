@@ -128,6 +128,7 @@ class DynamiqConfig:
     comm_ctas: int = 64  # CTAs of the persistent collective kernel (SM carve-out against backward)
     comm_threads: int = 256
     tail_ctas: int = 148  # grid of a step's last bucket, which nothing overlaps (0: same as comm_ctas)
+    comm_prefetch: bool = True  # bulk-copy staging of the next raw block (4 KiB of shared memory per warp)
     rotation: str = "simt"  # "simt": fp32 butterflies (bit-exact with the CPU oracle); "tc": tcgen05 / TMEM
     wait_timeout_ms: int = 2000  # budget of every device-side wait before it gives up with an error status
     max_bucket_mb: int = 128  # symmetric-buffer capacity (grown on demand between steps)
@@ -143,6 +144,8 @@ class DynamiqConfig:
         c = cls(**overrides)
         c.comm_ctas = _env(["DQ_COMM_CTAS"], c.comm_ctas, int)
         c.tail_ctas = _env(["DQ_TAIL_CTAS"], c.tail_ctas, int)
+        c.comm_threads = _env(["DQ_COMM_THREADS"], c.comm_threads, int)
+        c.comm_prefetch = _env(["DQ_COMM_PREFETCH"], c.comm_prefetch, _bool)
         c.wait_timeout_ms = int(1000 * _env(["DQ_TIMEOUT_SECONDS", "RING_RDMA_TIMEOUT_SECONDS"],
                                              c.wait_timeout_ms / 1000, float))
         c.max_bucket_mb = _env(["DQ_MAX_BUCKET_MB"], c.max_bucket_mb, int)

@@ -20,13 +20,13 @@ void fused_allreduce(at::Tensor bucket, at::Tensor steps, std::vector<int64_t> m
                      int64_t threads, int64_t blocks_per_shard, int64_t slot_stride, int64_t scales_off,
                      int64_t flag_base, int64_t epoch, int64_t seed, int64_t step, int64_t bucket_id,
                      double post_scale, int64_t timeout_ns, bool no_transmit, int64_t codec, double sc_lattice_max, double sc_c1, double sc_c2,
-                     c10::optional<at::Tensor> sc_lut, c10::optional<at::Tensor> sc_plan);
+                     c10::optional<at::Tensor> sc_lut, c10::optional<at::Tensor> sc_plan, bool prefetch);
 void fused_allreduce_local(std::vector<at::Tensor> buckets, at::Tensor steps, std::vector<at::Tensor> mailboxes,
                            std::vector<at::Tensor> flags, at::Tensor status, at::Tensor tail_ws, int64_t nslots,
                            int64_t bits, int64_t ctas, int64_t threads, int64_t blocks_per_shard, int64_t slot_stride,
                            int64_t scales_off, int64_t flag_base, int64_t epoch, int64_t seed, int64_t step,
                            int64_t bucket_id, double post_scale, int64_t timeout_ns, bool no_transmit, int64_t codec, double sc_lattice_max, double sc_c1, double sc_c2,
-                     c10::optional<at::Tensor> sc_lut, c10::optional<at::Tensor> sc_plan);
+                     c10::optional<at::Tensor> sc_lut, c10::optional<at::Tensor> sc_plan, bool prefetch);
 std::tuple<at::Tensor, at::Tensor, at::Tensor> norm_fwd(at::Tensor x, at::Tensor w, c10::optional<at::Tensor> b,
                                                         double eps, bool rms);
 std::tuple<at::Tensor, at::Tensor, at::Tensor> norm_bwd(at::Tensor dy, at::Tensor x, at::Tensor w, at::Tensor mean,
@@ -86,12 +86,12 @@ TORCH_LIBRARY(dq, m) {
       "fused_allreduce(Tensor(a!) bucket, Tensor steps, int[] mail_ptrs, int[] flag_ptrs, int mailbox_bytes, "
       "int flag_words, int nslots, int status_ptr, int tail_ws_ptr, int rank, int world, int bits, int ctas, "
       "int threads, int blocks_per_shard, int slot_stride, int scales_off, int flag_base, int epoch, int seed, "
-      "int step, int bucket_id, float post_scale, int timeout_ns, bool no_transmit, int codec, float sc_lattice_max, float sc_c1, float sc_c2, Tensor? sc_lut, Tensor? sc_plan=None) -> ()",
+      "int step, int bucket_id, float post_scale, int timeout_ns, bool no_transmit, int codec, float sc_lattice_max, float sc_c1, float sc_c2, Tensor? sc_lut, Tensor? sc_plan=None, bool prefetch=True) -> ()",
       &dq::fused_allreduce);
   m.def(
       "fused_allreduce_local(Tensor[] buckets, Tensor steps, Tensor[] mailboxes, Tensor[] flags, Tensor status, "
       "Tensor tail_ws, int nslots, int bits, int ctas, int threads, int blocks_per_shard, int slot_stride, "
       "int scales_off, int flag_base, int epoch, int seed, int step, int bucket_id, float post_scale, "
-      "int timeout_ns, bool no_transmit, int codec, float sc_lattice_max, float sc_c1, float sc_c2, Tensor? sc_lut, Tensor? sc_plan=None) -> ()",
+      "int timeout_ns, bool no_transmit, int codec, float sc_lattice_max, float sc_c1, float sc_c2, Tensor? sc_lut, Tensor? sc_plan=None, bool prefetch=True) -> ()",
       &dq::fused_allreduce_local);
 }

@@ -201,7 +201,7 @@ void fused_allreduce(at::Tensor bucket, at::Tensor steps, std::vector<int64_t> m
                      int64_t threads, int64_t blocks_per_shard, int64_t slot_stride, int64_t scales_off,
                      int64_t flag_base, int64_t epoch, int64_t seed, int64_t step, int64_t bucket_id,
                      double post_scale, int64_t timeout_ns, bool no_transmit, int64_t codec, double sc_lattice_max, double sc_c1, double sc_c2,
-                     c10::optional<at::Tensor> sc_lut, c10::optional<at::Tensor> sc_plan) {
+                     c10::optional<at::Tensor> sc_lut, c10::optional<at::Tensor> sc_plan, bool prefetch) {
   c10::cuda::CUDAGuard guard(bucket.device());
   TORCH_CHECK(static_cast<int64_t>(mail_ptrs.size()) == world && static_cast<int64_t>(flag_ptrs.size()) == world,
               "need one mailbox and one flag pointer per rank");
@@ -210,6 +210,7 @@ void fused_allreduce(at::Tensor bucket, at::Tensor steps, std::vector<int64_t> m
   fill_common(p, bucket, steps, rank, world, blocks_per_shard, slot_stride, scales_off, flag_base, epoch, seed, step,
               bucket_id, post_scale, timeout_ns, status_ptr, tail_ws_ptr, no_transmit);
   fill_sc(p, codec, bits, sc_lattice_max, sc_c1, sc_c2, sc_lut, sc_plan);
+  p.prefetch = prefetch ? 1 : 0;
   for (int r = 0; r < world; ++r) {
     p.mail[r] = reinterpret_cast<uint8_t*>(mail_ptrs[r]);
     p.flags[r] = reinterpret_cast<uint32_t*>(flag_ptrs[r]);
@@ -230,7 +231,7 @@ void fused_allreduce_local(std::vector<at::Tensor> buckets, at::Tensor steps, st
                            int64_t bits, int64_t ctas, int64_t threads, int64_t blocks_per_shard, int64_t slot_stride,
                            int64_t scales_off, int64_t flag_base, int64_t epoch, int64_t seed, int64_t step,
                            int64_t bucket_id, double post_scale, int64_t timeout_ns, bool no_transmit, int64_t codec, double sc_lattice_max, double sc_c1, double sc_c2,
-                     c10::optional<at::Tensor> sc_lut, c10::optional<at::Tensor> sc_plan) {
+                     c10::optional<at::Tensor> sc_lut, c10::optional<at::Tensor> sc_plan, bool prefetch) {
   const int64_t world = static_cast<int64_t>(buckets.size());
   TORCH_CHECK(world >= 1 && world <= kMaxWorld, "1..8 ranks");
   TORCH_CHECK(steps.dim() == 3 && steps.size(0) == world, "steps must be [world, nsteps, 8]");
@@ -254,6 +255,7 @@ void fused_allreduce_local(std::vector<at::Tensor> buckets, at::Tensor steps, st
                 reinterpret_cast<int64_t>(status.data_ptr()),
                 reinterpret_cast<int64_t>(tail_ws.data_ptr<float>() + r * kBlock), no_transmit);
     fill_sc(hp[r], codec, bits, sc_lattice_max, sc_c1, sc_c2, sc_lut, sc_plan);
+    hp[r].prefetch = prefetch ? 1 : 0;
     for (int64_t q = 0; q < world; ++q) {
       hp[r].mail[q] = static_cast<uint8_t*>(mailboxes[q].data_ptr());
       hp[r].flags[q] = reinterpret_cast<uint32_t*>(flags[q].data_ptr());
@@ -275,9 +277,9 @@ void fused_allreduce_local(std::vector<at::Tensor> buckets, at::Tensor steps, st
   C10_CUDA_CHECK(cudaStreamSynchronize(stream));  // hp is pageable host memory
   const ARParams* dp = reinterpret_cast<const ARParams*>(dev.data_ptr());
   if (buckets[0].scalar_type() == at::kFloat)
-    launch_bits<float>(static_cast<int>(bits), nullptr, dp, static_cast<int>(world), static_cast<int>(ctas), static_cast<int>(threads), stream, static_cast<int>(codec));
+    launch_bits<float>(static_cast<int>(bits), hp.data(), dp, static_cast<int>(world), static_cast<int>(ctas), static_cast<int>(threads), stream, static_cast<int>(codec));
   else
-    launch_bits<__nv_bfloat16>(static_cast<int>(bits), nullptr, dp, static_cast<int>(world), static_cast<int>(ctas), static_cast<int>(threads), stream, static_cast<int>(codec));
+    launch_bits<__nv_bfloat16>(static_cast<int>(bits), hp.data(), dp, static_cast<int>(world), static_cast<int>(ctas), static_cast<int>(threads), stream, static_cast<int>(codec));
   C10_CUDA_CHECK(cudaStreamSynchronize(stream));  // keep `dev` alive until the kernel has read it
 }
 

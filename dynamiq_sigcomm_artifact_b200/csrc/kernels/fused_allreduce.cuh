@@ -39,6 +39,8 @@ struct ARParams {
   unsigned long long timeout_ns;   // budget of each wait on a flag
   uint32_t* status;                // 4 words, local
   int no_transmit;                 // debug: run the maths, skip remote payload stores
+  int prefetch;                    // 1: per-warp bulk-copy staging of the next raw block (4 KiB of shared memory per
+                                   // warp); 0: read raw blocks directly, half the shared memory per CTA
   int tensor_rotation;             // host-side selector: 1 = tcgen05 rotation, 0 = SIMT butterflies
   int codec;                       // host-side selector: kCodecRht / kCodecScAee / kCodecScMee
   unsigned int block_bytes;        // bytes of one encoded 1024-element block inside a message

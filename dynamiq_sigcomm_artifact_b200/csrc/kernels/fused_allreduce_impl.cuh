@@ -85,10 +85,10 @@ __device__ __forceinline__ RawItem next_raw_item(const ARParams& p, int s, int b
 //   tensor rotation: [operands: nwg x 18 KiB][stage: nwarps x 4 KiB][H_32][sign words][prefetch barriers]
 //                    [MMA barriers: nwg][TMEM slot][error flag]
 template <bool TC>
-__host__ __device__ constexpr size_t fused_smem_bytes(int threads) {
+__host__ __device__ constexpr size_t fused_smem_bytes(int threads, bool stage = true) {
   const size_t nwarps = threads / 32, nwg = threads / 128;
-  return (TC ? nwg * tc::kOperandBytes + tc::kHBytes + nwg * 8 + 16 : nwarps * kBlock * 4) + nwarps * kBlock * 4 +
-         32 * 4 + nwarps * 8 + 128;
+  return (TC ? nwg * tc::kOperandBytes + tc::kHBytes + nwg * 8 + 16 : nwarps * kBlock * 4) +
+         (stage ? nwarps * kBlock * 4 : 0) + 32 * 4 + nwarps * 8 + 128;
 }
 
 template <int BITS, typename T, int CODEC>
@@ -118,8 +118,9 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
     tile = reinterpret_cast<float*>(cursor) + warp * kBlock;
     cursor += static_cast<size_t>(nwarps) * kBlock * 4;
   }
+  const bool use_stage = TC || p.prefetch != 0;  // the tensor-core path stages its operands through it
   float* stage = reinterpret_cast<float*>(cursor) + warp * kBlock;
-  cursor += static_cast<size_t>(nwarps) * kBlock * 4;
+  if (use_stage) cursor += static_cast<size_t>(nwarps) * kBlock * 4;
   uint8_t* hmat = cursor;
   if (TC) cursor += tc::kHBytes;
   uint32_t* sign_words = reinterpret_cast<uint32_t*>(cursor);
@@ -177,7 +178,7 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
   // prefetch state (warp-uniform): the item whose data is in flight or resident in `stage`
   RawItem pf = RawItem{-1, -1};
   uint32_t pf_parity = 0;
-  bool prefetch_ok = !SC;  // the superchunk codec reads lane-contiguous runs straight from global memory
+  bool prefetch_ok = !SC && use_stage;  // the record codecs read lane-contiguous runs straight from global memory
   const ScParams scp{p.sc_lattice_max, p.sc_c1, p.sc_c2, p.sc_lut};
   uint8_t* rec_tile = reinterpret_cast<uint8_t*>(tile);  // superchunk codec: the warp's record staging area
   auto issue_prefetch = [&](RawItem it) {
@@ -456,20 +457,25 @@ void launch_one(const ARParams* host_params, const ARParams* dev_params, int nra
   TORCH_CHECK(!TC || threads == 128 || threads == 256 || threads == 512,
               "the tensor-core rotation needs 1, 2 or 4 whole warpgroups (128, 256 or 512 threads): TMEM columns are "
               "allocated in powers of two");
-  const size_t smem = fused_smem_bytes<TC>(threads);
+  const bool stage = TC || host_params == nullptr || host_params->prefetch != 0;
+  const size_t smem = fused_smem_bytes<TC>(threads, stage);
   const void* fn = nranks == 1 ? reinterpret_cast<const void*>(&fused_allreduce_kernel<BITS, T, CODEC>)
                                : reinterpret_cast<const void*>(&fused_allreduce_multi_kernel<BITS, T, CODEC>);
   // attribute and occupancy are queried once per (kernel, device, block size) and cached
   struct Cache {
     int dev = -1, threads = -1, capacity = 0;
   };
-  static thread_local Cache cache[2];
-  Cache& c = cache[nranks == 1 ? 0 : 1];
+  static thread_local Cache cache[4];
+  Cache& c = cache[(nranks == 1 ? 0 : 1) + (stage ? 0 : 2)];
   int dev = 0;
   C10_CUDA_CHECK(cudaGetDevice(&dev));
   if (c.dev != dev || c.threads != threads) {
-    int sms = 0, per_sm = 0;
-    C10_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    int sms = 0, per_sm = 0, optin = 0;
+    // the limit is a property of the kernel, shared by every (block size, staging) combination that launches it:
+    // raise it to the device's opt-in maximum once instead of to this combination's need
+    C10_CUDA_CHECK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    TORCH_CHECK(static_cast<size_t>(optin) >= smem, "fused all-reduce: ", smem, " bytes of shared memory per CTA exceed the device limit ", optin);
+    C10_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, optin));
     C10_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     C10_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, threads, smem));
     c.dev = dev, c.threads = threads, c.capacity = sms * per_sm;

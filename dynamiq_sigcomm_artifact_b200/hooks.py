@@ -132,7 +132,8 @@ def _engine(state: HookState):
         state["engine"] = FusedAllreduce(group=state["group"], max_numel=cfg.max_bucket_mb * (1 << 20) // 4,
                                          ctas=cfg.comm_ctas, threads=cfg.comm_threads,
                                          timeout_ms=cfg.wait_timeout_ms, validate=cfg.validate_topology,
-                                         rotation=cfg.rotation, max_ctas=max(cfg.comm_ctas, cfg.tail_ctas))
+                                         rotation=cfg.rotation, max_ctas=max(cfg.comm_ctas, cfg.tail_ctas),
+                                         prefetch=cfg.comm_prefetch)
         state["comm_stream"] = torch.cuda.Stream(priority=-1)
     return state["engine"]
 

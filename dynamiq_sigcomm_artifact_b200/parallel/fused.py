@@ -144,7 +144,8 @@ class FusedAllreduce:
     """Compressed all-reduce (mean) over NVLink for the ranks of a process group."""
 
     def __init__(self, group=None, max_numel: int = 32 << 20, ctas: int = 64, threads: int = 256,
-                 timeout_ms: int = 2000, validate: bool = True, rotation: str = "simt", max_ctas: Optional[int] = None):
+                 timeout_ms: int = 2000, validate: bool = True, rotation: str = "simt", max_ctas: Optional[int] = None,
+                 prefetch: bool = True):
         """`ctas` is the default grid of a collective; a call may ask for any grid up to `max_ctas`
         (every rank must ask for the same one): a bucket that runs under backward wants a small grid,
         the last bucket of a step has the GPU to itself."""
@@ -154,6 +155,7 @@ class FusedAllreduce:
         self.rank = dist.get_rank(group)
         self.ctas, self.threads = int(ctas), int(threads)
         self.max_ctas = max(int(max_ctas or 0), self.ctas)
+        self.prefetch = bool(prefetch)  # False: no staging buffer, half the shared memory per CTA
         self.timeout_ns = int(timeout_ms) * 1_000_000
         self.validate = validate
         self.tensor_rotation = _rotation_flag(rotation)
@@ -218,7 +220,7 @@ class FusedAllreduce:
             self.buf.local_ptr + self.off_status, self.buf.local_ptr + self.off_tail, self.rank, self.world, bits,
             grid, self.threads, lay.blocks_per_shard, lay.slot_stride, lay.scales_off,
             parity * self.flag_words_per_set, self.epoch, seed, step, bucket_id, 1.0 / self.world, self.timeout_ns,
-            no_transmit, *codec_args(codec, bits, bucket.device), plan)
+            no_transmit, *codec_args(codec, bits, bucket.device), plan, self.prefetch)
         counters.add("fused_allreduce")
         return bucket
 
@@ -243,8 +245,9 @@ class LocalCluster:
     """All ranks of a collective on one GPU, one cooperative launch (blockIdx.y = rank)."""
 
     def __init__(self, world: int, max_numel: int, ctas: int = 8, threads: int = 256, device="cuda",
-                 timeout_ms: int = 1000, rotation: str = "simt"):
+                 timeout_ms: int = 1000, rotation: str = "simt", prefetch: bool = True):
         self.ops = _ops.require()
+        self.prefetch = bool(prefetch)
         self.tensor_rotation = _rotation_flag(rotation)
         self.world, self.ctas, self.threads = world, ctas, threads
         self.device = torch.device(device)
@@ -273,7 +276,7 @@ class LocalCluster:
             buckets, programs, self.mail, self.flags, self.status, self.tail_ws, self.nslots, bits, self.ctas,
             self.threads, lay.blocks_per_shard, lay.slot_stride, lay.scales_off, 0, self.epoch, seed, step, bucket_id,
             (1.0 / self.world) if post_scale is None else post_scale, self.timeout_ns, no_transmit,
-            *codec_args(codec, bits, buckets[0].device), plan)
+            *codec_args(codec, bits, buckets[0].device), plan, self.prefetch)
 
     def allreduce_(self, buckets: List[torch.Tensor], bits: int, topology: str = "ring", correlated: bool = False,
                    **kw) -> List[torch.Tensor]:

@@ -20,13 +20,16 @@ kernel for the gradient (16 bytes of HBM traffic), an optimizer pass that nothin
   fused AdamW step of exactly that bucket's parameters, both overlapping the rest of backward.
   Without gradient clipping nothing needs the whole gradient before the first update.
 
-* **Tied embedding across ranks** (``sparse_embedding``, on by default when there is more than one rank):
+* **Tied embedding across ranks** (``sparse_embedding=True``; off by default):
   the dense part of a tied embedding's gradient (the output projection's weight gradient) exists at the very
   start of backward, the lookup part only at its end but touches at most one row per token.  The parameter is
   therefore bucketed with the head (reduced through the hook under the whole backward pass); the lookup part
   travels as token rows (all-gather of ids and bf16 rows) and every rank adds all ranks' rows in the same
-  order after the dense part has been reduced, followed by that parameter's AdamW step.  What used to be the
-  step's exposed tail - the compressed collective of a vocabulary-sized bucket - is gone.
+  order after the dense part has been reduced, followed by that parameter's AdamW step.  This removes the
+  compressed collective of a vocabulary-sized bucket from the step's tail, but on B200 it measured slower than
+  the dense path (GPT-2 small, 2 GPUs: 10.77 vs 10.61 ms per step; Llama 1.2B: 74.4 vs 73.2 ms): the collective
+  kernel and the GEMMs of backward compete for the same SMs, so moving the big collective under backward
+  costs as much as it saves, and the row exchange adds two library all-gathers and a sort.
 
 In this mode one backward pass per step is assumed (a second one overwrites the in-place
 gradients); accumulate micro-batches with ``direct=False``.
@@ -119,7 +122,7 @@ class BucketReducer:
         self.direct = bool(direct and self.cuda)
         self.blocks = find_blocks(model)
         # tied embeddings whose lookup gradient is exchanged as rows (needs the in-place gradient path)
-        want = (self.world > 1) if self._sparse_wanted is None else bool(self._sparse_wanted)
+        want = bool(self._sparse_wanted)  # off unless asked for: measured slower than the dense path (see docstring)
         self.sparse_params: List[nn.Parameter] = []
         if want and self.direct and self.blocks is not None:
             from ..ops.embedding import TiedEmbedding

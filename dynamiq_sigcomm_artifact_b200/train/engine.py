@@ -51,11 +51,12 @@ class TrainConfig:
     comm_ctas: int = 64
     comm_threads: int = 256
     tail_ctas: int = 148  # grid of the step's last bucket (nothing left to overlap)
+    comm_prefetch: bool = True  # staging buffer of the collective kernel (off: half the shared memory per CTA)
     warmup_steps: int = 2
     measure_comm_error: bool = False
     cuda_graphs: bool = True  # capture each transformer block's forward and backward as CUDA graphs
     reducer: str = "flat"  # "flat": gradient arena + bucket pipeline of this package; "ddp": torch DDP + comm hook
-    sparse_embedding: Optional[bool] = None  # tied-embedding lookup gradient exchanged as token rows (None: when world > 1)
+    sparse_embedding: Optional[bool] = None  # True: tied-embedding lookup gradient exchanged as token rows
 
 
 class Trainer:
@@ -83,6 +84,7 @@ class Trainer:
         if self.world > 1:
             dcfg = DynamiqConfig.from_env(method=cfg.method, seed=cfg.seed, topology=cfg.topology,
                                           comm_ctas=cfg.comm_ctas, comm_threads=cfg.comm_threads, tail_ctas=cfg.tail_ctas,
+                                          comm_prefetch=cfg.comm_prefetch,
                                           warmup_steps=cfg.warmup_steps, measure_comm_error=cfg.measure_comm_error)
         use_graphs = cfg.cuda_graphs and device.type == "cuda" and cfg.dtype == "bf16"
         if cfg.reducer == "flat":

@@ -170,3 +170,20 @@ def test_collective_with_tensor_core_rotation(topology):
     xb = x.bfloat16()
     back16 = codec.decompress(codec.compress(xb), n, dtype=torch.bfloat16)
     assert float((back16.float() - xb.float()).pow(2).sum() / xb.float().pow(2).sum()) < 1e-3
+
+
+@pytest.mark.parametrize("topology", ["ring", "direct"])
+def test_collective_without_staging_buffer_is_bit_identical(topology):
+    """prefetch=False halves the shared memory of a CTA and must not change a single bit."""
+    from dynamiq_sigcomm_artifact_b200.parallel.fused import LocalCluster
+
+    world, n = 4, 37 * 1024 + 5
+    xs = [heavy_tail_grad(n, 90 + r) for r in range(world)]
+    outs = []
+    for prefetch in (True, False):
+        cl = LocalCluster(world, n, ctas=5, threads=128, prefetch=prefetch)
+        bufs = [torch.from_numpy(x).cuda() for x in xs]
+        cl.allreduce_(bufs, 5, topology, seed=3, step=2, bucket_id=1)
+        cl.check()
+        outs.append(bufs[0].clone())
+    assert torch.equal(outs[0], outs[1])
