@@ -85,6 +85,14 @@ def main(argv=None) -> None:
     timed("superchunk_center_64Mi", lambda: dq.superchunk_center(xs, 8), xs.numel() * 8 + xs.numel() // 32)
     bins = torch.randint(0, 16, (64 << 20,), dtype=torch.uint8, device=dev)
     timed("bins_to_bits_4bit_64Mi", lambda: dq.bins_to_bits(bins, 4), bins.numel() * 1.5)
+    # bias gradient of a linear layer: column sums of [8192, 3072] bf16; token-row scatter-add of a tied embedding
+    dyl = torch.randn(rows, 3072, device=dev).to(bf)
+    timed("colsum_8192x3072_bf16", lambda: dq.colsum(dyl, None), dyl.numel() * 2)
+    emb_grad = torch.zeros(50304, 768, device=dev)
+    tok = torch.randint(0, 50257, (2 * rows,), device=dev)
+    tok_rows = torch.randn(2 * rows, 768, device=dev).to(bf)
+    timed("scatter_add_rows_16384x768", lambda: dq.scatter_add_rows(emb_grad, tok, tok_rows, 0.5),
+          tok_rows.numel() * 2 + 2 * tok_rows.numel() * 4)
     # bit allocation of the superchunk codec: 64 Mi elements = 256 Ki superchunks
     _, stats = dq.superchunk_center(xs, 8)
     nsc = stats.shape[0]
