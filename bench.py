@@ -105,7 +105,7 @@ def main() -> None:
         tr.train_step(host_batches[i % 4])
     barrier()
 
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(local_rank, period_ms=100)
     if rank == 0:
         sampler.start()
 
