@@ -5,7 +5,7 @@
 #  2. its hook package and smoke test, copied byte for byte, with eden_utils placed inside
 #     new_comm_hooks/ exactly as testbed_evaluation/build_eden_utils_llm.zsh does.
 set -euo pipefail
-REF=${1:-/root/reference}
+REF=${1:?usage: install_reference.sh <path of the reference checkout>}
 HERE="$(cd "$(dirname "$0")" && pwd)"
 DST="$HERE/_ref"
 mkdir -p "$DST"

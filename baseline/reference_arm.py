@@ -51,7 +51,7 @@ def _hf_model(name: str):
 
 def run_reference(args, models) -> None:
     if not os.path.isdir(os.path.join(REF_TB, "new_comm_hooks")):
-        return _unavailable("baseline/_ref is missing: run baseline/install_reference.sh where /root/reference is mounted")
+        return _unavailable("baseline/_ref is missing: run baseline/install_reference.sh <path of the reference checkout>")
     if args.model not in ("gpt2-small", "llama-1.2b"):
         return _unavailable(f"no reference harness for model {args.model}")
     import torch
