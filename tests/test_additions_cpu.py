@@ -54,3 +54,33 @@ def test_thc_threshold_is_the_two_sided_normal_quantile():
     assert 0.0 < e255 < e31 < 0.02
     t_best, e_best = thc_tables.best_threshold(31)
     assert 2.0 < t_best < thc_tables.THC_T and e_best <= e31
+
+
+def test_threshold_widths_agree_with_group_split():
+    from dynamiq_sigcomm_artifact_b200.config import THRESHOLD_TABLE
+
+    g = torch.Generator().manual_seed(5)
+    for key in ("3bit", "5bit", "7bit", "4bit_fixed"):
+        thr = THRESHOLD_TABLE[key]
+        e = torch.exp(torch.randn(1003, generator=g) * 3)
+        e[10:20] = e[10]  # ties keep their original order (stable sort)
+        widths = bitalloc.threshold_widths(e, thr)
+        groups = bitalloc.split_by_thresholds(e, thr)
+        for b in (8, 4, 2):
+            assert sorted(torch.nonzero(widths == b).reshape(-1).tolist()) == sorted(groups[b].tolist()), (key, b)
+        assert widths.dtype == torch.uint8 and int((widths == 0).sum()) == 0
+
+
+def test_flat_bucket_quacks_like_a_grad_bucket():
+    from dynamiq_sigcomm_artifact_b200.parallel.reducer import FlatBucket
+
+    p = torch.nn.Parameter(torch.zeros(6))
+    buf = torch.arange(6.0)
+    p.grad = buf.view_as(p)
+    b = FlatBucket(3, buf, [p], last=True)
+    assert b.index() == 3 and b.is_last() and b.buffer() is buf
+    assert b.parameters() == [p] and b.gradients()[0].data_ptr() == buf.data_ptr()
+    b.set_buffer(torch.ones(6))
+    assert torch.equal(buf, torch.ones(6))
+    b.set_buffer(buf)  # the same storage: nothing to copy
+    assert torch.equal(p.grad, torch.ones(6))
