@@ -13,9 +13,16 @@ Two things of the reference cannot run on one 8-GPU host and are replaced by the
 alternatives: its trainer needs a patched ``accelerate`` that is not in the repository
 (train_llm_causal.py:16,416), so DDP is constructed directly with the same arguments
 (bucket_cap_mb 4000 for DynamiQ, 256 otherwise, :216,:416); and its ring callback needs two
-ranks per host plus an RDMA NIC (new_comm_hooks/ring_rdma.py:144-161,445-468), so the method
-runs with the ``_butterfly`` suffix and ``BUTTERFLY_RDMA_DISABLE=1``, the reference's own switch
-to its NCCL point-to-point butterfly (comm_hooks.py:36-39).
+ranks per host plus an RDMA NIC (new_comm_hooks/ring_rdma.py:144-161,445-468), so every hook method
+(``dynamiQ_*``, ``bf16``, ``MXfp8``, ``fp4`` / ``fp6``, ``omnireduce``, ``thc``) runs with the ``_butterfly``
+suffix and ``BUTTERFLY_RDMA_DISABLE=1``, the reference's own switch to its NCCL point-to-point butterfly
+(comm_hooks.py:36-45).
+
+``--method nccl`` (also ``none`` / ``fp32``) is the stock path the reference falls back to when no hook is
+selected: plain ``DistributedDataParallel`` with the library all-reduce and 25 MB buckets.
+
+Models: GPT-2 small, the 1.2B Llama-style model and BERT-base (masked LM, 15 % of the positions carry a
+label) from ``transformers`` with random-init weights.
 """
 from __future__ import annotations
 
@@ -46,13 +53,20 @@ def _hf_model(name: str):
                              num_attention_heads=32, num_key_value_heads=8, max_position_embeddings=2048,
                              rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=True)
         return tf.LlamaForCausalLM(cfg), 128256
+    if name == "bert-base":
+        cfg = tf.BertConfig(vocab_size=30522, hidden_size=768, num_hidden_layers=12, num_attention_heads=12,
+                            intermediate_size=3072, max_position_embeddings=512)
+        return tf.BertForMaskedLM(cfg), 30522
     raise ValueError(name)
+
+
+STOCK = ("nccl", "none", "fp32", "ddp")
 
 
 def run_reference(args, models) -> None:
     if not os.path.isdir(os.path.join(REF_TB, "new_comm_hooks")):
         return _unavailable("baseline/_ref is missing: run baseline/install_reference.sh <path of the reference checkout>")
-    if args.model not in ("gpt2-small", "llama-1.2b"):
+    if args.model not in ("gpt2-small", "llama-1.2b", "bert-base"):
         return _unavailable(f"no reference harness for model {args.model}")
     import torch
     import torch.distributed as dist
@@ -64,10 +78,11 @@ def run_reference(args, models) -> None:
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     method = args.method
-    if "dynamiq" in method.lower() and "butterfly" not in method.lower():
-        method = method + "_butterfly"
+    stock = method.lower() in STOCK
+    if not stock and "butterfly" not in method.lower():
+        method = method + "_butterfly"  # every hook of the reference takes its topology callback from the name
     os.environ["BUTTERFLY_RDMA_DISABLE"] = "1"
-    if world > 1 and world & (world - 1):
+    if world > 1 and not stock and world & (world - 1):
         return _unavailable("the reference's butterfly needs a power-of-two world size")
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
@@ -77,7 +92,10 @@ def run_reference(args, models) -> None:
     model, vocab = _hf_model(args.model)
     model = model.to(torch.bfloat16).to(dev)  # the reference loads torch_dtype=bfloat16
     state = None
-    if world > 1:
+    mlm = args.model == "bert-base"
+    if world > 1 and stock:
+        net = DDP(model, device_ids=[local_rank], bucket_cap_mb=25)
+    elif world > 1:
         sys.path.insert(0, REF_TB)
         argv = sys.argv
         sys.argv = ["smoke_test_new_comm_hooks.py", "--aggregation_method", method]
@@ -103,6 +121,17 @@ def run_reference(args, models) -> None:
         g = torch.Generator().manual_seed(7919 * 0 + 104729 * rank + i)
         return torch.randint(0, vocab, (mb, seq), generator=g, dtype=torch.int64).pin_memory()
 
+    def mlm_labels(ids):  # 15 % of the positions carry a label (80 % [MASK] id 103, 10 % random, 10 % kept)
+        g = torch.Generator(device=ids.device).manual_seed(int(ids[0, 0]))
+        r = torch.rand(ids.shape, generator=g, device=ids.device)
+        sel = r < 0.15
+        labels = torch.where(sel, ids, torch.full_like(ids, -100))
+        x = ids.clone()
+        x[sel & (r < 0.12)] = 103
+        rnd = sel & (r >= 0.12) & (r < 0.135)
+        x[rnd] = torch.randint(0, vocab, (int(rnd.sum()),), generator=g, device=ids.device)
+        return x, labels
+
     host = [batch(i) for i in range(4)]
     devb = [b.to(dev) for b in host]
     step_idx = [-1]
@@ -111,7 +140,11 @@ def run_reference(args, models) -> None:
         step_idx[0] += 1
         if state is not None:
             state["batch_idx"] = step_idx[0]
-        out = net(input_ids=ids, labels=ids)
+        if mlm:
+            x, labels = mlm_labels(ids)
+            out = net(input_ids=x, labels=labels)
+        else:
+            out = net(input_ids=ids, labels=ids)
         out.loss.backward()
         opt.step()
         sched.step()
@@ -152,7 +185,8 @@ def run_reference(args, models) -> None:
             "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
             "config": {"model": args.model, "arch": desc, "global_batch": mb * world, "seq_len": seq,
                        "parallelism": f"dp{world}", "method": method if world > 1 else "none (1 GPU)",
-                       "hook": "reference P2P_dynamiQ_hook + eden_utils (sm_100 build), NCCL point-to-point butterfly",
+                       "hook": ("stock DistributedDataParallel, library all-reduce, no hook" if stock or world == 1 else
+                                f"reference {hook.__name__} + eden_utils (sm_100 build), NCCL point-to-point butterfly"),
                        "model_impl": "transformers (random init, bf16 parameters), torch.optim.AdamW"},
             "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": host[0].numel() * 8, "d2h_bytes_per_step": 4},

@@ -10,6 +10,7 @@ same random numbers as the kernel (cuda_kernels/tests/test_scaling_quantization_
          trip is folded into the final scale, so no pass multiplies by 1/32)
       -> per-block fp32 scale  absmax / R,  R = 2^(b-1) - 1
       -> stochastic rounding  floor(y * R/absmax + u),  u = (byte + 0.5) / 256 from Philox-4x32-7
+         (evaluated as floor(fma(y, 256 R/absmax, 2^15 + byte + 0.5) / 256) - 128, the kernel's form)
       -> b-bit codes, b in 2..8, packed without padding (8 codes of 5 bits in 5 bytes)
 
 A hop adds the decoded incoming block to the locally rotated block with one fp32 fma per
@@ -20,9 +21,11 @@ All arithmetic is float32 in the order the kernel uses (fused multiply-adds wher
 fuses: the rounding argument and the hop accumulation), so that the kernel's bytes can be
 compared with ``==``.
 
-Layouts (shared with ``csrc/common/rht_codec.cuh``)
+Layouts (shared with ``csrc/common/rht_codec.cuh`` and ``csrc/kernels/fused_rht_tc.cuh``)
 * A warp owns a block; after the rotation lane ``l`` holds, in register ``k``, the
-  coefficient with index ``RHO[l, k] = (l & 3) + 4 k + 128 (l >> 2)``.
+  coefficient with index ``RHO[l, k] = (l & 3) + 4 k + 128 (l >> 2)`` when the rotation ran as register
+  butterflies (layout ``"simt"``) and ``RHO_TC[l, k] = 32 k + l`` when it ran on the tensor cores
+  (layout ``"tc"``: lane = accumulator row, register = accumulator column).
 * The 32 codes of a lane form a little-endian bit stream of ``b`` 32-bit words; word ``j`` of
   lane ``l`` is stored at word ``j * 32 + l`` of the block's ``128 b`` code bytes, so each of
   the ``b`` warp-wide stores is one contiguous 128-byte line.
@@ -40,6 +43,8 @@ BLOCK = 1024
 _L = np.arange(32).reshape(32, 1)
 _K = np.arange(32).reshape(1, 32)
 RHO = ((_L & 3) + 4 * _K + 128 * (_L >> 2)).astype(np.int64)  # [lane, reg] -> coefficient index
+RHO_TC = (32 * _K + _L).astype(np.int64)
+LAYOUTS = {"simt": RHO, "tc": RHO_TC}
 FWD_STAGES = (0, 1, 7, 8, 9, 2, 3, 4, 5, 6)  # bit of the element index handled by each butterfly stage
 INV_STAGES = (2, 3, 4, 5, 6, 0, 1, 7, 8, 9)
 F32 = np.float32
@@ -68,22 +73,24 @@ def wire_bits_per_element(bits: int) -> float:
 
 
 def to_blocks(x: np.ndarray) -> np.ndarray:
-    """Flat fp32 vector -> [nblocks, 1024], zero padded; non-finite inputs become 0."""
+    """Flat fp32 vector -> [nblocks, 1024], zero padded.  Non-finite inputs are kept: the rotation
+    spreads them over their block, and ``quantize`` then sends that block as zeros."""
     x = np.asarray(x, dtype=F32).reshape(-1)
     nb = (x.size + BLOCK - 1) // BLOCK
     out = np.zeros(nb * BLOCK, dtype=F32)
-    out[: x.size] = np.where(np.isfinite(x), x, F32(0))
+    out[: x.size] = x
     return out.reshape(nb, BLOCK)
 
 
 def _butterflies(v: np.ndarray, stages) -> np.ndarray:
     v = v.astype(F32, copy=True)
     idx = np.arange(BLOCK)
-    for bit in stages:
-        lo = idx[(idx >> bit) & 1 == 0]
-        hi = lo | (1 << bit)
-        a, b = v[:, lo], v[:, hi]
-        v[:, lo], v[:, hi] = a + b, a - b
+    with np.errstate(invalid="ignore", over="ignore"):
+        for bit in stages:
+            lo = idx[(idx >> bit) & 1 == 0]
+            hi = lo | (1 << bit)
+            a, b = v[:, lo], v[:, hi]
+            v[:, lo], v[:, hi] = a + b, a - b
     return v
 
 
@@ -102,47 +109,58 @@ TAG_STRATIFIED = 0x4000
 
 
 def quantize(y: np.ndarray, bits: int, block_idx: np.ndarray, tag: int, step: int, seed: int,
-             rank: int = 0, world: int = 1) -> Tuple[np.ndarray, np.ndarray]:
+             rank: int = 0, world: int = 1, layout: str = "simt") -> Tuple[np.ndarray, np.ndarray]:
     """Rotated blocks [nb, 1024] -> (codes uint8 [nb, 32 lanes, 32 regs], scale f32 [nb]).
+
+    A block whose largest magnitude is NaN, infinite or below 1e-30 is sent as zeros: scale 0 and
+    every code equal to R.
 
     With TAG_STRATIFIED set in `tag` the uniform of value k is the rank's stratum of a uniform all
     ranks share: u = (((rank + shift) mod W) * 256 + byte_k + 0.5) / (256 W), where shift is the
     byte of the neighbouring value ((k + 1) mod 32 of the same lane)."""
     R = qmax(bits)
     y = y.astype(F32, copy=False)
-    absmax = np.max(np.abs(y), axis=1)
+    rho = LAYOUTS[layout]
+    absmax = np.max(np.abs(y), axis=1)  # NaN if any coefficient is NaN
     with np.errstate(divide="ignore", invalid="ignore"):
         ok = (absmax >= F32(1e-30)) & np.isfinite(absmax)
         scale = np.where(ok, absmax / F32(R), F32(0)).astype(F32)
         inv = np.where(ok, F32(R) / absmax, F32(0)).astype(F32)
+    y = np.where(ok[:, None], y, F32(0))
     r8 = philox.block_uniforms8(block_idx, tag & ~TAG_STRATIFIED, step, seed)  # [nb, 32, 32]
     if tag & TAG_STRATIFIED and world > 1:
         shift = np.roll(r8, -1, axis=2).astype(np.int64)
         stratum = ((rank + shift) % world).astype(F32)
         u = ((stratum * F32(256.0) + r8.astype(F32)) + F32(0.5)) * F32(1.0 / (256.0 * world))
+        t = fma32(y[:, rho], inv[:, None, None], u)
+        code = np.floor(t).astype(np.int32) + R
     else:
-        u = (r8.astype(F32) + F32(0.5)) * F32(1.0 / 256.0)
-    t = fma32(y[:, RHO], inv[:, None, None], u)
-    code = np.clip(np.floor(t), -R, R).astype(np.int32) + R
+        a = r8.astype(F32) + F32(32768.5)  # 2^15 + byte + 0.5, exact in fp32
+        t = fma32(y[:, rho], (inv * F32(256.0))[:, None, None], a)
+        code = np.floor(t * F32(1.0 / 256.0)).astype(np.int32) - 128 + R
+    # |y| <= absmax keeps the code inside [0, 2 R]: no clamp
+    assert code.min(initial=R) >= 0 and code.max(initial=R) <= 2 * R
     return code.astype(np.uint8), scale
 
 
-def dequantize_add(codes: np.ndarray, scale: np.ndarray, bits: int, acc: np.ndarray) -> np.ndarray:
+def dequantize_add(codes: np.ndarray, scale: np.ndarray, bits: int, acc: np.ndarray,
+                   layout: str = "simt") -> np.ndarray:
     """acc [nb, 1024] (coefficient order) + decoded block, one fma per value."""
     R = qmax(bits)
     f = (codes.astype(np.int32) - R).astype(F32)
     out = acc.astype(F32, copy=True)
-    flat = RHO.reshape(-1)
-    out[:, flat] = fma32(f.reshape(codes.shape[0], BLOCK), scale[:, None], acc[:, flat])
+    flat = LAYOUTS[layout].reshape(-1)
+    with np.errstate(invalid="ignore", over="ignore"):
+        out[:, flat] = fma32(f.reshape(codes.shape[0], BLOCK), scale[:, None], acc[:, flat])
     return out
 
 
-def dequantize(codes: np.ndarray, scale: np.ndarray, bits: int) -> np.ndarray:
+def dequantize(codes: np.ndarray, scale: np.ndarray, bits: int, layout: str = "simt") -> np.ndarray:
     """(codes [nb,32,32], scale [nb]) -> rotated blocks [nb, 1024] in coefficient order."""
     R = qmax(bits)
     vals = (codes.astype(np.int32) - R).astype(F32) * scale[:, None, None].astype(F32)
     y = np.empty((codes.shape[0], BLOCK), dtype=F32)
-    y[:, RHO.reshape(-1)] = vals.reshape(codes.shape[0], BLOCK)
+    y[:, LAYOUTS[layout].reshape(-1)] = vals.reshape(codes.shape[0], BLOCK)
     return y
 
 
@@ -189,19 +207,19 @@ def from_message(msg: np.ndarray, nblocks: int, bits: int) -> Tuple[np.ndarray, 
 
 
 def encode_blocks(y: np.ndarray, bits: int, block_idx, tag: int, step: int, seed: int, rank: int = 0,
-                  world: int = 1) -> np.ndarray:
-    codes, scale = quantize(y, bits, np.asarray(block_idx), tag, step, seed, rank, world)
+                  world: int = 1, layout: str = "simt") -> np.ndarray:
+    codes, scale = quantize(y, bits, np.asarray(block_idx), tag, step, seed, rank, world, layout)
     return to_message(pack(codes, bits), scale)
 
 
-def decode_add_blocks(msg: np.ndarray, nblocks: int, bits: int, acc: np.ndarray) -> np.ndarray:
+def decode_add_blocks(msg: np.ndarray, nblocks: int, bits: int, acc: np.ndarray, layout: str = "simt") -> np.ndarray:
     words, scale = from_message(msg, nblocks, bits)
-    return dequantize_add(unpack(words, bits), scale, bits, acc)
+    return dequantize_add(unpack(words, bits), scale, bits, acc, layout)
 
 
-def decode_blocks(msg: np.ndarray, nblocks: int, bits: int) -> np.ndarray:
+def decode_blocks(msg: np.ndarray, nblocks: int, bits: int, layout: str = "simt") -> np.ndarray:
     words, scale = from_message(msg, nblocks, bits)
-    return dequantize(unpack(words, bits), scale, bits)
+    return dequantize(unpack(words, bits), scale, bits, layout)
 
 
 def nmse(estimate: np.ndarray, exact: np.ndarray) -> float:

@@ -89,7 +89,7 @@ __device__ __forceinline__ void mx_encode_block(const float (&v)[32], uint8_t* t
     codes[k + 1] = (two >> 8) & 0xFFu;
   }
   uint32_t w[B];
-  pack_codes<B>(codes, w);  // 32 codes of b bits -> b words, little-endian bit stream
+  pack_codes<B>(codes, w, 0u);  // 32 clean codes of b bits -> b words, little-endian bit stream
   uint32_t* dst = reinterpret_cast<uint32_t*>(tile + lane * MxGeom<B>::kLaneBytes);
 #pragma unroll
   for (int j = 0; j < B; ++j) dst[j] = w[j];

@@ -29,14 +29,9 @@ struct U4 {
 };
 
 DQ_HD void mulhilo(uint32_t a, uint32_t b, uint32_t& hi, uint32_t& lo) {
-#if defined(__CUDA_ARCH__)
-  hi = __umulhi(a, b);
-  lo = a * b;
-#else
-  uint64_t p = static_cast<uint64_t>(a) * b;
+  const uint64_t p = static_cast<uint64_t>(a) * b;  // one wide multiply on the device
   hi = static_cast<uint32_t>(p >> 32);
   lo = static_cast<uint32_t>(p);
-#endif
 }
 
 template <int ROUNDS = 10>

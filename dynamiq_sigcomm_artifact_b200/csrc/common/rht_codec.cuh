@@ -80,22 +80,28 @@ __device__ __forceinline__ void transpose_to_load(float (&v)[32], float* tile, i
   __syncwarp();
 }
 
-// bit t of the result = sign bit of the element a lane holds in register t of the load layout
-__device__ __forceinline__ uint32_t lane_sign_mask(const uint32_t* sign_words, int lane) {
-  uint32_t m = 0;
+// Sign tables.  The Rademacher diagonal is applied by multiplying with +-1.0 (forward) or +-c (inverse, c =
+// post_scale / 1024) read from two 1024-float tables in shared memory that a CTA builds once from the 32 sign
+// words; a packed multiply replaces the per-element bit extraction and xor.  Table order: element index.
+__device__ __forceinline__ void fill_sign_tables(float* sgn_fwd, float* sgn_inv, const uint32_t* sign_words, float c,
+                                                 int tid, int nthreads) {
+  for (int e = tid; e < 1024; e += nthreads) {
+    const bool neg = (sign_words[e >> 5] >> (e & 31)) & 1u;
+    sgn_fwd[e] = neg ? -1.0f : 1.0f;
+    sgn_inv[e] = neg ? -c : c;
+  }
+}
+
+// v (load layout) *= table (element order): eight 16-byte table reads and sixteen packed multiplies
+__device__ __forceinline__ void scale_by_table(float (&v)[32], const float* table, int lane) {
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    uint32_t w = sign_words[4 * j + (lane >> 3)];
-    m |= ((w >> ((lane & 7) * 4)) & 0xFu) << (4 * j);
+    const float4 q = *reinterpret_cast<const float4*>(table + j * 128 + lane * 4);
+    const float2 a = __fmul2_rn(make_float2(v[4 * j], v[4 * j + 1]), make_float2(q.x, q.y));
+    const float2 b = __fmul2_rn(make_float2(v[4 * j + 2], v[4 * j + 3]), make_float2(q.z, q.w));
+    v[4 * j] = a.x, v[4 * j + 1] = a.y, v[4 * j + 2] = b.x, v[4 * j + 3] = b.y;
   }
-  return m;
 }
-
-__device__ __forceinline__ float flip(float x, uint32_t bit) {
-  return __uint_as_float(__float_as_uint(x) ^ (bit << 31));
-}
-
-__device__ __forceinline__ float sanitize(float x) { return (fabsf(x) <= 3.402823466e38f) ? x : 0.0f; }
 
 template <typename T>
 struct Elem;
@@ -173,59 +179,97 @@ __device__ __forceinline__ void store_block(T* base, int valid, bool vec_ok, int
   }
 }
 
-// raw gradients (load layout) -> rotated coefficients (coefficient layout): y = H (s * x), unnormalised
-__device__ __forceinline__ void rotate_forward(float (&v)[32], uint32_t sign_mask, float* tile, int lane) {
-#pragma unroll
-  for (int t = 0; t < 32; ++t) v[t] = flip(sanitize(v[t]), (sign_mask >> t) & 1u);
+// raw gradients (load layout) -> rotated coefficients (coefficient layout): y = H (s * x), unnormalised.
+// Non-finite inputs are not filtered here: they reach every coefficient of the block, and the quantiser
+// then transmits the whole block as zeros.
+__device__ __forceinline__ void rotate_forward(float (&v)[32], const float* sgn_fwd, float* tile, int lane) {
+  scale_by_table(v, sgn_fwd, lane);
   butterflies32(v);
   transpose_to_coeff(v, tile, lane);
   butterflies32(v);
 }
 
 // rotated coefficients -> gradients in the load layout: x = s * (H y) * c, c = post_scale / 1024
-__device__ __forceinline__ void rotate_inverse(float (&v)[32], uint32_t sign_mask, float c, float* tile, int lane) {
+__device__ __forceinline__ void rotate_inverse(float (&v)[32], const float* sgn_inv, float* tile, int lane) {
   butterflies32(v);
   transpose_to_load(v, tile, lane);
   butterflies32(v);
-#pragma unroll
-  for (int t = 0; t < 32; ++t) v[t] = flip(__fmul_rn(v[t], c), (sign_mask >> t) & 1u);
+  scale_by_table(v, sgn_inv, lane);
 }
 
+__device__ __forceinline__ float sanitize(float x) { return (fabsf(x) <= 3.402823466e38f) ? x : 0.0f; }
+
+// Dense packing of 32 codes of B bits into B words.  `f[k]` = G + code k, where G (the bit pattern of the
+// quantiser's magic number) is the same for every k and has its low bits clear.  The words are built as
+// sum_k f[k] * 2^shift_k, one integer multiply-add per code, and the known contribution of G is subtracted
+// once per word; a code that straddles two words adds its high part with a shift.
 template <int B>
-__device__ __forceinline__ void pack_codes(const uint32_t (&c)[32], uint32_t (&w)[B]) {
+__device__ __forceinline__ void pack_codes(const uint32_t (&f)[32], uint32_t (&w)[B], uint32_t G) {
+  if constexpr (B == 8) {  // byte 0 of four values per word: three byte permutes
 #pragma unroll
-  for (int j = 0; j < B; ++j) w[j] = 0;
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t lo = __byte_perm(f[4 * j], f[4 * j + 1], 0x0040u);
+      const uint32_t hi = __byte_perm(f[4 * j + 2], f[4 * j + 3], 0x0040u);
+      w[j] = __byte_perm(lo, hi, 0x5410u);
+    }
+  } else {
+    uint32_t gsum[B];  // multiples of G accumulated in each word (compile-time after unrolling)
 #pragma unroll
-  for (int k = 0; k < 32; ++k) {
-    constexpr int dummy = 0;
-    (void)dummy;
-    const int off = k * B, wi = off >> 5, sh = off & 31;
-    w[wi] |= c[k] << sh;
-    if (sh + B > 32) w[wi + 1] |= c[k] >> (32 - sh);
+    for (int j = 0; j < B; ++j) w[j] = 0, gsum[j] = 0;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+      const int off = k * B, wi = off >> 5, sh = off & 31;
+      w[wi] += f[k] * (1u << sh);
+      gsum[wi] += 1u << sh;
+      if (sh + B > 32) {  // the code's top bits open the next word: (G + c) >> r = (G >> r) + (c >> r), r < B
+        w[wi + 1] += f[k] >> (32 - sh);
+        w[wi + 1] -= G >> (32 - sh);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < B; ++j) w[j] -= G * gsum[j];
   }
 }
 
 template <int B>
 __device__ __forceinline__ uint32_t unpack_code(const uint32_t (&w)[B], int k) {
   const int off = k * B, wi = off >> 5, sh = off & 31;
-  uint32_t x = w[wi] >> sh;
-  if (sh + B > 32) x |= w[wi + 1] << (32 - sh);
+  uint32_t x = (sh + B > 32) ? __funnelshift_r(w[wi], w[wi + 1], sh) : (w[wi] >> sh);
   return x & ((1u << B) - 1u);
 }
 
+// max(m, |a|, |b|) in one instruction (three-input max of sm_100); a NaN operand makes the result NaN
+__device__ __forceinline__ float max3_abs(float m, float a, float b) {
+  float d;
+  asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(m), "f"(fabsf(a)), "f"(fabsf(b)));
+  return d;
+}
+__device__ __forceinline__ float max_nan(float a, float b) {
+  float d;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+  return d;
+}
+
+// largest magnitude of the block; NaN if any coefficient is NaN
 __device__ __forceinline__ float warp_absmax(const float (&y)[32]) {
   float m = 0.0f;
 #pragma unroll
-  for (int k = 0; k < 32; ++k) m = fmaxf(m, fabsf(y[k]));
+  for (int k = 0; k < 32; k += 2) m = max3_abs(m, y[k], y[k + 1]);
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(kFullMask, m, o));
+  for (int o = 16; o > 0; o >>= 1) m = max_nan(m, __shfl_xor_sync(kFullMask, m, o));
   return m;
 }
 
 // Stochastic b-bit quantisation of a block in the coefficient layout.  Returns the block scale.
-//   code = clamp(floor(fma(y, R / absmax, u)), -R, R) + R,   u = (byte + 0.5) / 256
-// computed 256 times larger so that u needs no multiply, with the floor taken by a round-down
-// add of 1.5 * 2^31 (one ulp = 256 there): no int<->float conversion instruction is issued.
+//   code = floor(y * R / absmax + u) + R,   u = (byte + 0.5) / 256
+// computed 256 times larger and shifted by 2^15, so that every step is one instruction on bit patterns:
+//   a = 2^15 + byte + 0.5         one byte permute: the float 0x47'00'bb'80 has the byte at value 1
+//   t = fma(y, 256 R / absmax, a)
+//   g = t + (1.5 * 2^31 + 256 (R - 128))   rounded DOWN; one ulp = 256 there, so the low bits of g's
+//                                          pattern are floor((t - 2^15) / 256) + R = the code
+// No conversion, subtraction or clamp is issued.  No clamp is needed because |y| <= absmax holds exactly:
+// |y * (R / absmax)| <= R (1 + 2^-24), so t - 2^15 lies strictly inside (-256 R, 256 (R + 1)).
+// A block whose absmax is NaN, infinite or below 1e-30 is sent as zeros (scale 0, every code = R).
 //
 // Stratified ("correlated") rounding, strat_world > 1: all ranks draw the same byte per value and
 // rank r uses u = (((r + shift) mod W) * 256 + byte + 0.5) / (256 W), shift = the byte of the
@@ -242,22 +286,24 @@ __device__ __forceinline__ void draw_block_randoms(uint32_t (&rw)[8], uint32_t b
 }
 
 template <int B>
-__device__ __forceinline__ float quantize_block_rw(const float (&y)[32], uint32_t (&w)[B], const uint32_t (&rw)[8],
+__device__ __forceinline__ float quantize_block_rw(float (&y)[32], uint32_t (&w)[B], const uint32_t (&rw)[8],
                                                    int lane, int strat_rank = 0, int strat_world = 1) {
   constexpr int R = (1 << (B - 1)) - 1;
   const float m = warp_absmax(y);
   const bool ok = (m >= 1e-30f) && (m <= 3.402823466e38f);
   const float scale = ok ? __fdiv_rn(m, static_cast<float>(R)) : 0.0f;
   const float inv = ok ? __fdiv_rn(static_cast<float>(R), m) : 0.0f;
-  const float2 inv256 = make_float2(inv * 256.0f, inv * 256.0f);
-  const float2 half_off = make_float2(-8388607.5f, -8388607.5f);
-  const float2 magic = make_float2(3221225472.0f, 3221225472.0f);  // 1.5 * 2^31 = 0x4F400000
-  uint32_t c[32];
+  if (!ok) {  // warp-uniform and rare
+#pragma unroll
+    for (int k = 0; k < 32; ++k) y[k] = 0.0f;
+  }
+  uint32_t f[32];
   if (strat_world > 1) {
+    const float2 half_off = make_float2(-8388607.5f, -8388607.5f);
     const float cw = 1.0f / (256.0f * static_cast<float>(strat_world));
     const uint32_t recip = 65536u / static_cast<uint32_t>(strat_world) + 1u;  // x / W for x < 512
     const float2 inv2 = make_float2(inv, inv), cw2 = make_float2(cw, cw);
-    const float2 magic1 = make_float2(12582912.0f, 12582912.0f);  // 1.5 * 2^23 = 0x4B400000, one ulp = 1
+    const float2 magic1 = make_float2(12582912.0f + R, 12582912.0f + R);  // 1.5 * 2^23 + R, one ulp = 1
 #pragma unroll
     for (int k = 0; k < 32; k += 2) {
       float xs[2];
@@ -271,33 +317,30 @@ __device__ __forceinline__ float quantize_block_rw(const float (&y)[32], uint32_
       }
       const float2 u = __fmul2_rn(__fadd2_rn(make_float2(xs[0], xs[1]), half_off), cw2);
       const float2 t = __ffma2_rn(make_float2(y[k], y[k + 1]), inv2, u);
-      const float2 f = __fadd2_rd(t, magic1);
-      const int c0 = static_cast<int>(__float_as_uint(f.x)) - 0x4B400000 + R;
-      const int c1 = static_cast<int>(__float_as_uint(f.y)) - 0x4B400000 + R;
-      c[k] = static_cast<uint32_t>(max(0, min(2 * R, c0)));
-      c[k + 1] = static_cast<uint32_t>(max(0, min(2 * R, c1)));
+      const float2 g = __fadd2_rd(t, magic1);
+      f[k] = __float_as_uint(g.x);
+      f[k + 1] = __float_as_uint(g.y);
     }
   } else {
+    const float2 inv256 = make_float2(inv * 256.0f, inv * 256.0f);
+    const float magic_v = 3221225472.0f + 256.0f * (R - 128);  // 1.5 * 2^31 + 256 (R - 128): exact
+    const float2 magic = make_float2(magic_v, magic_v);
 #pragma unroll
     for (int k = 0; k < 32; k += 2) {
-      // 2^23 + byte as a float, straight from the byte (no conversion)
-      const float b0 = __uint_as_float(__byte_perm(rw[k >> 2], 0x4B000000u, 0x7650u | (k & 3)));
-      const float b1 = __uint_as_float(__byte_perm(rw[k >> 2], 0x4B000000u, 0x7650u | ((k + 1) & 3)));
-      const float2 u256 = __fadd2_rn(make_float2(b0, b1), half_off);  // byte + 0.5
-      const float2 t = __ffma2_rn(make_float2(y[k], y[k + 1]), inv256, u256);
-      const float2 f = __fadd2_rd(t, magic);
-      const int c0 = static_cast<int>(__float_as_uint(f.x)) - 0x4F400000 + R;
-      const int c1 = static_cast<int>(__float_as_uint(f.y)) - 0x4F400000 + R;
-      c[k] = static_cast<uint32_t>(max(0, min(2 * R, c0)));
-      c[k + 1] = static_cast<uint32_t>(max(0, min(2 * R, c1)));
+      const float a0 = __uint_as_float(__byte_perm(rw[k >> 2], 0x47000080u, 0x7504u | ((k & 3) << 4)));
+      const float a1 = __uint_as_float(__byte_perm(rw[k >> 2], 0x47000080u, 0x7504u | (((k + 1) & 3) << 4)));
+      const float2 t = __ffma2_rn(make_float2(y[k], y[k + 1]), inv256, make_float2(a0, a1));
+      const float2 g = __fadd2_rd(t, magic);
+      f[k] = __float_as_uint(g.x);
+      f[k + 1] = __float_as_uint(g.y);
     }
   }
-  pack_codes<B>(c, w);
+  pack_codes<B>(f, w, strat_world > 1 ? 0x4B400000u : 0x4F400000u);
   return scale;
 }
 
 template <int B>
-__device__ __forceinline__ float quantize_block(const float (&y)[32], uint32_t (&w)[B], uint32_t block_idx,
+__device__ __forceinline__ float quantize_block(float (&y)[32], uint32_t (&w)[B], uint32_t block_idx,
                                                 uint32_t tag, uint32_t step, uint32_t k0, uint32_t k1, int lane,
                                                 int strat_rank = 0, int strat_world = 1) {
   uint32_t rw[8];

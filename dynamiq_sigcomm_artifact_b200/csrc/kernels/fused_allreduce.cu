@@ -189,7 +189,7 @@ static void check_layout(const ARParams& p, int bits, int64_t mailbox_bytes, int
     TORCH_CHECK(st[0] >= 0 && st[0] < p.world, "step ", s, ": bad shard");
     TORCH_CHECK(st[3] == 0 || (st[2] >= 0 && st[2] + st[3] <= nslots), "step ", s, ": bad receive slots");
     if (st[4] == kOutSend) TORCH_CHECK(st[5] >= 0 && st[5] < p.world && st[6] >= 0 && st[6] < nslots, "step ", s, ": bad send");
-    if (st[4] == kOutFinal) TORCH_CHECK(p.world == 1 || (st[6] >= 0 && st[6] < nslots), "step ", s, ": bad final slot");
+    if (st[4] == kOutFinal) TORCH_CHECK(st[6] >= 0 && st[6] < nslots, "step ", s, ": bad final slot");
   }
 }
 

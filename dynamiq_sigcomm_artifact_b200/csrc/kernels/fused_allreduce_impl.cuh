@@ -6,66 +6,17 @@
 #include <cuda_runtime.h>
 
 #include "../common/rht_codec.cuh"
-#include "../common/rht_tc.cuh"
 #include "../common/sc_codec.cuh"
 #include "../common/mx_codec.cuh"
 #include "fused_allreduce.cuh"
+#include "fused_wire.cuh"
+#include "fused_rht_tc.cuh"
 
 namespace dq {
-
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned long long now_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ uint32_t ld_cg_u32(const uint32_t* p) { return __ldcg(p); }
-
-// Wait until *flag reaches `epoch`; false when the budget ran out.
-__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, unsigned long long budget_ns) {
-  if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
-  const unsigned long long t0 = now_ns();
-  unsigned spins = 0;
-  for (;;) {
-    if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
-    if ((++spins & 63u) == 0) {
-      if (now_ns() - t0 > budget_ns) return false;
-      __nanosleep(64);
-    }
-  }
-}
-
-// ---- per-warp bulk prefetch (TMA engine, 1-D form) of the next raw block --------------------
-// Lane 0 arms the warp's mbarrier with the byte count and issues one cp.async.bulk of a whole
-// block (4 KiB fp32 / 2 KiB bf16) from this GPU's own bucket into the warp's staging buffer; the
-// warp later waits on the barrier's phase (bounded) and reads the block from shared memory.
-
-using tc::mbar_init;
-using tc::mbar_wait;
-__device__ __forceinline__ void bulk_prefetch(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
-  tc::bulk_load(dst_smem, src_gmem, bytes, bar);
-}
 
 struct RawItem {
   int s, blk;  // program step and block index; s < 0: none
 };
-
-// [lo, hi) of CTA `cta` inside the shard of step s, and the shard's first block
-__device__ __forceinline__ void step_range(const ARParams& p, int s, int cta, int per_cta, int& shard_lo, int& lo,
-                                           int& hi) {
-  const int shard = p.steps[s][0];
-  shard_lo = min(shard * p.blocks_per_shard, p.nblocks);
-  const int shard_hi = min(shard_lo + p.blocks_per_shard, p.nblocks);
-  lo = min(shard_lo + cta * per_cta, shard_hi);
-  hi = min(lo + per_cta, shard_hi);
-}
 
 // the next block after (s, blk) that this warp will read as raw gradients (blk < 0: start of step s)
 __device__ __forceinline__ RawItem next_raw_item(const ARParams& p, int s, int blk, int cta, int per_cta, int warp,
@@ -80,20 +31,19 @@ __device__ __forceinline__ RawItem next_raw_item(const ARParams& p, int s, int b
   return RawItem{-1, -1};
 }
 
-// Shared-memory layout of a CTA (nwarps warps, nwg = nwarps / 4 warpgroups):
-//   SIMT rotation:   [tile: nwarps x 4 KiB][stage: nwarps x 4 KiB][sign words][prefetch barriers]
-//   tensor rotation: [operands: nwg x 18 KiB][stage: nwarps x 4 KiB][H_32][sign words][prefetch barriers]
-//                    [MMA barriers: nwg][TMEM slot][error flag]
+// Shared-memory layout of a CTA of the SIMT bodies (nwarps warps):
+//   [tile: nwarps x 4 KiB][stage: nwarps x 4 KiB (optional)][sign table fwd][sign table inv][sign words]
+//   [prefetch barriers]
+// The tensor-core rotation has its own layout (fused_rht_tc.cuh).
 template <bool TC>
 __host__ __device__ constexpr size_t fused_smem_bytes(int threads, bool stage = true) {
-  const size_t nwarps = threads / 32, nwg = threads / 128;
-  return (TC ? nwg * tc::kOperandBytes + tc::kHBytes + nwg * 8 + 16 : nwarps * kBlock * 4) +
-         (stage ? nwarps * kBlock * 4 : 0) + 32 * 4 + nwarps * 8 + 128;
+  if (TC) return rht_tc_smem_bytes(threads, stage);
+  const size_t nwarps = threads / 32;
+  return nwarps * kBlock * 4 + (stage ? nwarps * kBlock * 4 : 0) + 2 * 4096 + 32 * 4 + nwarps * 8 + 128;
 }
 
 template <int BITS, typename T, int CODEC>
-__device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
-  constexpr bool TC = CODEC == kCodecRhtTc;
+__device__ __forceinline__ void fused_simt_body(const ARParams& p) {
   constexpr bool MX = CODEC == kCodecMx;      // block-float codes (8 / 6 / 4 bit) with native conversions
   constexpr bool CAST = CODEC == kCodecCast;  // identity wire: bf16 (16) or fp32 (32) values
   constexpr bool MIX = CODEC == kCodecScMixAee || CODEC == kCodecScMixMee;  // superchunk records of per-superchunk width
@@ -105,67 +55,27 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
   const int cta = blockIdx.x, G = gridDim.x;
-  constexpr int GS = TC ? 4 : 1;  // warps that move through the block loop together
-  const int nwg = nwarps / 4, wg = warp >> 2, wi = warp & 3;
 
   uint8_t* cursor = smem_raw;
-  float* tile = nullptr;
-  uint8_t* operands = nullptr;
-  if (TC) {
-    operands = cursor;
-    cursor += static_cast<size_t>(nwg) * tc::kOperandBytes;
-  } else {
-    tile = reinterpret_cast<float*>(cursor) + warp * kBlock;
-    cursor += static_cast<size_t>(nwarps) * kBlock * 4;
-  }
-  const bool use_stage = TC || p.prefetch != 0;  // the tensor-core path stages its operands through it
+  float* tile = reinterpret_cast<float*>(cursor) + warp * kBlock;
+  cursor += static_cast<size_t>(nwarps) * kBlock * 4;
+  const bool use_stage = p.prefetch != 0;
   float* stage = reinterpret_cast<float*>(cursor) + warp * kBlock;
   if (use_stage) cursor += static_cast<size_t>(nwarps) * kBlock * 4;
-  uint8_t* hmat = cursor;
-  if (TC) cursor += tc::kHBytes;
+  float* sgn_fwd = reinterpret_cast<float*>(cursor);
+  cursor += 4096;
+  float* sgn_inv = reinterpret_cast<float*>(cursor);
+  cursor += 4096;
   uint32_t* sign_words = reinterpret_cast<uint32_t*>(cursor);
   cursor += 32 * 4;
   uint64_t* bar = reinterpret_cast<uint64_t*>(cursor) + warp;
-  cursor += static_cast<size_t>(nwarps) * 8;
-  uint64_t* mma_bars = reinterpret_cast<uint64_t*>(cursor);
-  if (TC) cursor += static_cast<size_t>(nwg) * 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cursor);
-  int* tc_error = reinterpret_cast<int*>(cursor + 8);
 
   if (tid < 32) sign_words[tid] = sign_word(tid, p.step, p.bucket_id, p.seed_lo, p.seed_hi);
   if (lane == 0) mbar_init(bar, 1);
-  if (TC) {
-    tc::fill_hadamard32(hmat, tid, blockDim.x);
-    if (tid < nwg) tc::mbar_init(&mma_bars[tid], 1);
-    if (tid == 0) *tc_error = 0;
-  }
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  const uint32_t tmem_cols = static_cast<uint32_t>(nwg) * 64u;  // D1 | D2 per warpgroup; 64 / 128 / 256
-  if (TC) {
-    if (warp == 0) tc::tmem_alloc(tmem_slot, tmem_cols);
-    tc::fence_async_smem();
-    tc::tc_fence_before();
-  }
   __syncthreads();
-  if (TC) tc::tc_fence_after();
-  const uint32_t sign_mask = lane_sign_mask(sign_words, lane);
-  const uint32_t col_signs = lane_col_signs(sign_words, lane);  // tensor path: element 32 m + lane
-
-  TcGroup tg{};
-  uint32_t tmem_base = 0;
-  if (TC) {
-    tmem_base = *tmem_slot;
-    tg.a = operands + static_cast<size_t>(wg) * tc::kOperandBytes;
-    tg.hmat = tc::smem_u32(hmat);
-    tg.bar = &mma_bars[wg];
-    tg.tmem_wg = tmem_base + static_cast<uint32_t>(wg) * 64u;
-    tg.tmem_d1 = tg.tmem_wg + (static_cast<uint32_t>(wi * 32) << 16);
-    tg.parity = 0;
-    tg.barrier_id = 1 + wg;
-    tg.wi = wi;
-    tg.leader = (wi == 0 && lane == 0);
-    tg.error = tc_error;
-  }
+  if (!SC) fill_sign_tables(sgn_fwd, sgn_inv, sign_words, p.finish_scale, tid, blockDim.x);
+  __syncthreads();
 
   T* bucket = static_cast<T*>(p.bucket);
   const bool vec_ok = (reinterpret_cast<uintptr_t>(bucket) & 15u) == 0;
@@ -189,12 +99,7 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
   };
   issue_prefetch(next_raw_item(p, 0, -1, cta, per_cta, warp, nwarps));
 
-  auto fail = [&](uint32_t code, int s, int slot) {
-    if (atomicCAS(p.status, kOk, code) == kOk) {
-      p.status[1] = (static_cast<uint32_t>(s) << 16) | static_cast<uint32_t>(cta);
-      p.status[2] = static_cast<uint32_t>(slot);
-    }
-  };
+  auto fail = [&](uint32_t code, int s, int slot) { report_failure(p, code, s, slot); };
 
   bool aborted = false;
   for (int s = 0; s < p.nsteps && !aborted; ++s) {
@@ -223,9 +128,8 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
     const bool rotate_in = (out != kOutDecode) && (local == kLocalRaw);
     const bool rotate_out = (out == kOutFinal) || (out == kOutDecode);
 
-    for (int base = lo + GS * (warp / GS); base < hi; base += nwarps) {
-      const int blk = base + (warp % GS);
-      const bool active = blk < hi;  // warps of a warpgroup past the end still join its barriers
+    for (int blk = lo + warp; blk < hi; blk += nwarps) {
+      constexpr bool active = true;
       const int bs = blk - shard_lo;  // block index inside the shard = inside the message
       const long long e0 = static_cast<long long>(blk) * kBlock;
       const int valid = static_cast<int>(min(static_cast<long long>(kBlock), p.n - e0));
@@ -340,17 +244,7 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
           load_block<T>(bucket + e0, kBlock, vec_ok, lane, v);
         }
       }
-      uint32_t rw[8];  // rounding bytes, drawn under the first tensor-core pass when there is one
-      const bool have_rw = TC && rotate_in && active && (out == kOutSend || out == kOutFinal);
-      if (rotate_in) {
-        if (TC) {
-          rotate_forward_tc(v, sign_mask, tg, lane, [&]() {
-            if (have_rw) draw_block_randoms(rw, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi, lane);
-          });
-        } else {
-          rotate_forward(v, sign_mask, tile, lane);
-        }
-      }
+      if (rotate_in) rotate_forward(v, sgn_fwd, tile, lane);
 
       if (active && out != kOutDecode) {
         if (nrecv > 0) dequantize_add_block<RB>(w, scale, v);
@@ -371,9 +265,8 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
         }
       } else if (out == kOutSend) {
         if (active) {
-          scale = have_rw ? quantize_block_rw<RB>(v, w, rw, lane, p.rank, strat_world)
-                          : quantize_block<RB>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi,
-                                                 lane, p.rank, strat_world);
+          scale = quantize_block<RB>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi, lane,
+                                     p.rank, strat_world);
           if (!p.no_transmit) {
             uint8_t* slot = p.mail[dst] + static_cast<unsigned long long>(send_slot) * p.slot_stride;
             uint32_t* codes = reinterpret_cast<uint32_t*>(slot) + static_cast<size_t>(bs) * (RB * 32);
@@ -385,9 +278,7 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
       } else {
         if (active) {
           if (out == kOutFinal) {
-            scale = have_rw ? quantize_block_rw<RB>(v, w, rw, lane)
-                            : quantize_block<RB>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi,
-                                                   lane);
+            scale = quantize_block<RB>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi, lane);
             if (!p.no_transmit) {
               for (int peer = 0; peer < p.world; ++peer) {
                 if (peer == p.rank) continue;
@@ -402,14 +293,8 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
           // kOutDecode: w / scale were loaded from the all-gather slot above
           dequantize_block<RB>(w, scale, v);
         }
-        if (rotate_out) {
-          if (TC) rotate_inverse_tc(v, col_signs, p.finish_scale, tg, lane);
-          else rotate_inverse(v, sign_mask, p.finish_scale, tile, lane);
-        }
-        if (active) {
-          if (TC) store_block_cols<T>(bucket + e0, valid, lane, v);
-          else store_block<T>(bucket + e0, valid, vec_ok, lane, v);
-        }
+        if (rotate_out) rotate_inverse(v, sgn_inv, tile, lane);
+        store_block<T>(bucket + e0, valid, vec_ok, lane, v);
       }
       }  // rotation codec
     }
@@ -429,16 +314,20 @@ __device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
   }
 
   if (aborted && pf.s >= 0) mbar_wait(bar, pf_parity);  // let this warp's copy in flight land before leaving
-  if (TC) {
-    if (tid == 0 && *tc_error) fail(kErrMmaTimeout, 0, -1);
-    tc::tc_fence_before();
-    __syncthreads();
-    if (warp == 0) tc::tmem_dealloc(tmem_base, tmem_cols);
-  }
 }
 
 template <int BITS, typename T, int CODEC>
-__global__ void __launch_bounds__(512, 1) fused_allreduce_kernel(const __grid_constant__ ARParams p) {
+__device__ __forceinline__ void fused_allreduce_body(const ARParams& p) {
+  if constexpr (CODEC == kCodecRhtTc) rht_tc_body<BITS, T>(p);
+  else fused_simt_body<BITS, T, CODEC>(p);
+}
+
+// largest CTA of a codec's kernels (the tensor-core body trades a warpgroup for registers)
+template <int CODEC>
+constexpr int max_cta_threads() { return CODEC == kCodecRhtTc ? 512 : 512; }
+
+template <int BITS, typename T, int CODEC>
+__global__ void __launch_bounds__(max_cta_threads<CODEC>(), 1) fused_allreduce_kernel(const __grid_constant__ ARParams p) {
   fused_allreduce_body<BITS, T, CODEC>(p);
 }
 
@@ -446,7 +335,7 @@ __global__ void __launch_bounds__(512, 1) fused_allreduce_kernel(const __grid_co
 // collective used by the standalone codec ops and by tests.  Cooperative, so that CTAs that
 // wait on one another are co-resident.
 template <int BITS, typename T, int CODEC>
-__global__ void __launch_bounds__(512, 1) fused_allreduce_multi_kernel(const ARParams* __restrict__ plist) {
+__global__ void __launch_bounds__(max_cta_threads<CODEC>(), 1) fused_allreduce_multi_kernel(const ARParams* __restrict__ plist) {
   fused_allreduce_body<BITS, T, CODEC>(plist[blockIdx.y]);
 }
 
@@ -454,10 +343,9 @@ template <int BITS, typename T, int CODEC>
 void launch_one(const ARParams* host_params, const ARParams* dev_params, int nranks, int ctas, int threads,
                 cudaStream_t stream) {
   constexpr bool TC = CODEC == kCodecRhtTc;
-  TORCH_CHECK(!TC || threads == 128 || threads == 256 || threads == 512,
-              "the tensor-core rotation needs 1, 2 or 4 whole warpgroups (128, 256 or 512 threads): TMEM columns are "
-              "allocated in powers of two");
-  const bool stage = TC || host_params == nullptr || host_params->prefetch != 0;
+  TORCH_CHECK(!TC || (threads % 128 == 0 && threads >= 128 && threads <= 512),
+              "the tensor-core rotation runs with 1 to 4 whole warpgroups (128, 256, 384 or 512 threads)");
+  const bool stage = host_params == nullptr || host_params->prefetch != 0;
   const size_t smem = fused_smem_bytes<TC>(threads, stage);
   const void* fn = nranks == 1 ? reinterpret_cast<const void*>(&fused_allreduce_kernel<BITS, T, CODEC>)
                                : reinterpret_cast<const void*>(&fused_allreduce_multi_kernel<BITS, T, CODEC>);

@@ -28,9 +28,12 @@ class RhtCodecCPU:
 
     block = cr.BLOCK
 
-    def __init__(self, bits: int, seed: int, step: int, bucket: int, world: int, rank: int = 0):
+    def __init__(self, bits: int, seed: int, step: int, bucket: int, world: int, rank: int = 0,
+                 layout: str = "simt"):
+        """`layout`: which lane / register holds which coefficient on the wire ("simt": register
+        butterflies, "tc": tensor-core rotation; see ``codec_ref``)."""
         self.bits, self.seed, self.step, self.bucket, self.world = bits, seed, step, bucket, world
-        self.rank = rank
+        self.rank, self.layout = rank, layout
         self.signs = philox.sign_vector(step, bucket, seed)
         # the RNG stream id mixes the bucket in so that buckets do not share uniforms
         self._tag_base = (bucket & 0xFFFF) << 16
@@ -43,13 +46,13 @@ class RhtCodecCPU:
 
     def encode(self, y: np.ndarray, block_idx: np.ndarray, tag: int) -> np.ndarray:
         return cr.encode_blocks(y, self.bits, block_idx, self._tag_base | tag, self.step, self.seed, self.rank,
-                                self.world)
+                                self.world, self.layout)
 
     def decode(self, msg: np.ndarray, nblocks: int) -> np.ndarray:
-        return cr.decode_blocks(msg, nblocks, self.bits)
+        return cr.decode_blocks(msg, nblocks, self.bits, self.layout)
 
     def decode_add(self, msg: np.ndarray, nblocks: int, acc: np.ndarray) -> np.ndarray:
-        return cr.decode_add_blocks(msg, nblocks, self.bits, acc)
+        return cr.decode_add_blocks(msg, nblocks, self.bits, acc, self.layout)
 
     def finish(self, y: np.ndarray) -> np.ndarray:
         return cr.rotate_inv(y, self.signs, 1.0 / self.world)
@@ -65,6 +68,7 @@ class LocalTransport:
         self.sent_bytes = [0] * world
         self.timeout = timeout
         self.drop = drop
+        self.log: Dict[tuple, np.ndarray] = {}  # (src, dst, slot) -> message bytes, every message ever sent
 
     def _box(self, rank: int, slot: int) -> "queue.Queue":
         with self.lock:
@@ -83,6 +87,8 @@ class LocalEndpoint:
 
     def send(self, dst: int, slot: int, msg: np.ndarray) -> None:
         self.t.sent_bytes[self.rank] += msg.nbytes
+        with self.t.lock:
+            self.t.log[(self.rank, dst, slot)] = msg.copy()
         if self.t.drop is not None and self.t.drop(self.rank, dst, slot):
             return
         self.t._box(dst, slot).put(msg.copy())
@@ -183,7 +189,8 @@ def run_rank(x: np.ndarray, codec, rank: int, world: int, topology: str, ep, cor
 
 def simulate_allreduce(xs: Sequence[np.ndarray], bits: int, topology: str = "ring", seed: int = 0,
                        step: int = 0, bucket: int = 0, codec_factory=None, return_transport: bool = False,
-                       transport: Optional[LocalTransport] = None, correlated: bool = False):
+                       transport: Optional[LocalTransport] = None, correlated: bool = False,
+                       layout: str = "simt"):
     """Run all ranks of one collective as threads; returns the per-rank results."""
     world = len(xs)
     transport = transport or LocalTransport(world)
@@ -192,7 +199,8 @@ def simulate_allreduce(xs: Sequence[np.ndarray], bits: int, topology: str = "rin
 
     def work(r: int) -> None:
         try:
-            codec = (codec_factory or RhtCodecCPU)(bits, seed, step, bucket, world, r)
+            codec = (codec_factory(bits, seed, step, bucket, world, r) if codec_factory
+                     else RhtCodecCPU(bits, seed, step, bucket, world, r, layout))
             out[r] = run_rank(np.asarray(xs[r], dtype=np.float32), codec, r, world, topology, transport.endpoint(r),
                               correlated)
         except BaseException as e:  # surfaced to the caller below

@@ -128,7 +128,7 @@ def build_program(rank: int, world: int, topology: str, correlated: bool = False
     if topology not in TOPOLOGIES:
         raise ValueError(f"unknown topology {topology!r}")
     if W == 1:
-        return [Step(shard=0, out=OUT_FINAL, tag=TAG_FINAL)]
+        return [Step(shard=0, out=OUT_FINAL, tag=TAG_FINAL, send_slot=ag_slot(1, topology, 0))]
     steps: List[Step] = []
     if topology == "ring":
         right = (rank + 1) % W

@@ -121,16 +121,34 @@ class SymmetricBuffer:
         return self.ops.wrap_ptr(self.local_ptr, self.nbytes, self.device)
 
     def close(self) -> None:
+        """Unmap the peers' buffers and free this rank's.  Collective: a rank frees its allocation only after
+        every rank has closed its mapping of it (freeing memory that a peer still has mapped is undefined
+        behaviour), hence two barriers.  If a barrier fails (a rank is gone), the local allocation is leaked
+        on purpose rather than freed under a possible mapping, and the failure is logged."""
         if self._closed:
             return
         self._closed = True
         torch.cuda.synchronize(self.device)
-        if self.world > 1 and dist.is_initialized():
-            try:
-                dist.barrier(group=self.group)
-            except Exception:
-                pass
+        collective = self.world > 1 and dist.is_initialized()
+        safe_to_free = True
+        if collective:
+            safe_to_free = self._barrier("before unmapping the peers")
         for r, p in enumerate(self.ptrs):
             if r != self.rank:
                 self.ops.symm_close(p)
-        self.ops.symm_free(self.local_ptr)
+        if collective and safe_to_free:
+            safe_to_free = self._barrier("before freeing the local allocation")
+        if safe_to_free:
+            self.ops.symm_free(self.local_ptr)
+
+    def _barrier(self, what: str) -> bool:
+        import logging
+
+        try:
+            dist.barrier(group=self.group)
+            return True
+        except Exception as e:  # a peer never arrived: keep going, but say so and do not free
+            logging.getLogger(__name__).warning(
+                "rank %d: barrier %s failed (%s); the %d-byte symmetric allocation is not freed", self.rank, what,
+                e, self.nbytes)
+            return False

@@ -51,8 +51,10 @@ def make_input(numel: int, rank: int, seed: int, device) -> torch.Tensor:
     return x * s.repeat_interleave(BLOCK)[:numel]
 
 
-def time_op(fn, prepare, iters: int, warmup: int) -> float:
-    """Mean device milliseconds of fn(); prepare() runs before each call, outside the interval."""
+def time_op(fn, prepare, iters: int, warmup: int, reps: int = 1) -> float:
+    """Mean device milliseconds of fn(); prepare() runs before each timed interval, outside it.
+    With reps > 1 an interval holds that many back-to-back calls (the device stays busy, so the
+    host's launch latency is not part of the figure) and the result is per call."""
     for _ in range(warmup):
         prepare()
         fn()
@@ -64,10 +66,11 @@ def time_op(fn, prepare, iters: int, warmup: int) -> float:
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        fn()
+        for _ in range(reps):
+            fn()
         e1.record()
         torch.cuda.synchronize()
-        total += e0.elapsed_time(e1)
+        total += e0.elapsed_time(e1) / reps
     ms = total / iters
     if dist.is_initialized():
         t = torch.tensor([ms], device="cuda", dtype=torch.float64)
@@ -183,18 +186,26 @@ def run_kernels(args) -> None:
             "hop": (sch.Step(shard=0, recv_slot=0, nrecv=1, out=sch.OUT_SEND, dst=0, send_slot=1,
                              tag=sch.TAG_ENCODE + 1), 4 * numel + 2 * msg),
             "decode": (sch.Step(shard=0, recv_slot=0, nrecv=1, out=sch.OUT_DECODE), 4 * numel + msg),
-            "final": (sch.Step(shard=0, recv_slot=0, nrecv=1, out=sch.OUT_FINAL, tag=sch.TAG_FINAL), 8 * numel + msg),
+            "final": (sch.Step(shard=0, recv_slot=0, nrecv=1, out=sch.OUT_FINAL, tag=sch.TAG_FINAL, send_slot=1),
+                      8 * numel + msg),
         }
         for name, (step, nbytes) in progs.items():
+            if args.stages and name not in args.stages.split(","):
+                continue
             prog = torch.tensor([[step.as_ints()]], dtype=torch.int32)
             ms = time_op(lambda: cl.run([work], prog, bits, seed=args.seed, preset_flags=True),
-                         lambda: work.copy_(x), args.iters, args.warmup)
+                         lambda: work.copy_(x), args.iters, args.warmup, args.reps)
             cl.check()
             row = {"kernel": f"rht_{name}", "bits": bits, "numel": numel, "ms": ms, "gbs": nbytes / ms / 1e6,
                    "gelem_s": numel / ms / 1e6, "hbm_fraction_of_measured": nbytes / ms / 1e6 / hbm,
-                   "ctas": args.ctas, "threads": args.threads, "rotation": args.rotation}
+                   "ctas": args.ctas, "threads": args.threads, "rotation": args.rotation, "reps": args.reps}
             rows.append(row)
             print(json.dumps(row), flush=True)
+    if args.rht_only:
+        if args.out:
+            with open(args.out, "w") as f:
+                json.dump(rows, f, indent=1)
+        return
     from ..ops import require
 
     dq = require()
@@ -251,6 +262,9 @@ def main(argv=None) -> None:
     ap.add_argument("--ctas", type=int, default=148)
     ap.add_argument("--threads", type=int, default=512)
     ap.add_argument("--rotation", default="simt", choices=["simt", "tc"])
+    ap.add_argument("--reps", type=int, default=1, help="--kernels: back-to-back launches per timed interval")
+    ap.add_argument("--stages", default="", help="--kernels: comma list out of encode,hop,decode,final (default all)")
+    ap.add_argument("--rht-only", action="store_true", help="--kernels: only the rotation codec's stages")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--seed", type=int, default=1)

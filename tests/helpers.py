@@ -17,3 +17,16 @@ def lognormal_block_grad(n: int, seed: int, sigma: float = 2.0) -> np.ndarray:
     nb = (n + 1023) // 1024
     s = np.exp(sigma * rng.standard_normal(nb)).astype(np.float32)
     return (g * np.repeat(s, 1024)[:n]).astype(np.float32)
+
+
+def small_int_grad(n: int, seed: int) -> np.ndarray:
+    """Integers in [-31, 31] times a power of two per 1024-element block.  A 1024-point Hadamard
+    transform of such a block is exact in any arithmetic that keeps 11 significant bits of its inputs
+    and of the 32-term partial sums (|partial sum| <= 992), which is what a single-TF32 tensor-core
+    rotation provides: on these inputs it must agree with fp32 butterflies bit for bit."""
+    rng = np.random.default_rng(seed)
+    g = np.clip(np.rint(rng.standard_normal(n) * 8.0), -31, 31)
+    g[rng.random(n) < 0.3] = 0
+    nb = (n + 1023) // 1024
+    e = rng.integers(-6, 7, nb)
+    return (g * np.repeat(np.exp2(e), 1024)[:n]).astype(np.float32)

@@ -66,10 +66,29 @@ def test_encode_is_deterministic_and_stream_dependent():
     assert a.size == cr.payload_bytes(4, 5)
 
 
-def test_nonfinite_inputs_are_zeroed():
-    x = np.ones(1024, dtype=np.float32)
+def test_a_block_with_nonfinite_values_is_sent_as_zeros():
+    """NaN / Inf reach every coefficient of their block; the quantiser then sends scale 0 and the
+    zero code everywhere, and the neighbouring blocks are untouched."""
+    x = np.ones(2048, dtype=np.float32)
     x[3], x[77] = np.inf, np.nan
-    blk = cr.to_blocks(x)
-    assert np.isfinite(blk).all() and blk[0, 3] == 0 and blk[0, 77] == 0
+    signs = philox.sign_vector(0, 0, 1)
+    y = cr.rotate_fwd(cr.to_blocks(x), signs)
+    assert not np.isfinite(y[0]).any() and np.isfinite(y[1]).all()
+    codes, scale = cr.quantize(y, 4, np.arange(2), 0, 0, 0)
+    assert scale[0] == 0 and (codes[0] == cr.qmax(4)).all() and scale[1] > 0
+    back = cr.rotate_inv(cr.dequantize(codes, scale, 4), signs)
+    assert (back[0] == 0).all() and cr.nmse(back[1], np.ones(1024)) < 0.2
     codes, scale = cr.quantize(np.zeros((1, 1024), np.float32), 4, np.arange(1), 0, 0, 0)
     assert scale[0] == 0 and (codes == cr.qmax(4)).all()
+
+
+def test_tensor_core_layout_is_a_permutation_of_the_same_codec():
+    """The two wire layouts carry the same codes in a different lane / register order."""
+    y = cr.rotate_fwd(cr.to_blocks(heavy_tail_grad(4096, 4)), philox.sign_vector(0, 0, 9))
+    for layout in ("simt", "tc"):
+        msg = cr.encode_blocks(y, 5, np.arange(4), 0x100, 3, 9, layout=layout)
+        back = cr.decode_blocks(msg, 4, 5, layout=layout)
+        assert cr.nmse(back, y) < 0.02
+        acc = cr.decode_add_blocks(msg, 4, 5, y, layout=layout)
+        assert np.allclose(acc, back + y, rtol=1e-6, atol=1e-6)
+    assert sorted(cr.RHO_TC.reshape(-1)) == list(range(1024))

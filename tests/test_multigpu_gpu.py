@@ -1,0 +1,36 @@
+"""Launches the multi-process oracle check (tests/multigpu/check_collective.py) when the machine has
+at least two GPUs; skipped on a single-GPU machine."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("rotation", ["tc", "simt"])
+def test_collective_over_peer_mappings_matches_the_simulator(rotation, tmp_path):
+    ngpu = torch.cuda.device_count()
+    if ngpu < 2:
+        pytest.skip("needs at least two GPUs")
+    n = 4 if ngpu >= 4 else 2
+    out = tmp_path / "summary.json"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+           os.path.join(ROOT, "tests", "multigpu", "check_collective.py"), "--rotation", rotation, "--quick",
+           "--stress", "60", "--out", str(out)]
+    res = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    summary = json.loads(out.read_text())
+    assert summary["ok"] and summary["collectives_checked"] >= 60
