@@ -53,7 +53,86 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--sparse-embedding", type=int, default=-1, help="-1: automatic, 0 / 1: force off / on")
     ap.add_argument("--bucket-cap-mb", type=int, default=0, help="0: 25 MB (GPT-2, BERT) or 100 MB (Llama 1.2B)")
     ap.add_argument("--rotation", default="simt", choices=["simt", "tc"])
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the collective self-check and the same-engine fp32 comparison after the timed regions")
     return ap.parse_args()
+
+
+def collective_self_check(tr, world: int, rank: int):
+    """One fused collective on a 4 MB tensor against the CPU step-program simulator, after the timed
+    regions: every rank regenerates all ranks' inputs, simulates the collective and compares its own
+    result bit for bit (register-butterfly rotation) or within TF32 accuracy (tensor-core rotation)."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from dynamiq_sigcomm_artifact_b200 import codec_ref as cr
+    from dynamiq_sigcomm_artifact_b200.parallel import cpu_backend as cb
+    from dynamiq_sigcomm_artifact_b200.parallel.fused import wire_bytes_per_rank
+
+    state = tr.state
+    if world == 1 or state is None or state["spec"].hook not in ("dynamiq", "dynamiq_bitrate") \
+            or state["spec"].family != "rht":
+        return None
+    from dynamiq_sigcomm_artifact_b200 import hooks
+
+    eng = hooks._engine(state)
+    n, bits, topo = (1 << 20) + 77, state["spec"].bits, state["spec"].topology
+    tc = eng.tensor_rotation
+    rng = [np.random.default_rng(1000 + r) for r in range(world)]
+    if tc:  # small integers times a power of two per block: the TF32 rotation is exact on them
+        xs = [(np.clip(np.rint(g.standard_normal(n) * 8), -31, 31) *
+               np.repeat(np.exp2(g.integers(-6, 7, (n + 1023) // 1024)), 1024)[:n]).astype(np.float32) for g in rng]
+    else:
+        xs = [g.standard_normal(n).astype(np.float32) * np.where(g.random(n) < 0.01, 100.0, 1.0).astype(np.float32)
+              for g in rng]
+    want = cb.simulate_allreduce(xs, bits, topo, seed=11, step=3, bucket=1, layout="tc" if tc else "simt")[rank]
+    buf = torch.from_numpy(xs[rank]).cuda()
+    eng.allreduce_(buf, bits, topo, seed=11, step=3, bucket_id=1)
+    eng.check()
+    got = buf.cpu().numpy()
+    if tc:
+        tol = 4e-3 * np.repeat(np.abs(cr.to_blocks(want)).max(axis=1), 1024)[:n] + 1e-30
+        ok = bool((np.abs(got - want) <= tol).all())
+    else:
+        ok = bool(np.array_equal(got, want))
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    exact = np.mean(np.stack(xs).astype(np.float64), 0)
+    return {"bit_exact": bool(flag.item()) and not tc, "within_tf32_tolerance": bool(flag.item()),
+            "rotation": "tc" if tc else "simt", "numel": n, "bits": bits, "topology": topo,
+            "nmse_vs_exact_mean": cr.nmse(got, exact), "collectives": int(state["stats"]["collectives"]) + 1,
+            "wire_bytes": int(state["stats"]["wire_bytes"]) + wire_bytes_per_rank(n, world, bits, "rht")}
+
+
+def same_engine_fp32(args, cfg_kwargs: dict, steps: int, warmup: int):
+    """The same trainer with the library's fp32 all-reduce as its hook: what compression itself buys."""
+    import torch
+    import torch.distributed as dist
+
+    from dynamiq_sigcomm_artifact_b200.train.engine import TrainConfig, Trainer
+
+    kw = dict(cfg_kwargs)
+    kw["method"] = "fp32"
+    tr = Trainer(TrainConfig(**kw))
+    batches = [tr.synthetic_batch(pinned=True).to(tr.device) for _ in range(4)]
+    for i in range(max(warmup, 3)):
+        tr.train_step_device(batches[i % 4])
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        tr.train_step_device(batches[i % 4])
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=tr.device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    tokens = tr.tokens_per_step() * steps
+    tr.close()
+    return {"value": tokens / (float(t[0]) / 1e3), "unit": "tokens/s", "ms_per_step": float(t[0]) / steps,
+            "method": "fp32 (library all-reduce through the same reducer and optimizer)"}
 
 
 def main() -> None:
@@ -86,10 +165,12 @@ def main() -> None:
     if args.bucket_cap_mb <= 0:
         args.bucket_cap_mb = 100 if args.model == "llama-1.2b" else 25
     os.environ.setdefault("DQ_ROTATION", args.rotation)
-    cfg = TrainConfig(model=args.model, method=args.method, micro_batch=mb, seq_len=seq, task=task,
+    cfg_kwargs = dict(model=args.model, method=args.method, micro_batch=mb, seq_len=seq, task=task,
                       bucket_cap_mb=args.bucket_cap_mb, topology=args.topology, comm_ctas=args.comm_ctas,
-                      comm_threads=args.comm_threads, tail_ctas=args.tail_ctas, reducer=args.reducer, comm_prefetch=bool(args.comm_prefetch),
+                      comm_threads=args.comm_threads, tail_ctas=args.tail_ctas, reducer=args.reducer,
+                      comm_prefetch=bool(args.comm_prefetch),
                       sparse_embedding=None if args.sparse_embedding < 0 else bool(args.sparse_embedding))
+    cfg = TrainConfig(**cfg_kwargs)
     tr = Trainer(cfg)
     dev = tr.device
     host_batches = [tr.synthetic_batch(pinned=True) for _ in range(4)]
@@ -134,6 +215,12 @@ def main() -> None:
     ms_e2e = max(e2.elapsed_time(e3), wall_e2e)
     clocks = sampler.stop() if rank == 0 else {}
     tr.check()
+    check = fp32_arm = None
+    if world > 1 and not args.no_extras:
+        check = collective_self_check(tr, world, rank)
+        resolved = tr.state["spec"] if tr.state is not None else None
+    else:
+        resolved = tr.state["spec"] if tr.state is not None else None
 
     t = torch.tensor([ms_dev, ms_e2e], dtype=torch.float64, device=dev)
     if world > 1:
@@ -159,8 +246,19 @@ def main() -> None:
                     "d2h_bytes_per_step": 4},
             "gpu_launches": launches, "final_loss": last,
         }
-        print(json.dumps(out), flush=True)
+        if resolved is not None:
+            out["config"]["resolved"] = {"hook": resolved.hook, "family": resolved.family, "bits": resolved.bits,
+                                         "topology": resolved.topology, "rotation": args.rotation,
+                                         "codec": ("rotation codec (randomised Hadamard, 1024-element blocks)"
+                                                   if resolved.family == "rht" else
+                                                   f"superchunk records, {resolved.lattice} lattice")}
+        out["collective_check"] = check
     tr.close()
+    if world > 1 and not args.no_extras:
+        fp32_arm = same_engine_fp32(args, cfg_kwargs, args.steps, args.warmup)
+    if rank == 0:
+        out["same_engine_nccl_fp32"] = fp32_arm
+        print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
 

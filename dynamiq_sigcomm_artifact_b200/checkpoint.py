@@ -20,7 +20,10 @@ FORMAT_VERSION = 1
 
 
 def save(path: str, trainer, extra: Optional[dict] = None) -> None:
-    """Write a checkpoint (rank 0 writes; every rank must call, a barrier follows)."""
+    """Write a checkpoint (rank 0 writes; every rank must call, a barrier follows).  The collective engine's
+    status is checked first: weights that a timed-out collective left half reduced are never written."""
+    if hasattr(trainer, "check"):
+        trainer.check()
     rank = dist.get_rank() if dist.is_initialized() else 0
     if rank == 0:
         os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)

@@ -43,7 +43,7 @@ class MethodSpec:
     fixed: bool = False  # superchunk: only the 4-bit group is communicated
     dynamic_bitrate: bool = False
     momentum: bool = False  # superchunk: widths from two energy thresholds tracked with momentum across steps
-    topology: str = "ring"  # ring | butterfly | direct
+    topology: str = "direct"  # ring | butterfly | direct (direct unless the method string or the config names one)
     correlated: bool = False  # stratified uniforms across ranks
     no_compress: bool = False  # run the selection logic but skip the collective (debug)
     compute_only: bool = False  # "coov": kernels run, nothing is transmitted (debug)
@@ -65,9 +65,20 @@ def parse_method(name: str, topology: Optional[str] = None) -> MethodSpec:
 
     The substring order is the reference's: thc, omnireduce, bf16, dynamiq(+bitrate), fp8,
     fp4/fp6/zero; then fp16/fp32, which the reference defines but cannot reach.
+
+    Topology: ``_butterfly`` / ``_ring`` / ``_direct`` in the name, or the `topology` argument, select one.
+    Without either the collective is ``direct``: on an NVSwitch box every shard goes straight to its owner,
+    which is as fast as or faster than the ring at every message size and rounds a value twice instead of
+    once per rank (the reference, built for rings of RDMA links, defaults to the ring).
+
+    Codec family of ``dynamiQ_*``: names with ``mee``, ``fixed``, ``bitrate``, ``momentum`` or
+    ``superchunk`` select the reference's superchunk records; plain ``dynamiQ_aee_{b}bit`` selects the
+    rotation codec (randomised Hadamard rotation of 1024-element blocks, one scale per block, b-bit codes) -
+    add ``_superchunk`` to run that name through the reference's AEE superchunk format instead, and
+    ``_mixed`` to let the rotation codec choose a width per block around the b-bit average.
     """
     low = name.lower()
-    topo = topology or ("butterfly" if "butterfly" in low else "direct" if "direct" in low else "ring")
+    topo = topology or ("butterfly" if "butterfly" in low else "ring" if "ring" in low else "direct")
     common = dict(name=name, topology=topo, compute_only="coov" in low)
     if "thc" in low:
         return MethodSpec(hook="thc", bits=5, quantization_levels=31, **common)

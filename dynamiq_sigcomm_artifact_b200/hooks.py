@@ -163,6 +163,10 @@ def _rht_allreduce(state: HookState, bucket) -> torch.futures.Future:
     st = state["stats"]
     st["collectives"] += 1
     st["buckets"][index] = {"numel": buf.numel(), "bits": bits}
+    if buf.is_cuda:
+        from .parallel.fused import wire_bytes_per_rank
+
+        st["wire_bytes"] += wire_bytes_per_rank(buf.numel(), world, bits, "rht")
     exact = None
     if cfg.measure_comm_error:
         exact = buf.detach().clone().float()

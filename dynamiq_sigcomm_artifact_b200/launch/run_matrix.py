@@ -62,7 +62,7 @@ def main(argv=None) -> int:
     ap.add_argument("--gpus", type=int, default=8)
     ap.add_argument("--aggregation-methods", "--aggregation_methods", default=DEFAULT_METHODS)
     ap.add_argument("--tasks", default="causal:llama-1.2b,causal:gpt2-small,mlm:bert-base")
-    ap.add_argument("--topology", default="ring", choices=["ring", "butterfly", "direct"])
+    ap.add_argument("--topology", default="direct", choices=["ring", "butterfly", "direct"])
     ap.add_argument("--max-train-steps", "--max_train_steps", type=int, default=151)
     ap.add_argument("--output-root", "--output_root", default="matrix_results")
     ap.add_argument("--base-port", type=int, default=0)

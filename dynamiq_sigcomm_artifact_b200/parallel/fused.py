@@ -77,6 +77,16 @@ class Layout:
         return _align(self.scales_off + scales, 256)
 
 
+def wire_bytes_per_rank(numel: int, world: int, bits: int, codec: str = "rht") -> int:
+    """Bytes one rank puts on NVLink in one collective of `numel` elements (each direction): W - 1
+    reduce-scatter messages and its own shard to W - 1 peers, whatever the topology."""
+    if world <= 1:
+        return 0
+    lay = Layout(numel, world, bits, codec)
+    per_block = block_bytes(bits, codec) + (4 if codec in ("rht", "rht_tc") else 0)
+    return 2 * (world - 1) * lay.blocks_per_shard * per_block
+
+
 def program_tensor(rank: int, world: int, topology: str, correlated: bool = False) -> torch.Tensor:
     prog = sch.build_program(rank, world, topology, correlated)
     return torch.tensor([s.as_ints() for s in prog], dtype=torch.int32)

@@ -123,6 +123,8 @@ class Trainer:
                                                        total_iters=cfg.total_steps)
         self.step_idx = 0
         self._dev_ids = None
+        self._status_host = None  # pinned copy of the collective engine's status words, refreshed every step
+        self._status_event = None
         self._gen = torch.Generator(device=device).manual_seed(cfg.seed + 17 * self.rank + 1) \
             if device.type == "cuda" else torch.Generator().manual_seed(cfg.seed + 17 * self.rank + 1)
         self.autocast_dtype = {"bf16": torch.bfloat16, "fp32": None}[cfg.dtype]
@@ -218,13 +220,40 @@ class Trainer:
             else:
                 self.opt.zero_grad(set_to_none=False)
         self.step_idx += 1
+        self._poll_status(enqueue=True)
         return loss.detach()
 
     def train_step(self, input_ids_host: torch.Tensor, labels_host: Optional[torch.Tensor] = None) -> float:
         """Public API: host batch in, loss out.  Copies the batch to the device every call."""
         ids = input_ids_host.to(self.device, non_blocking=True)
         lab = labels_host.to(self.device, non_blocking=True) if labels_host is not None else None
-        return float(self.train_step_device(ids, lab).item())
+        loss = float(self.train_step_device(ids, lab).item())
+        self._poll_status(enqueue=False)  # the loss read-back synchronised: this step's status copy has landed
+        return loss
+
+    def _poll_status(self, enqueue: bool) -> None:
+        """A device-side wait that gave up leaves an error code in the engine's status words and a partly
+        reduced bucket behind.  Every step queues a 16-byte copy of those words into pinned memory behind the
+        step's kernels; the copy of the previous step (or of this one, once the caller has synchronised) is
+        inspected without blocking, so a failed collective raises :class:`CollectiveTimeout` at most one step
+        late instead of at the end of the run.  A rank whose peer gave up runs out of its own wait budget in
+        the same collective, so every rank raises."""
+        eng = self.state["engine"] if self.state is not None else None
+        if eng is None or self.device.type != "cuda":
+            return
+        if self._status_event is not None and self._status_event.query():
+            from ..parallel.fused import CollectiveTimeout, decode_status
+
+            msg = decode_status(self._status_host.tolist())
+            self._status_event = None
+            if msg is not None:
+                raise CollectiveTimeout(f"rank {self.rank}: {msg} (noticed at step {self.step_idx})")
+        if enqueue:
+            if self._status_host is None:
+                self._status_host = torch.zeros(4, dtype=torch.int32).pin_memory()
+            self._status_host.copy_(eng._status_view, non_blocking=True)
+            self._status_event = torch.cuda.Event()
+            self._status_event.record()
 
     def tokens_per_step(self) -> int:
         return self.cfg.micro_batch * self.cfg.seq_len * self.world
@@ -237,6 +266,8 @@ class Trainer:
         return ids.pin_memory() if pinned and torch.cuda.is_available() else ids
 
     def check(self) -> None:
+        """Blocking check of the collective engine's status (call before saving a checkpoint or reporting
+        results)."""
         if self.state is not None and self.state["engine"] is not None:
             self.state["engine"].check()
 

@@ -141,7 +141,9 @@ def main(task: str, argv=None, default_model: str = "gpt2-small", default_seq: i
         if t_start is not None and step + 1 == min(args.measure_end_step, args.max_train_steps):
             if use_cuda:
                 torch.cuda.synchronize()
-            line = log.results(measured, time.perf_counter() - t_start)
+            elapsed = time.perf_counter() - t_start
+            tr.check()  # no results line from a run whose collectives gave up on a wait
+            line = log.results(measured, elapsed)
             if rank == 0:
                 print(line, flush=True)
     if args.eval_batches > 0:

@@ -51,7 +51,8 @@ def _run(method, numel=1 << 20, steps=4, world=2):
 
 def test_method_grammar():
     s = parse_method("dynamiQ_aee_5bit")
-    assert (s.hook, s.family, s.bits, s.topology) == ("dynamiq", "rht", 5, "ring")
+    assert (s.hook, s.family, s.bits, s.topology) == ("dynamiq", "rht", 5, "direct")
+    assert parse_method("dynamiQ_aee_5bit_ring").topology == "ring"
     s = parse_method("dynamiQ_mee_5bit_dynamic_bitrate_butterfly")
     assert (s.hook, s.family, s.lattice, s.topology, s.dynamic_bitrate) == ("dynamiq_bitrate", "superchunk", "mee",
                                                                             "butterfly", True)
