@@ -123,17 +123,42 @@ def _done(buf: torch.Tensor) -> torch.futures.Future:
     return fut
 
 
+def widest_wire(spec: MethodSpec) -> tuple:
+    """(bits, codec) of the largest message per element that `spec` can put on the wire."""
+    if spec.hook in ("dynamiq", "dynamiq_bitrate"):
+        if spec.family == "rht":
+            return (8 if (spec.dynamic_bitrate or "mixed" in spec.name.lower()) else spec.bits, "rht")
+        return (8, "scmix_" + spec.lattice)  # records of per-superchunk width: sized for the widest
+    if spec.hook == "mxfp8":
+        return (8, "mx")
+    if spec.hook == "fpx":
+        return (max(spec.bits, 4), "mx")
+    if spec.hook in ("bf16", "omnireduce"):
+        return (16, "cast")
+    return (32, "cast")
+
+
+def note_bucket(state: HookState, buf: torch.Tensor) -> None:
+    """Remember the largest bucket seen; the library-served warm-up steps see every bucket of the model, so
+    the engine created afterwards is sized once and never re-allocates inside a training step."""
+    if buf.numel() > state.get("max_bucket_numel", 0):
+        state["max_bucket_numel"] = buf.numel()
+
+
 def _engine(state: HookState):
-    """The NVLink engine, created on first use (a collective call: every rank gets here together)."""
+    """The NVLink engine, created on first use (a collective call: every rank gets here together).  Its
+    mailbox is sized for the largest bucket seen so far (or announced through ``state["max_bucket_numel"]``
+    by the bucket reducer) on the widest wire the method can select."""
     if state["engine"] is None:
         from .parallel.fused import FusedAllreduce
 
         cfg: DynamiqConfig = state["config"]
-        state["engine"] = FusedAllreduce(group=state["group"], max_numel=cfg.max_bucket_mb * (1 << 20) // 4,
+        numel = int(state.get("max_bucket_numel", 0)) or cfg.max_bucket_mb * (1 << 20) // 4
+        state["engine"] = FusedAllreduce(group=state["group"], max_numel=numel,
                                          ctas=cfg.comm_ctas, threads=cfg.comm_threads,
                                          timeout_ms=cfg.wait_timeout_ms, validate=cfg.validate_topology,
                                          rotation=cfg.rotation, max_ctas=max(cfg.comm_ctas, cfg.tail_ctas),
-                                         prefetch=cfg.comm_prefetch)
+                                         prefetch=cfg.comm_prefetch, widest=widest_wire(state["spec"]))
         state["comm_stream"] = torch.cuda.Stream(priority=-1)
     return state["engine"]
 
@@ -174,7 +199,6 @@ def _rht_allreduce(state: HookState, bucket) -> torch.futures.Future:
         exact.div_(world)
     if buf.is_cuda:
         eng = _engine(state)
-        eng.ensure_capacity(buf.numel())
         if cfg.overlap:
             stream = state["comm_stream"]
             stream.wait_stream(torch.cuda.current_stream())
@@ -211,6 +235,7 @@ def dynamiq_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.T
     """`dynamiQ_*` methods: rotation codec (`rht`) or the reference's superchunk codec."""
     state = _unwrap(state)
     state._auto_advance(bucket.index())
+    note_bucket(state, bucket.buffer())
     if state["batch_idx"] < state["config"].warmup_steps:
         return _library_mean(state, bucket.buffer())
     if state["spec"].family == "superchunk":
@@ -239,6 +264,7 @@ def bf16_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tens
     state = _unwrap(state)
     state._auto_advance(bucket.index())
     buf = bucket.buffer()
+    note_bucket(state, buf)
     world = _world(state)
     use_p2p = (buf.is_cuda and world > 1 and buf.dtype in (torch.float32, torch.bfloat16)
                and os.environ.get("DQ_BF16_LIBRARY", "0") not in ("1", "true")
@@ -247,7 +273,6 @@ def bf16_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tens
         return _library_mean(state, buf, torch.bfloat16)
     spec, cfg = state["spec"], state["config"]
     eng = _engine(state)
-    eng.ensure_capacity(buf.numel())
     stream = state["comm_stream"]
     stream.wait_stream(torch.cuda.current_stream())
     fut = torch.futures.Future(devices=[buf.device])

@@ -20,6 +20,8 @@ THC_MAX_PART = 1 << 23
 def _begin(state, bucket):
     state = state[0] if isinstance(state, (list, tuple)) else state
     state._auto_advance(bucket.index())
+    if bucket.buffer().numel() > state.get("max_bucket_numel", 0):
+        state["max_bucket_numel"] = bucket.buffer().numel()
     return state
 
 
@@ -54,7 +56,6 @@ def _block_float_hook(fmt_of):
             from ..hooks import _engine
 
             eng = _engine(state)
-            eng.ensure_capacity(buf.numel())
             width = {"fp8": 8, "fp6": 6, "fp4": 4}[fmt]
             eng.allreduce_(buf.reshape(-1), width, spec.topology, state["config"].seed, int(state["batch_idx"]),
                            bucket.index(), no_transmit=spec.compute_only, codec="mx")
@@ -104,7 +105,6 @@ def _p2p_mean(state, x: torch.Tensor, wire_bits: int, spec, step: int, bucket_id
     from ..hooks import _engine
 
     eng = _engine(state)
-    eng.ensure_capacity(x.numel())
     eng.allreduce_(x, wire_bits, spec.topology, state["config"].seed, step, bucket_id,
                    no_transmit=spec.compute_only, codec="cast")
     return x

@@ -155,10 +155,15 @@ class FusedAllreduce:
 
     def __init__(self, group=None, max_numel: int = 32 << 20, ctas: int = 64, threads: int = 256,
                  timeout_ms: int = 2000, validate: bool = True, rotation: str = "simt", max_ctas: Optional[int] = None,
-                 prefetch: bool = True):
+                 prefetch: bool = True, widest: Tuple[int, str] = (32, "cast")):
         """`ctas` is the default grid of a collective; a call may ask for any grid up to `max_ctas`
         (every rank must ask for the same one): a bucket that runs under backward wants a small grid,
-        the last bucket of a step has the GPU to itself."""
+        the last bucket of a step has the GPU to itself.
+
+        The mailbox is sized for `max_numel` elements on the `widest` wire (bits, codec) the caller will use
+        - (32, "cast"), the fp32 identity wire, unless told otherwise; a 5-bit rotation codec needs a sixth
+        of that.  A call that needs more grows the buffers (a collective re-allocation), so callers that know
+        their largest bucket and codec pass them here and never re-allocate inside a training step."""
         self.ops = _ops.require()
         self.group = group
         self.world = dist.get_world_size(group)
@@ -174,16 +179,19 @@ class FusedAllreduce:
         self._programs: Dict[tuple, torch.Tensor] = {}
         self.buf: Optional[SymmetricBuffer] = None
         self.max_numel = 0
-        self._alloc(max_numel)
+        self.slot_bytes = 0
+        self.allocations = 0  # how many times the symmetric buffers were (re-)allocated
+        self.nslots = sch.n_slots(self.world, "ring")  # same count for every topology
+        self._alloc(Layout(int(max_numel), self.world, widest[0], widest[1]).slot_stride, int(max_numel))
 
     # -- buffers ---------------------------------------------------------------------------
-    def _alloc(self, max_numel: int) -> None:
+    def _alloc(self, slot_bytes: int, max_numel: int) -> None:
         if self.buf is not None:
             self.buf.close()
+        self.allocations += 1
         self.max_numel = int(max_numel)
-        self.nslots = sch.n_slots(self.world, "ring")  # same count for every topology
-        worst = Layout(self.max_numel, self.world, 32, "cast")  # the largest message: the fp32 identity wire
-        self.set_bytes = _align(self.nslots * worst.slot_stride, 4096)
+        self.slot_bytes = _align(int(slot_bytes), 256)
+        self.set_bytes = _align(self.nslots * self.slot_bytes, 4096)
         self.flag_words_per_set = self.nslots * self.max_ctas
         self.off_flags = 2 * self.set_bytes
         self.off_status = self.off_flags + _align(2 * self.flag_words_per_set * 4, 4096)
@@ -192,10 +200,16 @@ class FusedAllreduce:
         self.buf = SymmetricBuffer(total, group=self.group, device=self.device, validate=self.validate)
         self._status_view = self.buf.local()[self.off_status: self.off_status + 16].view(torch.int32)
 
-    def ensure_capacity(self, numel: int) -> None:
-        """Grow the symmetric buffers (collective call: every rank must see the same sizes)."""
-        if numel > self.max_numel:
-            self._alloc(max(numel, int(self.max_numel * 1.5)))
+    def ensure_capacity(self, numel: int, bits: int = 32, codec: str = "cast") -> None:
+        """Grow the symmetric buffers if a message of `numel` elements on the (bits, codec) wire does not fit a
+        slot (collective call: every rank must see the same sizes)."""
+        need = Layout(int(numel), self.world, bits, codec).slot_stride
+        if need > self.slot_bytes:
+            self._alloc(max(need, int(self.slot_bytes * 1.5)), max(int(numel), self.max_numel))
+
+    def mailbox_bytes(self) -> int:
+        """Bytes of symmetric memory this rank holds (two slot sets, flags, status, tail scratch)."""
+        return self.buf.nbytes if self.buf is not None else 0
 
     def program(self, topology: str, correlated: bool = False) -> torch.Tensor:
         key = (topology, correlated)
@@ -216,7 +230,7 @@ class FusedAllreduce:
         if self.world == 1:
             return bucket
         codec = codec or ("rht_tc" if self.tensor_rotation else "rht")
-        self.ensure_capacity(bucket.numel())
+        self.ensure_capacity(bucket.numel(), bits, codec)
         lay = Layout(bucket.numel(), self.world, bits, codec)
         grid = int(ctas or self.ctas)
         if not 1 <= grid <= self.max_ctas:

@@ -234,6 +234,11 @@ class BucketReducer:
         self.buckets = [FlatBucket(bi, self.arena[s:e], self.bucket_params[bi], bi == len(spans) - 1)
                         for bi, (s, e) in enumerate(spans)]
         self.n_direct = len(direct_ids)
+        # announce the largest bucket to the hook state, so that the collective engine is sized once, before
+        # the first step, for exactly this arena
+        st = self.hook_state[0] if isinstance(self.hook_state, (list, tuple)) and self.hook_state else self.hook_state
+        if isinstance(st, dict):
+            st["max_bucket_numel"] = max([e - s0 for s0, e in spans] + [int(st.get("max_bucket_numel", 0))])
 
     def install_marks(self) -> None:
         """Put the readiness markers in front of the blocks (after any CUDA-graph capture of them)."""

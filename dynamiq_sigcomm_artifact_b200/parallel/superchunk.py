@@ -109,7 +109,6 @@ def superchunk_allreduce(state, bucket) -> torch.futures.Future:
         if spec.no_compress:
             rows = rows / world
         elif native:
-            eng.ensure_capacity(rows.numel())
             eng.allreduce_(rows, bits, spec.topology, cfg.seed, step, (index << 2) | gid,
                            no_transmit=spec.compute_only, codec=f"sc_{spec.lattice}")
         else:
@@ -173,7 +172,6 @@ def _native_mixed(state, bucket) -> torch.futures.Future:
             widths = bitalloc.threshold_widths(stats[:, 1], spec.thresholds)
         plan = dq.superchunk_plan(widths)
         counters.add("superchunk_plan")
-        eng.ensure_capacity(flat.numel())
         eng.allreduce_(flat, 8, spec.topology, cfg.seed, step, (index << 2) | 3, no_transmit=spec.compute_only,
                        codec=f"scmix_{spec.lattice}", plan=plan, ctas=_grid(state, bucket))
         dq.superchunk_add_mean(flat, stats[:, 0].contiguous(), buf.reshape(-1))
