@@ -262,50 +262,75 @@ def threshold_widths(energy: torch.Tensor, thresholds: Dict[int, float]) -> torc
     return widths
 
 
-class BucketBitPolicy:
-    """Per-bucket width for the rotation codec: b-1 / b / b+1 by energy per element.
+# ---- rotation codec: a code width per 1024-element block -------------------------------------------------
+#
+# Reverse water-filling: with a fixed budget of bits, a block whose rotated coefficients are 2^d times
+# larger than another's should get d more bits (each bit quarters its error).  So
+#     width_k = clamp(round(c + log2(absmax_k)), RHT_MIN_BITS, RHT_MAX_BITS)
+# with one offset c per bucket chosen so that the mean width meets the target - the rotation-codec
+# counterpart of the reference's 8 / 4 / 2 threshold split and dynamic-bitrate controller
+# (testbed_evaluation/new_comm_hooks/comm_hooks.py:48-139,713-721,842-856).  absmax_k is what every rank
+# already holds after a collective: the scale of block k in the all-gathered message times R(width), bit
+# identical on all ranks, so the widths of the NEXT step need no extra communication and no host read.
+# Everything is integer arithmetic on 1/8-bit quantised logarithms (``quantised_log2``), so the device
+# kernel (csrc/kernels/bitalloc_ops.cu: rht_widths_update) and this host twin agree exactly.
 
-    Energies are read one step late (an asynchronous scalar per bucket), so choosing a width
-    never synchronises the host with the device.  Buckets are ranked by the logarithm of their
-    energy per element; the top quarter gets b+1 bits, the bottom quarter b-1, which keeps the
-    element-weighted average within one quarter of a bit of b.
-    """
+RHT_MIN_BITS, RHT_MAX_BITS = 2, 8
+_LOG2_STEPS = None
 
-    def __init__(self, bits: int, spread: int = 1):
-        self.bits, self.spread = int(bits), int(spread)
-        self.energy: Dict[int, torch.Tensor] = {}
-        self.numel: Dict[int, int] = {}
-        self.assigned: Dict[int, int] = {}
 
-    def bits_for(self, index: int, buf: torch.Tensor) -> int:
-        self.numel[index] = buf.numel()
-        self.energy[index] = (buf.detach().float().pow(2).mean()).to("cpu", non_blocking=True)
-        return self.assigned.get(index, self.bits)
+def _log2_thresholds():
+    """fp32 values of 2^(j/8), j = 1..7, as the device kernel spells them."""
+    global _LOG2_STEPS
+    if _LOG2_STEPS is None:
+        import numpy as np
 
-    def end_of_step(self) -> None:
-        if len(self.energy) < 4:
-            return
-        items = sorted(self.energy, key=lambda i: float(self.energy[i]))
-        n = len(items)
-        k = n // 4
-        self.assigned = {i: self.bits for i in items}
-        lo, hi = items[:k], items[n - k:]
-        # keep the element-weighted budget: only widen as many elements as were narrowed
-        saved = sum(self.numel[i] for i in lo)
-        for i in lo:
-            self.assigned[i] = max(2, self.bits - self.spread)
-        for i in reversed(hi):
-            if self.numel[i] <= saved:
-                self.assigned[i] = min(8, self.bits + self.spread)
-                saved -= self.numel[i]
+        _LOG2_STEPS = np.array([1.0905077, 1.1892071, 1.2968396, 1.4142135, 1.5422108, 1.6817929, 1.8340080],
+                               dtype=np.float32)
+    return _LOG2_STEPS
 
-    def average_bits(self) -> float:
-        tot = sum(self.numel.values())
-        return sum(self.assigned.get(i, self.bits) * n for i, n in self.numel.items()) / tot if tot else self.bits
 
-    def state_dict(self) -> dict:
-        return {"bits": self.bits, "assigned": dict(self.assigned)}
+def quantised_log2(x):
+    """floor(8 log2 x) for positive finite fp32 x, from the exponent field and seven comparisons of the
+    mantissa; x <= 0, NaN and infinity give the smallest value (-1016 = 8 * -127)."""
+    import numpy as np
 
-    def load_state_dict(self, d: dict) -> None:
-        self.bits = int(d["bits"])
-        self.assigned = {int(k): int(v) for k, v in d["assigned"].items()}
+    x = np.asarray(x, dtype=np.float32)
+    bits = x.view(np.uint32)
+    expo = ((bits >> np.uint32(23)) & np.uint32(0xFF)).astype(np.int32) - 127
+    mant = ((bits & np.uint32(0x007FFFFF)) | np.uint32(0x3F800000)).view(np.float32)  # in [1, 2)
+    frac = (mant[..., None] >= _log2_thresholds()).sum(axis=-1).astype(np.int32)
+    ok = (x > 0) & np.isfinite(x)
+    return np.where(ok, 8 * expo + frac, -1016).astype(np.int32)
+
+
+def rht_block_widths(absmax, target_bits: float):
+    """(widths uint8 [nblocks], offset c in 1/8 bit) for per-block magnitudes `absmax`: the largest offset
+    whose total width does not exceed round(target_bits * nblocks)."""
+    import numpy as np
+
+    lq = quantised_log2(absmax)
+    budget = int(round(float(target_bits) * lq.size))
+
+    def widths_at(c8: int):
+        return np.clip((lq + c8 + 4) >> 3, RHT_MIN_BITS, RHT_MAX_BITS)
+
+    lo, hi = -2048, 2048  # invariant: total(lo) <= budget (or lo is the floor), total(hi) > budget (or hi is the cap)
+    if int(widths_at(hi).sum()) <= budget:
+        return widths_at(hi).astype(np.uint8), hi
+    while hi - lo > 1:
+        mid = (lo + hi) // 2
+        if int(widths_at(mid).sum()) <= budget:
+            lo = mid
+        else:
+            hi = mid
+    return widths_at(lo).astype(np.uint8), lo
+
+
+def rht_plan(widths):
+    """int32 [2 nblocks + 1]: exclusive prefix sum of the widths (message offset of each block's codes in
+    units of 128 bytes), then the widths - the layout the kernel reads."""
+    import numpy as np
+
+    w = np.asarray(widths, dtype=np.int64)
+    return np.concatenate([[0], np.cumsum(w), w]).astype(np.int32)

@@ -222,6 +222,55 @@ def decode_blocks(msg: np.ndarray, nblocks: int, bits: int, layout: str = "simt"
     return dequantize(unpack(words, bits), scale, bits, layout)
 
 
+# ---- a width per block ----------------------------------------------------------------------------------
+# Message of a shard whose blocks have widths w_0 .. w_{n-1}: the blocks' code bytes back to back (block k
+# takes 128 w_k bytes), then the fp32 scales at a fixed offset sized for 8-bit blocks, so that a receiver
+# finds a scale without the prefix sum.  The bytes below are the codes then the scales, without the gap.
+
+def encode_blocks_mixed(y: np.ndarray, widths: np.ndarray, block_idx, tag: int, step: int, seed: int, rank: int = 0,
+                        world: int = 1, layout: str = "simt") -> np.ndarray:
+    widths = np.asarray(widths)
+    block_idx = np.asarray(block_idx)
+    parts, scales = [None] * len(widths), np.zeros(len(widths), dtype=F32)
+    for b in np.unique(widths):
+        sel = np.nonzero(widths == b)[0]
+        codes, sc = quantize(y[sel], int(b), block_idx[sel], tag, step, seed, rank, world, layout)
+        words = pack(codes, int(b))
+        for j, k in enumerate(sel):
+            parts[k] = words[j].reshape(-1).view(np.uint8)
+        scales[sel] = sc
+    return np.concatenate(parts + [scales.view(np.uint8)]) if len(widths) else np.zeros(0, np.uint8)
+
+
+def _split_mixed(msg: np.ndarray, widths: np.ndarray):
+    widths = np.asarray(widths, dtype=np.int64)
+    offs = np.concatenate([[0], np.cumsum(128 * widths)])
+    scale = msg[offs[-1]: offs[-1] + 4 * len(widths)].view(F32)
+    return offs, scale
+
+
+def decode_blocks_mixed(msg: np.ndarray, widths: np.ndarray, layout: str = "simt",
+                        acc: np.ndarray = None) -> np.ndarray:
+    """Decoded blocks [n, 1024]; with `acc` the hop's fused multiply-add into it."""
+    widths = np.asarray(widths)
+    offs, scale = _split_mixed(msg, widths)
+    out = np.zeros((len(widths), BLOCK), dtype=F32) if acc is None else acc.astype(F32, copy=True)
+    for b in np.unique(widths):
+        sel = np.nonzero(widths == b)[0]
+        words = np.stack([msg[offs[k]: offs[k] + 128 * int(b)].view(np.uint32).reshape(int(b), 32) for k in sel])
+        codes = unpack(words, int(b))
+        if acc is None:
+            out[sel] = dequantize(codes, scale[sel], int(b), layout)
+        else:
+            out[sel] = dequantize_add(codes, scale[sel], int(b), acc[sel], layout)
+    return out
+
+
+def mixed_payload_bytes(widths) -> int:
+    widths = np.asarray(widths, dtype=np.int64)
+    return int(128 * widths.sum() + 4 * len(widths))
+
+
 def nmse(estimate: np.ndarray, exact: np.ndarray) -> float:
     """||estimate - exact||^2 / ||exact||^2 in float64 (the reference's vNMSE,
     simulations_llm/new_comm_hooks/comm_hooks.py:22-50)."""

@@ -43,6 +43,7 @@ class MethodSpec:
     fixed: bool = False  # superchunk: only the 4-bit group is communicated
     dynamic_bitrate: bool = False
     momentum: bool = False  # superchunk: widths from two energy thresholds tracked with momentum across steps
+    mixed: bool = False  # rotation codec: a code width per 1024-element block around the `bits` average
     topology: str = "direct"  # ring | butterfly | direct (direct unless the method string or the config names one)
     correlated: bool = False  # stratified uniforms across ranks
     no_compress: bool = False  # run the selection logic but skip the collective (debug)
@@ -90,8 +91,9 @@ def parse_method(name: str, topology: Optional[str] = None) -> MethodSpec:
         bits = _bits_in(low, 5)
         family = "superchunk" if ("superchunk" in low or "mee" in low or "bitrate" in low or "fixed" in low
                                   or "momentum" in low) else "rht"
-        if "rht" in low:
+        if "rht" in low or "mixed" in low:
             family = "rht"
+        mixed = family == "rht" and ("mixed" in low or "bitrate" in low)
         lattice = "aee" if "aee" in low else "mee"
         fixed = "fixed" in low
         key = f"{bits}bit_fixed" if (fixed and bits == 4) else f"{bits}bit"
@@ -99,7 +101,7 @@ def parse_method(name: str, topology: Optional[str] = None) -> MethodSpec:
         return MethodSpec(hook="dynamiq_bitrate" if "bitrate" in low else "dynamiq", family=family,
                           lattice=lattice, bits=bits, fixed=fixed, dynamic_bitrate="bitrate" in low,
                           correlated="correlated" in low, no_compress="no_compress" in low,
-                          momentum="momentum" in low,
+                          momentum="momentum" in low, mixed=mixed,
                           thresholds=thresholds, **common)
     if "fp8" in low:
         return MethodSpec(hook="mxfp8", bits=8, **common)

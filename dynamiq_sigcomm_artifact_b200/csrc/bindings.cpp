@@ -49,6 +49,8 @@ void fwht_levels_(at::Tensor x, int64_t first, int64_t nlevels, double scale);
 void superchunk_widths(at::Tensor stats, at::Tensor state, at::Tensor s_out, at::Tensor widths);
 at::Tensor superchunk_plan(at::Tensor widths);
 void superchunk_bitrate_update(at::Tensor sorted_s, at::Tensor state, double target);
+void rht_widths_update(at::Tensor mailbox, at::Tensor plan, int64_t nblocks, int64_t blocks_per_shard,
+                       int64_t slot_stride, int64_t scales_off, int64_t first_ag_slot, int64_t budget);
 at::Tensor rope(at::Tensor x, at::Tensor cos, at::Tensor sin, bool backward);
 void adamw_step(at::Tensor table, at::Tensor numel, at::Tensor chunk_start, int64_t total_chunks, bool param_bf16,
                 bool grad_bf16, double lr, double beta1, double beta2, double eps, double weight_decay, int64_t step,
@@ -73,6 +75,8 @@ TORCH_LIBRARY(dq, m) {
   m.def("superchunk_widths(Tensor stats, Tensor state, Tensor(a!) s_out, Tensor(b!) widths) -> ()", &dq::superchunk_widths);
   m.def("superchunk_plan(Tensor widths) -> Tensor", &dq::superchunk_plan);
   m.def("superchunk_bitrate_update(Tensor sorted_s, Tensor(a!) state, float target) -> ()", &dq::superchunk_bitrate_update);
+  m.def("rht_widths_update(Tensor mailbox, Tensor(a!) plan, int nblocks, int blocks_per_shard, int slot_stride, "
+        "int scales_off, int first_ag_slot, int budget) -> ()", &dq::rht_widths_update);
   m.def("rope(Tensor x, Tensor cos, Tensor sin, bool backward) -> Tensor", &dq::rope);
   m.def("adamw_step(Tensor table, Tensor numel, Tensor chunk_start, int total_chunks, bool param_bf16, bool grad_bf16, "
         "float lr, float beta1, float beta2, float eps, float weight_decay, int step, float grad_scale) -> ()", &dq::adamw_step);

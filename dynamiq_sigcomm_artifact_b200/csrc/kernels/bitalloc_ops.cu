@@ -169,4 +169,120 @@ void superchunk_bitrate_update(at::Tensor sorted_s, at::Tensor state, double tar
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
+// ---- rotation codec: a code width per 1024-element block ---------------------------------------------------
+//
+// width_k = clamp(round(c + log2(absmax_k)), 2, 8), one offset c per bucket, the largest whose total width
+// stays within the budget (reverse water-filling; host twin and rationale: bitalloc.py, rht_block_widths).
+// absmax_k = scale_k * R(previous width_k), where scale_k is what the last collective left in this rank's
+// own all-gather slots - identical on every rank, so the widths need no communication and no host read.
+// All arithmetic is on integers: logarithms quantised to 1/8 bit from the exponent field and seven
+// comparisons, a 2048-bin histogram, a bisection on the histogram, a block-wide prefix sum.
+
+namespace {
+
+constexpr int kLogBins = 2048, kLogBias = 1016;  // floor(8 log2 x) + 1016 for fp32 x > 0 lies in [0, 2040]
+
+__device__ __forceinline__ int quantised_log2(float x) {
+  if (!(x > 0.0f) || x > 3.402823466e38f) return -kLogBias;
+  const uint32_t bits = __float_as_uint(x);
+  const int expo = static_cast<int>((bits >> 23) & 0xFFu) - 127;
+  const float mant = __uint_as_float((bits & 0x007FFFFFu) | 0x3F800000u);
+  const int frac = (mant >= 1.0905077f) + (mant >= 1.1892071f) + (mant >= 1.2968396f) + (mant >= 1.4142135f) +
+                   (mant >= 1.5422108f) + (mant >= 1.6817929f) + (mant >= 1.8340080f);
+  return 8 * expo + frac;
+}
+
+__device__ __forceinline__ int rht_width_at(int lq, int c8) { return max(2, min(8, (lq + c8 + 4) >> 3)); }
+
+// Sum over the thread block of one long long per thread (blockDim.x a multiple of 32, at most 1024).
+__device__ long long block_sum(long long v, long long* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  const int warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) scratch[warp] = v;
+  __syncthreads();
+  long long t = 0;
+  for (int i = 0; i < nwarps; ++i) t += scratch[i];
+  return t;
+}
+
+__global__ void __launch_bounds__(1024, 1) rht_widths_update_kernel(const uint8_t* __restrict__ mail, int* __restrict__ plan,
+                                                                   int nblocks, int blocks_per_shard,
+                                                                   long long slot_stride, long long scales_off,
+                                                                   int first_ag_slot, long long budget) {
+  __shared__ int hist[kLogBins];
+  __shared__ long long scratch[32];
+  __shared__ int prefix[1024];
+  const int tid = threadIdx.x, nt = blockDim.x;
+  int* widths = plan + nblocks + 1;
+  auto log_of = [&](int k) {
+    const int shard = k / blocks_per_shard, bs = k - shard * blocks_per_shard;
+    const float scale = *reinterpret_cast<const float*>(mail + (first_ag_slot + shard) * slot_stride + scales_off + 4ll * bs);
+    const int wprev = max(2, min(8, widths[k]));
+    return quantised_log2(__fmul_rn(scale, static_cast<float>((1 << (wprev - 1)) - 1)));
+  };
+  for (int i = tid; i < kLogBins; i += nt) hist[i] = 0;
+  __syncthreads();
+  for (int k = tid; k < nblocks; k += nt) atomicAdd(&hist[log_of(k) + kLogBias], 1);
+  __syncthreads();
+  auto total_at = [&](int c8) {
+    long long v = 0;
+    for (int b = tid; b < kLogBins; b += nt) v += static_cast<long long>(hist[b]) * rht_width_at(b - kLogBias, c8);
+    return block_sum(v, scratch);
+  };
+  int lo = -2048, hi = 2048;
+  if (total_at(hi) <= budget) {
+    lo = hi;
+  } else {
+    while (hi - lo > 1) {  // total_at(lo) <= budget (or lo is the floor), total_at(hi) > budget
+      const int m = (lo + hi) >> 1;  // floor, also for negative sums, like the host twin's //
+      if (total_at(m) <= budget) lo = m; else hi = m;
+    }
+  }
+  // widths and their exclusive prefix sum: thread t owns a contiguous run of blocks
+  const int chunk = (nblocks + nt - 1) / nt;
+  const int k0 = min(tid * chunk, nblocks), k1 = min(k0 + chunk, nblocks);
+  int mine = 0;
+  for (int k = k0; k < k1; ++k) mine += rht_width_at(log_of(k), lo);
+  prefix[tid] = mine;
+  __syncthreads();
+  for (int o = 1; o < nt; o <<= 1) {  // Hillis-Steele inclusive scan
+    const int add = tid >= o ? prefix[tid - o] : 0;
+    __syncthreads();
+    prefix[tid] += add;
+    __syncthreads();
+  }
+  int run = prefix[tid] - mine;
+  for (int k = k0; k < k1; ++k) {
+    const int wnew = rht_width_at(log_of(k), lo);  // reads the previous width of block k, then replaces it
+    plan[k] = run;
+    run += wnew;
+    widths[k] = wnew;
+  }
+  if (tid == nt - 1) plan[nblocks] = prefix[nt - 1];
+}
+
+}  // namespace
+
+// In-place update of a rotation-codec plan (int32 [2 nblocks + 1]: offsets in 128-byte units, then widths) from
+// the scales that the last collective left in `mailbox` (this rank's slot set, uint8): the widths of the next
+// collective of this bucket.  `budget` = total width allowed, round(target bits per value * nblocks).
+void rht_widths_update(at::Tensor mailbox, at::Tensor plan, int64_t nblocks, int64_t blocks_per_shard,
+                       int64_t slot_stride, int64_t scales_off, int64_t first_ag_slot, int64_t budget) {
+  TORCH_CHECK(mailbox.is_cuda() && mailbox.scalar_type() == at::kByte && mailbox.is_contiguous(), "mailbox: uint8 CUDA");
+  TORCH_CHECK(plan.is_cuda() && plan.scalar_type() == at::kInt && plan.is_contiguous() && plan.numel() >= 2 * nblocks + 1,
+              "plan: int32 CUDA tensor of 2 nblocks + 1 entries");
+  TORCH_CHECK(nblocks > 0 && blocks_per_shard > 0, "empty bucket");
+  const int64_t nshards = (nblocks + blocks_per_shard - 1) / blocks_per_shard;
+  TORCH_CHECK((first_ag_slot + nshards - 1) * slot_stride + scales_off + 4 * blocks_per_shard <= mailbox.numel(),
+              "the all-gather slots lie outside the mailbox");
+  TORCH_CHECK(scales_off % 4 == 0 && slot_stride % 4 == 0, "misaligned scales");
+  c10::cuda::CUDAGuard guard(plan.device());
+  rht_widths_update_kernel<<<1, 1024, 0, at::cuda::getCurrentCUDAStream()>>>(
+      mailbox.data_ptr<uint8_t>(), plan.data_ptr<int>(), static_cast<int>(nblocks), static_cast<int>(blocks_per_shard),
+      slot_stride, scales_off, static_cast<int>(first_ag_slot), budget);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
 }  // namespace dq

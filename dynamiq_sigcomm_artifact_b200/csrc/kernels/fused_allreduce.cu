@@ -92,6 +92,7 @@ static void launch_bits(int bits, const ARParams* hp, const ARParams* dp, int nr
     case kCodecCast: launch_cast<T>(bits, hp, dp, nranks, ctas, threads, stream); break;
     case kCodecScMixAee: launch_one<8, T, kCodecScMixAee>(hp, dp, nranks, ctas, threads, stream); break;
     case kCodecScMixMee: launch_one<8, T, kCodecScMixMee>(hp, dp, nranks, ctas, threads, stream); break;
+    case kCodecRhtMix: launch_one<8, T, kCodecRhtMix>(hp, dp, nranks, ctas, threads, stream); break;
     default: TORCH_CHECK(false, "unknown codec ", codec);
   }
 }
@@ -101,6 +102,7 @@ static unsigned block_bytes_of(int codec, int bits) {
   if (codec == kCodecScMixAee || codec == kCodecScMixMee) return 4u * 274u;  // the widest block: four 8-bit records
   if (codec == kCodecMx) return 128u * bits + 32u;
   if (codec == kCodecCast) return 128u * bits;
+  if (codec == kCodecRhtMix) return 128u * 8u;  // slots are sized for the widest block
   return 128u * bits;
 }
 
@@ -130,6 +132,12 @@ static void fill_sc(ARParams& p, int64_t codec, int64_t bits, double lattice_max
                     plan->numel() >= 2 * static_cast<int64_t>(p.nblocks) + 1,
                 "the mixed-width codec needs an int32 CUDA plan of nblocks + 1 offsets and nblocks packed widths");
     p.sc_lut = lut->data_ptr<float>();
+    p.sc_plan = reinterpret_cast<const uint32_t*>(plan->data_ptr<int>());
+  }
+  if (codec == kCodecRhtMix) {
+    TORCH_CHECK(plan.has_value() && plan->is_cuda() && plan->scalar_type() == at::kInt && plan->is_contiguous() &&
+                    plan->numel() >= 2 * static_cast<int64_t>(p.nblocks) + 1,
+                "the mixed-width rotation codec needs an int32 CUDA plan of nblocks + 1 offsets and nblocks widths");
     p.sc_plan = reinterpret_cast<const uint32_t*>(plan->data_ptr<int>());
   }
 }
@@ -176,7 +184,7 @@ static void check_layout(const ARParams& p, int bits, int64_t mailbox_bytes, int
                          int ctas) {
   (void)bits;
   const unsigned long long need = static_cast<unsigned long long>(p.blocks_per_shard) * p.block_bytes;
-  const bool has_scales = p.codec == kCodecRht || p.codec == kCodecRhtTc;  // one fp32 scale per block after the codes
+  const bool has_scales = p.codec == kCodecRht || p.codec == kCodecRhtTc || p.codec == kCodecRhtMix;  // fp32 scales after the codes
   TORCH_CHECK(p.scales_off >= need && (p.scales_off % 16) == 0, "scales overlap the codes of a slot");
   TORCH_CHECK(p.slot_stride >= p.scales_off + (has_scales ? 4ull * p.blocks_per_shard : 0ull) &&
                   (p.slot_stride % 16) == 0,

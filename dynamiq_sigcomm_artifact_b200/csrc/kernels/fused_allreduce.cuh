@@ -14,7 +14,8 @@ enum : int { kLocalRaw = 0, kLocalWs = 1 };
 enum : int { kOutSend = 0, kOutStore = 1, kOutFinal = 2, kOutDecode = 3 };
 enum : int {
   kCodecRht = 0, kCodecRhtTc = 1, kCodecScAee = 2, kCodecScMee = 3, kCodecMx = 4, kCodecCast = 5,
-  kCodecScMixAee = 6, kCodecScMixMee = 7  // superchunk records whose width (2 / 4 / 8) varies per superchunk
+  kCodecScMixAee = 6, kCodecScMixMee = 7,  // superchunk records whose width (2 / 4 / 8) varies per superchunk
+  kCodecRhtMix = 8                         // rotation codec whose code width (2..8) varies per 1024-element block
 };
 
 // error codes left in status[0]; status[1] = (step << 16) | cta, status[2] = slot
@@ -48,7 +49,8 @@ struct ARParams {
   const float* sc_lut;             // superchunk codec decode levels [2^bits] (device memory); mixed widths: the
                                    // constant table of sc_codec.cuh (kScMixTableFloats)
   const uint32_t* sc_plan;         // mixed widths: [nblocks + 1] message offsets of the blocks in 8-byte units (a prefix
-                                   // sum), then [nblocks] packed widths (byte j = width of superchunk j of the block)
+                                   // sum), then [nblocks] packed widths (byte j = width of superchunk j of the block);
+                                   // kCodecRhtMix: offsets in 128-byte units, then one width (2..8) per block
   int steps[kMaxSteps][kStepInts];
 };
 

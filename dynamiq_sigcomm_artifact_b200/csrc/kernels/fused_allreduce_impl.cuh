@@ -5,6 +5,8 @@
 #include <c10/cuda/CUDAException.h>
 #include <cuda_runtime.h>
 
+#include <type_traits>
+
 #include "../common/rht_codec.cuh"
 #include "../common/sc_codec.cuh"
 #include "../common/mx_codec.cuh"
@@ -212,17 +214,48 @@ __device__ __forceinline__ void fused_simt_body(const ARParams& p) {
         }
       } else {
       // ---- rotation codec ----
-      constexpr int RB = (BITS >= 2 && BITS <= 8) ? BITS : 8;  // code width of the rotation codec
+      constexpr bool MIXR = CODEC == kCodecRhtMix;  // a code width per block, from the plan
+      constexpr int RB = MIXR ? 8 : ((BITS >= 2 && BITS <= 8) ? BITS : 8);  // (largest) code width
       uint32_t w[RB];
       float scale = 0.f;
-
-      if (active && nrecv > 0) {  // first incoming message: issue its loads before the local work
-        const uint8_t* slot = my_mail + static_cast<unsigned long long>(recv_slot) * p.slot_stride;
-        const uint32_t* codes = reinterpret_cast<const uint32_t*>(slot) + static_cast<size_t>(bs) * (RB * 32);
-#pragma unroll
-        for (int j = 0; j < RB; ++j) w[j] = ld_cg_u32(codes + j * 32 + lane);
-        scale = __ldcg(reinterpret_cast<const float*>(slot + p.scales_off) + bs);
+      int wb = RB;                                             // this block's width
+      size_t code_word = static_cast<size_t>(bs) * (RB * 32);  // first code word of the block inside a message
+      if constexpr (MIXR) {
+        wb = static_cast<int>(__ldg(p.sc_plan + p.nblocks + 1 + blk));
+        code_word = static_cast<size_t>(__ldg(p.sc_plan + blk) - __ldg(p.sc_plan + shard_lo)) * 32;
       }
+      auto with_width = [&](auto&& fn) {  // fn(width as a compile-time constant)
+        if constexpr (!MIXR) {
+          fn(std::integral_constant<int, RB>{});
+        } else {
+          switch (wb) {
+            case 2: fn(std::integral_constant<int, 2>{}); break;
+            case 3: fn(std::integral_constant<int, 3>{}); break;
+            case 4: fn(std::integral_constant<int, 4>{}); break;
+            case 5: fn(std::integral_constant<int, 5>{}); break;
+            case 6: fn(std::integral_constant<int, 6>{}); break;
+            case 7: fn(std::integral_constant<int, 7>{}); break;
+            default: fn(std::integral_constant<int, 8>{}); break;
+          }
+        }
+      };
+      auto load_codes = [&](const uint8_t* slot) {
+        const uint32_t* codes = reinterpret_cast<const uint32_t*>(slot) + code_word;
+#pragma unroll
+        for (int j = 0; j < RB; ++j)
+          if (!MIXR || j < wb) w[j] = ld_cg_u32(codes + j * 32 + lane);
+        scale = __ldcg(reinterpret_cast<const float*>(slot + p.scales_off) + bs);
+      };
+      auto store_codes = [&](uint8_t* slot) {
+        uint32_t* codes = reinterpret_cast<uint32_t*>(slot) + code_word;
+#pragma unroll
+        for (int j = 0; j < RB; ++j)
+          if (!MIXR || j < wb) codes[j * 32 + lane] = w[j];
+        if (lane == 0) reinterpret_cast<float*>(slot + p.scales_off)[bs] = scale;
+      };
+
+      if (active && nrecv > 0)  // first incoming message: issue its loads before the local work
+        load_codes(my_mail + static_cast<unsigned long long>(recv_slot) * p.slot_stride);
 
       if (active && out != kOutDecode) {
         if (local == kLocalRaw) {
@@ -247,14 +280,11 @@ __device__ __forceinline__ void fused_simt_body(const ARParams& p) {
       if (rotate_in) rotate_forward(v, sgn_fwd, tile, lane);
 
       if (active && out != kOutDecode) {
-        if (nrecv > 0) dequantize_add_block<RB>(w, scale, v);
-        for (int r = 1; r < nrecv; ++r) {
-          const uint8_t* slot = my_mail + static_cast<unsigned long long>(recv_slot + r) * p.slot_stride;
-          const uint32_t* codes = reinterpret_cast<const uint32_t*>(slot) + static_cast<size_t>(bs) * (RB * 32);
-#pragma unroll
-          for (int j = 0; j < RB; ++j) w[j] = ld_cg_u32(codes + j * 32 + lane);
-          scale = __ldcg(reinterpret_cast<const float*>(slot + p.scales_off) + bs);
-          dequantize_add_block<RB>(w, scale, v);
+        for (int r = 0; r < nrecv; ++r) {
+          if (r > 0) load_codes(my_mail + static_cast<unsigned long long>(recv_slot + r) * p.slot_stride);
+          with_width([&](auto B) {
+            dequantize_add_block<B.value>(reinterpret_cast<const uint32_t(&)[B.value]>(w), scale, v);
+          });
         }
       }
 
@@ -265,33 +295,34 @@ __device__ __forceinline__ void fused_simt_body(const ARParams& p) {
         }
       } else if (out == kOutSend) {
         if (active) {
-          scale = quantize_block<RB>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi, lane,
-                                     p.rank, strat_world);
-          if (!p.no_transmit) {
-            uint8_t* slot = p.mail[dst] + static_cast<unsigned long long>(send_slot) * p.slot_stride;
-            uint32_t* codes = reinterpret_cast<uint32_t*>(slot) + static_cast<size_t>(bs) * (RB * 32);
-#pragma unroll
-            for (int j = 0; j < RB; ++j) codes[j * 32 + lane] = w[j];
-            if (lane == 0) reinterpret_cast<float*>(slot + p.scales_off)[bs] = scale;
-          }
+          with_width([&](auto B) {
+            scale = quantize_block<B.value>(v, reinterpret_cast<uint32_t(&)[B.value]>(w), static_cast<uint32_t>(blk), tag,
+                                            p.step, p.seed_lo, p.seed_hi, lane, p.rank, strat_world);
+          });
+          if (!p.no_transmit) store_codes(p.mail[dst] + static_cast<unsigned long long>(send_slot) * p.slot_stride);
         }
       } else {
         if (active) {
           if (out == kOutFinal) {
-            scale = quantize_block<RB>(v, w, static_cast<uint32_t>(blk), tag, p.step, p.seed_lo, p.seed_hi, lane);
+            with_width([&](auto B) {
+              scale = quantize_block<B.value>(v, reinterpret_cast<uint32_t(&)[B.value]>(w), static_cast<uint32_t>(blk),
+                                              tag, p.step, p.seed_lo, p.seed_hi, lane);
+            });
             if (!p.no_transmit) {
               for (int peer = 0; peer < p.world; ++peer) {
                 if (peer == p.rank) continue;
-                uint8_t* slot = p.mail[peer] + static_cast<unsigned long long>(send_slot) * p.slot_stride;
-                uint32_t* codes = reinterpret_cast<uint32_t*>(slot) + static_cast<size_t>(bs) * (RB * 32);
-#pragma unroll
-                for (int j = 0; j < RB; ++j) codes[j * 32 + lane] = w[j];
-                if (lane == 0) reinterpret_cast<float*>(slot + p.scales_off)[bs] = scale;
+                store_codes(p.mail[peer] + static_cast<unsigned long long>(send_slot) * p.slot_stride);
               }
             }
+            // the width policy of the next step reads the scale of every block from this rank's own slots
+            if (MIXR && lane == 0)
+              reinterpret_cast<float*>(my_mail + static_cast<unsigned long long>(send_slot) * p.slot_stride +
+                                       p.scales_off)[bs] = scale;
           }
           // kOutDecode: w / scale were loaded from the all-gather slot above
-          dequantize_block<RB>(w, scale, v);
+          with_width([&](auto B) {
+            dequantize_block<B.value>(reinterpret_cast<const uint32_t(&)[B.value]>(w), scale, v);
+          });
         }
         if (rotate_out) rotate_inverse(v, sgn_inv, tile, lane);
         store_block<T>(bucket + e0, valid, vec_ok, lane, v);
@@ -400,6 +431,11 @@ void launch_one(const ARParams* host_params, const ARParams* dev_params, int nra
   template void launch_one<BITS, __nv_bfloat16, kCodecScAee>(const ARParams*, const ARParams*, int, int, int, cudaStream_t); \
   template void launch_one<BITS, float, kCodecScMee>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);         \
   template void launch_one<BITS, __nv_bfloat16, kCodecScMee>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);
+
+// rotation codec with a width per block: the BITS parameter is a placeholder (8, the widest block)
+#define DQ_INSTANTIATE_FUSED_ALLREDUCE_RHTMIX                                                                           \
+  template void launch_one<8, float, kCodecRhtMix>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);         \
+  template void launch_one<8, __nv_bfloat16, kCodecRhtMix>(const ARParams*, const ARParams*, int, int, int, cudaStream_t);
 
 // mixed-width superchunk codec: the BITS parameter is a placeholder (8, the widest record)
 #define DQ_INSTANTIATE_FUSED_ALLREDUCE_SCMIX                                                                              \

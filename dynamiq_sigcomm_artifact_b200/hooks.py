@@ -42,7 +42,6 @@ class HookState(dict):
         self["comm_stream"] = None
         self["auto_step"] = True
         self["stats"] = {"buckets": {}, "collectives": 0, "wire_bytes": 0, "err_sq": 0.0, "ref_sq": 0.0}
-        self["bit_policy"] = None
         self["_seen_first"] = False
 
     # -- step accounting -------------------------------------------------------------------
@@ -61,8 +60,9 @@ class HookState(dict):
     def state_dict(self) -> dict:
         d = {"batch_idx": self["batch_idx"], "method": self["config"].method, "seed": self["config"].seed,
              "stats": {k: v for k, v in self["stats"].items() if k != "buckets"}}
-        if self["bit_policy"] is not None:
-            d["bit_policy"] = self["bit_policy"].state_dict()
+        plans = self["params"].get("rht_plans")
+        if plans:  # per-block widths of the rotation codec (mixed methods): needed to resume bit for bit
+            d["rht_plans"] = {int(k): (v.cpu() if torch.is_tensor(v) else torch.as_tensor(v)) for k, v in plans.items()}
         ctl = self["params"].get("bitrate")
         if ctl is not None and hasattr(ctl, "state_dict"):
             sd = ctl.state_dict()
@@ -76,8 +76,8 @@ class HookState(dict):
     def load_state_dict(self, d: dict) -> None:
         self["batch_idx"] = int(d["batch_idx"])
         self["auto_step"] = False
-        if "bit_policy" in d and self["bit_policy"] is not None:
-            self["bit_policy"].load_state_dict(d["bit_policy"])
+        if "rht_plans" in d:
+            self["params"]["rht_plans_restored"] = {int(k): v for k, v in d["rht_plans"].items()}
         for k in ("bitrate_u",):
             if k in d:
                 self["params"][k] = d[k]
@@ -127,7 +127,7 @@ def widest_wire(spec: MethodSpec) -> tuple:
     """(bits, codec) of the largest message per element that `spec` can put on the wire."""
     if spec.hook in ("dynamiq", "dynamiq_bitrate"):
         if spec.family == "rht":
-            return (8 if (spec.dynamic_bitrate or "mixed" in spec.name.lower()) else spec.bits, "rht")
+            return (8, "rht_mix") if spec.mixed else (spec.bits, "rht")
         return (8, "scmix_" + spec.lattice)  # records of per-superchunk width: sized for the widest
     if spec.hook == "mxfp8":
         return (8, "mx")
@@ -171,9 +171,22 @@ def _grid(state: HookState, bucket) -> Optional[int]:
     return None
 
 
-def _bucket_bits(state: HookState, index: int, buf: torch.Tensor) -> int:
-    policy = state["bit_policy"]
-    return policy.bits_for(index, buf) if policy is not None else state["spec"].bits
+def _mixed_plan(state: HookState, index: int, numel: int, device) -> torch.Tensor:
+    """The width plan of bucket `index` (int32 [2 nblocks + 1]: offsets, then widths): what the previous
+    collective of this bucket derived, the restored one after a resume, or every block at the nominal width."""
+    from .parallel.fused import BLOCK, uniform_plan
+
+    plans = state["params"].setdefault("rht_plans", {})
+    nb = (numel + BLOCK - 1) // BLOCK
+    plan = plans.get(index)
+    if plan is None or plan.numel() != 2 * nb + 1:
+        restored = state["params"].get("rht_plans_restored", {}).pop(index, None)
+        if restored is not None and restored.numel() == 2 * nb + 1:
+            plan = restored.to(device=device, dtype=torch.int32)
+        else:
+            plan = uniform_plan(numel, state["spec"].bits, device)
+        plans[index] = plan
+    return plan
 
 
 def _rht_allreduce(state: HookState, bucket) -> torch.futures.Future:
@@ -184,14 +197,14 @@ def _rht_allreduce(state: HookState, bucket) -> torch.futures.Future:
     world = _world(state)
     if world == 1 or buf.numel() == 0:
         return _done(buf)
-    bits = _bucket_bits(state, index, buf)
+    bits = spec.bits
     st = state["stats"]
     st["collectives"] += 1
-    st["buckets"][index] = {"numel": buf.numel(), "bits": bits}
+    st["buckets"][index] = {"numel": buf.numel(), "bits": bits, "mixed": spec.mixed}
     if buf.is_cuda:
         from .parallel.fused import wire_bytes_per_rank
 
-        st["wire_bytes"] += wire_bytes_per_rank(buf.numel(), world, bits, "rht")
+        st["wire_bytes"] += wire_bytes_per_rank(buf.numel(), world, bits, "rht")  # mixed: the average meets `bits`
     exact = None
     if cfg.measure_comm_error:
         exact = buf.detach().clone().float()
@@ -199,25 +212,52 @@ def _rht_allreduce(state: HookState, bucket) -> torch.futures.Future:
         exact.div_(world)
     if buf.is_cuda:
         eng = _engine(state)
+        if spec.mixed and eng.tensor_rotation:
+            raise ValueError("a code width per block needs rotation='simt' (DQ_ROTATION)")
+
+        def launch(grid):
+            if spec.mixed:  # one collective with a width per block, then the next step's widths from its scales
+                plan = _mixed_plan(state, index, buf.numel(), buf.device)
+                eng.allreduce_(buf, 8, spec.topology, cfg.seed, step, index, no_transmit=spec.compute_only,
+                               correlated=spec.correlated, codec="rht_mix", plan=plan, ctas=grid)
+                if not spec.compute_only:
+                    eng.update_widths_(plan, buf.numel(), float(bits))
+            else:
+                eng.allreduce_(buf, bits, spec.topology, cfg.seed, step, index, no_transmit=spec.compute_only,
+                               correlated=spec.correlated, ctas=grid)
+
         if cfg.overlap:
             stream = state["comm_stream"]
             stream.wait_stream(torch.cuda.current_stream())
             fut = torch.futures.Future(devices=[buf.device])
             with torch.cuda.stream(stream), tracing.nvtx_range(f"bucket{index}.fused_{spec.topology}_{bits}bit"):
-                eng.allreduce_(buf, bits, spec.topology, cfg.seed, step, index, no_transmit=spec.compute_only,
-                               correlated=spec.correlated, ctas=_grid(state, bucket))
+                launch(_grid(state, bucket))
                 buf.record_stream(stream)
                 if exact is not None:
                     _account_error(state, buf, exact)
                 fut.set_result(buf)
             return fut
-        eng.allreduce_(buf, bits, spec.topology, cfg.seed, step, index, no_transmit=spec.compute_only,
-                               correlated=spec.correlated)
+        launch(None)
     else:
-        from .parallel.cpu_backend import allreduce_gloo
+        from .parallel import cpu_backend as cb
 
-        out = allreduce_gloo(buf.detach().float().numpy(), bits, spec.topology, cfg.seed, step, index,
-                             group=state["group"], correlated=spec.correlated)
+        factory, made = None, {}
+        if spec.mixed:
+            nb = (buf.numel() + 1023) // 1024
+            widths = state["params"].setdefault("rht_widths", {}).get(index)
+            if widths is None or len(widths) != nb:
+                widths = np.full(nb, bits, dtype=np.uint8)
+
+            def factory(_bits, seed, step_, bucket_, world_, rank_):
+                made["codec"] = cb.RhtMixCodecCPU(widths, seed, step_, bucket_, world_, rank_)
+                return made["codec"]
+
+        out = cb.allreduce_gloo(buf.detach().float().numpy(), bits, spec.topology, cfg.seed, step, index,
+                                group=state["group"], correlated=spec.correlated, codec_factory=factory)
+        if spec.mixed:
+            from . import bitalloc
+
+            state["params"]["rht_widths"][index] = bitalloc.rht_block_widths(made["codec"].block_absmax(nb), bits)[0]
         buf.copy_(torch.from_numpy(out).to(buf.dtype))
     if exact is not None:
         _account_error(state, buf, exact)
@@ -305,13 +345,7 @@ def select_comm_hook(method: str, topology: Optional[str] = None) -> Callable:
 
 def build_comm_state(config: DynamiqConfig, group=None) -> List[HookState]:
     """``[state]`` as the reference's ``build_comm_state`` returns it (train_llm_causal.py:242-286)."""
-    state = HookState(config, group)
-    spec = state["spec"]
-    if spec.hook in ("dynamiq", "dynamiq_bitrate") and spec.family == "rht" and spec.dynamic_bitrate:
-        from .bitalloc import BucketBitPolicy
-
-        state["bit_policy"] = BucketBitPolicy(spec.bits)
-    return [state]
+    return [HookState(config, group)]
 
 
 def register(model, method: str = "dynamiQ_aee_5bit", config: Optional[DynamiqConfig] = None, group=None,

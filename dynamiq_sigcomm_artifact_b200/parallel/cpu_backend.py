@@ -38,7 +38,7 @@ class RhtCodecCPU:
         # the RNG stream id mixes the bucket in so that buckets do not share uniforms
         self._tag_base = (bucket & 0xFFFF) << 16
 
-    def message_bytes(self, nblocks: int) -> int:
+    def message_bytes(self, nblocks: int, block_idx=None) -> int:
         return cr.payload_bytes(nblocks, self.bits)
 
     def rotate(self, x_blocks: np.ndarray) -> np.ndarray:
@@ -48,14 +48,47 @@ class RhtCodecCPU:
         return cr.encode_blocks(y, self.bits, block_idx, self._tag_base | tag, self.step, self.seed, self.rank,
                                 self.world, self.layout)
 
-    def decode(self, msg: np.ndarray, nblocks: int) -> np.ndarray:
+    def decode(self, msg: np.ndarray, nblocks: int, block_idx=None) -> np.ndarray:
         return cr.decode_blocks(msg, nblocks, self.bits, self.layout)
 
-    def decode_add(self, msg: np.ndarray, nblocks: int, acc: np.ndarray) -> np.ndarray:
+    def decode_add(self, msg: np.ndarray, nblocks: int, acc: np.ndarray, block_idx=None) -> np.ndarray:
         return cr.decode_add_blocks(msg, nblocks, self.bits, acc, self.layout)
 
     def finish(self, y: np.ndarray) -> np.ndarray:
         return cr.rotate_inv(y, self.signs, 1.0 / self.world)
+
+
+class RhtMixCodecCPU(RhtCodecCPU):
+    """The rotation codec with a code width per block (`widths`: one entry per block of the bucket)."""
+
+    def __init__(self, widths, seed: int, step: int, bucket: int, world: int, rank: int = 0, layout: str = "simt"):
+        super().__init__(8, seed, step, bucket, world, rank, layout)
+        self.widths = np.asarray(widths, dtype=np.uint8)
+        self.final_scales = {}  # block index -> scale of the all-gathered message (what the next widths derive from)
+
+    def message_bytes(self, nblocks: int, block_idx=None) -> int:
+        return cr.mixed_payload_bytes(self.widths[np.asarray(block_idx)])
+
+    def encode(self, y: np.ndarray, block_idx: np.ndarray, tag: int) -> np.ndarray:
+        return cr.encode_blocks_mixed(y, self.widths[block_idx], block_idx, self._tag_base | tag, self.step, self.seed,
+                                      self.rank, self.world, self.layout)
+
+    def decode(self, msg: np.ndarray, nblocks: int, block_idx=None) -> np.ndarray:
+        w = self.widths[np.asarray(block_idx)]
+        _, scale = cr._split_mixed(msg, w)
+        for k, b in enumerate(np.asarray(block_idx)):
+            self.final_scales[int(b)] = float(scale[k])
+        return cr.decode_blocks_mixed(msg, w, self.layout)
+
+    def decode_add(self, msg: np.ndarray, nblocks: int, acc: np.ndarray, block_idx=None) -> np.ndarray:
+        return cr.decode_blocks_mixed(msg, self.widths[np.asarray(block_idx)], self.layout, acc)
+
+    def block_absmax(self, nblocks: int) -> np.ndarray:
+        """absmax of every block of the reduced bucket, as the scales of the final messages give it."""
+        out = np.zeros(nblocks, dtype=np.float32)
+        for b, s in self.final_scales.items():
+            out[b] = np.float32(s) * np.float32(cr.qmax(int(self.widths[b])))
+        return out
 
 
 class LocalTransport:
@@ -149,9 +182,9 @@ def message_sizes(codec, nblocks: int, world: int, topology: str, rank: int) -> 
         for st in prog:
             lo, hi = sch.shard_range(nblocks, world, st.shard)
             if st.out == sch.OUT_SEND and st.dst == rank:
-                sizes[st.send_slot] = codec.message_bytes(hi - lo)
+                sizes[st.send_slot] = codec.message_bytes(hi - lo, np.arange(lo, hi))
             elif st.out == sch.OUT_FINAL and r != rank:
-                sizes[sch.ag_slot(world, topology, st.shard)] = codec.message_bytes(hi - lo)
+                sizes[sch.ag_slot(world, topology, st.shard)] = codec.message_bytes(hi - lo, np.arange(lo, hi))
     return sizes
 
 
@@ -168,11 +201,11 @@ def run_rank(x: np.ndarray, codec, rank: int, world: int, topology: str, ep, cor
         idx = np.arange(lo, hi)
         if st.out == sch.OUT_DECODE:
             msg = ep.recv(st.recv_slot)
-            blocks[lo:hi] = codec.finish(codec.decode(msg, nb))
+            blocks[lo:hi] = codec.finish(codec.decode(msg, nb, idx))
             continue
         v = blocks[lo:hi] if st.local == sch.LOCAL_WS else codec.rotate(blocks[lo:hi])
         for k in range(st.nrecv):
-            v = codec.decode_add(ep.recv(st.recv_slot + k), nb, v)
+            v = codec.decode_add(ep.recv(st.recv_slot + k), nb, v, idx)
         if st.out == sch.OUT_STORE:
             blocks[lo:hi] = v
         elif st.out == sch.OUT_SEND:
@@ -182,7 +215,7 @@ def run_rank(x: np.ndarray, codec, rank: int, world: int, topology: str, ep, cor
             for p in range(world):
                 if p != rank:
                     ep.send(p, sch.ag_slot(world, topology, st.shard), msg)
-            blocks[lo:hi] = codec.finish(codec.decode(msg, nb))
+            blocks[lo:hi] = codec.finish(codec.decode(msg, nb, idx))
     ep.flush()
     return blocks.reshape(-1)[:n].copy()
 

@@ -36,7 +36,9 @@ def _align(x: int, a: int) -> int:
     return (x + a - 1) // a * a
 
 
-CODECS = {"rht": 0, "rht_tc": 1, "sc_aee": 2, "sc_mee": 3, "mx": 4, "cast": 5, "scmix_aee": 6, "scmix_mee": 7}
+CODECS = {"rht": 0, "rht_tc": 1, "sc_aee": 2, "sc_mee": 3, "mx": 4, "cast": 5, "scmix_aee": 6, "scmix_mee": 7,
+          "rht_mix": 8}
+RHT_CODECS = ("rht", "rht_tc", "rht_mix")  # messages of these carry one fp32 scale per block after the codes
 
 
 def block_bytes(bits: int, codec: str = "rht") -> int:
@@ -47,6 +49,8 @@ def block_bytes(bits: int, codec: str = "rht") -> int:
         return 4 * (16 * (2 * 8 + 1) + 2)
     if codec == "mx":
         return 128 * bits + 32
+    if codec == "rht_mix":  # a width per block: slots are sized for the widest
+        return 128 * 8
     return 128 * bits
 
 
@@ -73,7 +77,7 @@ class Layout:
 
     @property
     def slot_stride(self) -> int:
-        scales = 4 * self.blocks_per_shard if self.codec in ("rht", "rht_tc") else 0
+        scales = 4 * self.blocks_per_shard if self.codec in RHT_CODECS else 0
         return _align(self.scales_off + scales, 256)
 
 
@@ -83,8 +87,16 @@ def wire_bytes_per_rank(numel: int, world: int, bits: int, codec: str = "rht") -
     if world <= 1:
         return 0
     lay = Layout(numel, world, bits, codec)
-    per_block = block_bytes(bits, codec) + (4 if codec in ("rht", "rht_tc") else 0)
+    per_block = (128 * bits if codec in RHT_CODECS else block_bytes(bits, codec)) + (4 if codec in RHT_CODECS else 0)
     return 2 * (world - 1) * lay.blocks_per_shard * per_block
+
+
+def uniform_plan(numel: int, bits: int, device) -> torch.Tensor:
+    """int32 [2 nblocks + 1] plan of the "rht_mix" codec with every block at `bits`: exclusive prefix sum of the
+    widths (message offsets in units of 128 bytes), then the widths."""
+    nb = (int(numel) + BLOCK - 1) // BLOCK
+    return torch.cat([torch.arange(nb + 1, dtype=torch.int32) * int(bits),
+                      torch.full((nb,), int(bits), dtype=torch.int32)]).to(device)
 
 
 def program_tensor(rank: int, world: int, topology: str, correlated: bool = False) -> torch.Tensor:
@@ -104,7 +116,7 @@ _SC_CACHE: Dict[tuple, tuple] = {}
 
 def codec_args(codec: str, bits: int, device) -> tuple:
     """(codec id, lattice_max, c1, c2, lut) as the native operators take them."""
-    if codec in ("rht", "rht_tc", "mx", "cast"):
+    if codec in ("rht", "rht_tc", "rht_mix", "mx", "cast"):
         return CODECS[codec], 0.0, 0.0, 0.0, None
     if codec.startswith("scmix_"):
         key = (codec, 0, str(device))
@@ -248,6 +260,23 @@ class FusedAllreduce:
         counters.add("fused_allreduce")
         return bucket
 
+    # -- a code width per block (codec "rht_mix") ------------------------------------------
+    def uniform_plan(self, numel: int, bits: int) -> torch.Tensor:
+        """The plan of a bucket whose blocks all have `bits`-bit codes (what a bucket starts with)."""
+        return uniform_plan(numel, bits, torch.device("cuda", self.device))
+
+    def update_widths_(self, plan: torch.Tensor, numel: int, target_bits: float) -> torch.Tensor:
+        """After a collective with codec "rht_mix" (same stream): rewrite `plan` in place with the widths the
+        next collective of this bucket should use, from the block scales the collective left in this rank's
+        all-gather slots.  Every rank computes the same plan; nothing is communicated or read by the host."""
+        lay = Layout(int(numel), self.world, 8, "rht_mix")
+        parity = self.epoch & 1
+        mailbox = self.buf.local()[parity * self.set_bytes: (parity + 1) * self.set_bytes]
+        self.ops.rht_widths_update(mailbox, plan, lay.nblocks, lay.blocks_per_shard, lay.slot_stride, lay.scales_off,
+                                   sch.ag_slot(self.world, "ring", 0), int(round(float(target_bits) * lay.nblocks)))
+        counters.add("rht_widths_update")
+        return plan
+
     def check(self) -> None:
         """Raise :class:`CollectiveTimeout` if any kernel so far gave up on a wait (synchronises)."""
         words = self._status_view.cpu().tolist()
@@ -301,6 +330,14 @@ class LocalCluster:
             self.threads, lay.blocks_per_shard, lay.slot_stride, lay.scales_off, 0, self.epoch, seed, step, bucket_id,
             (1.0 / self.world) if post_scale is None else post_scale, self.timeout_ns, no_transmit,
             *codec_args(codec, bits, buckets[0].device), plan, self.prefetch)
+
+    def update_widths_(self, plan: torch.Tensor, numel: int, target_bits: float, rank: int = 0) -> torch.Tensor:
+        """`FusedAllreduce.update_widths_` for the emulated rank `rank` (whose mailbox the last run filled)."""
+        lay = Layout(int(numel), self.world, 8, "rht_mix")
+        self.ops.rht_widths_update(self.mail[rank], plan, lay.nblocks, lay.blocks_per_shard, lay.slot_stride,
+                                   lay.scales_off, sch.ag_slot(self.world, "ring", 0),
+                                   int(round(float(target_bits) * lay.nblocks)))
+        return plan
 
     def allreduce_(self, buckets: List[torch.Tensor], bits: int, topology: str = "ring", correlated: bool = False,
                    **kw) -> List[torch.Tensor]:

@@ -119,7 +119,10 @@ def main() -> None:
     args = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    import datetime
+
+    # a rank that raises leaves the others in a library collective: bound that wait
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=180))
     rank, world = dist.get_rank(), dist.get_world_size()
     gen = small_int_grad if args.rotation == "tc" else heavy_tail_grad
     t0 = time.time()
