@@ -149,7 +149,7 @@ class DynamiqConfig:
     use_nvls: bool = True  # multimem for the uncompressed baseline where the box exposes it
     measure_comm_error: bool = False  # exact all-reduce of a clone + vNMSE accounting
     nvtx: bool = False
-    debug: bool = False
+    debug: bool = False  # guard zones around the mailbox / flag regions, checked by every status check
     validate_topology: bool = True
 
     @classmethod
@@ -168,8 +168,6 @@ class DynamiqConfig:
         c.debug = _env(["DQ_DEBUG", "RING_RDMA_DEBUG"], c.debug, _bool)
         c.nvtx = _env(["DQ_NVTX"], c.nvtx, _bool)
         c.validate_topology = _env(["DQ_VALIDATE_NVLINK", "RING_VALIDATE_NVLINK"], c.validate_topology, _bool)
-        if _env(["BUTTERFLY_RDMA_DISABLE"], False, _bool) and c.topology is None:
-            c.topology = None  # the old switch chose the NCCL butterfly; topology still comes from the method
         return c
 
     def spec(self) -> MethodSpec:

@@ -49,6 +49,9 @@ void fwht_levels_(at::Tensor x, int64_t first, int64_t nlevels, double scale);
 void superchunk_widths(at::Tensor stats, at::Tensor state, at::Tensor s_out, at::Tensor widths);
 at::Tensor superchunk_plan(at::Tensor widths);
 void superchunk_bitrate_update(at::Tensor sorted_s, at::Tensor state, double target);
+void thc_quantize_(at::Tensor y, at::Tensor stats, int64_t world, double t_over_sqrt_d, int64_t levels, int64_t stream,
+                   int64_t step, int64_t seed);
+void thc_dequantize_(at::Tensor total, at::Tensor stats, int64_t world, double t_over_sqrt_d, int64_t levels);
 void rht_widths_update(at::Tensor mailbox, at::Tensor plan, int64_t nblocks, int64_t blocks_per_shard,
                        int64_t slot_stride, int64_t scales_off, int64_t first_ag_slot, int64_t budget);
 at::Tensor rope(at::Tensor x, at::Tensor cos, at::Tensor sin, bool backward);
@@ -77,6 +80,10 @@ TORCH_LIBRARY(dq, m) {
   m.def("superchunk_bitrate_update(Tensor sorted_s, Tensor(a!) state, float target) -> ()", &dq::superchunk_bitrate_update);
   m.def("rht_widths_update(Tensor mailbox, Tensor(a!) plan, int nblocks, int blocks_per_shard, int slot_stride, "
         "int scales_off, int first_ag_slot, int budget) -> ()", &dq::rht_widths_update);
+  m.def("thc_quantize_(Tensor(a!) y, Tensor stats, int world, float t_over_sqrt_d, int levels, int stream, int step, "
+        "int seed) -> ()", &dq::thc_quantize_);
+  m.def("thc_dequantize_(Tensor(a!) total, Tensor stats, int world, float t_over_sqrt_d, int levels) -> ()",
+        &dq::thc_dequantize_);
   m.def("rope(Tensor x, Tensor cos, Tensor sin, bool backward) -> Tensor", &dq::rope);
   m.def("adamw_step(Tensor table, Tensor numel, Tensor chunk_start, int total_chunks, bool param_bf16, bool grad_bf16, "
         "float lr, float beta1, float beta2, float eps, float weight_decay, int step, float grad_scale) -> ()", &dq::adamw_step);

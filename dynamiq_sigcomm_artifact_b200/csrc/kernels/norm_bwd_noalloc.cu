@@ -36,8 +36,8 @@ int scratch_for_current_device(float** out) {
   if (g_scratch_addr[dev] == nullptr) {
     float* p = nullptr;
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch);
-    if (e != cudaSuccess || p == nullptr) {
-      t_last_cuda_error = static_cast<int>(e);
+    if (e != cudaSuccess || p == nullptr) {  // a null address with a success code still is a failure to report
+      t_last_cuda_error = static_cast<int>(e != cudaSuccess ? e : cudaErrorInvalidSymbol);
       return DQ_NOALLOC_CUDA_ERROR;
     }
     g_scratch_addr[dev] = p;
@@ -84,6 +84,7 @@ extern "C" int dq_rmsnorm_bwd_noalloc(const void* dy, const void* x, const float
   const int rc = scratch_for_current_device(&parts);
   if (rc != DQ_NOALLOC_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  (void)cudaGetLastError();  // an error left behind by the caller's earlier launches is not this call's
   const int max_grid = DQ_NOALLOC_MAX_PARTS / kNormWarps;
   int grid = (rows + kNormWarps - 1) / kNormWarps;
   if (grid > max_grid) grid = max_grid;

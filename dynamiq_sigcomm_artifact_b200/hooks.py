@@ -158,7 +158,8 @@ def _engine(state: HookState):
                                          ctas=cfg.comm_ctas, threads=cfg.comm_threads,
                                          timeout_ms=cfg.wait_timeout_ms, validate=cfg.validate_topology,
                                          rotation=cfg.rotation, max_ctas=max(cfg.comm_ctas, cfg.tail_ctas),
-                                         prefetch=cfg.comm_prefetch, widest=widest_wire(state["spec"]))
+                                         prefetch=cfg.comm_prefetch, widest=widest_wire(state["spec"]),
+                                         debug=cfg.debug)
         state["comm_stream"] = torch.cuda.Stream(priority=-1)
     return state["engine"]
 

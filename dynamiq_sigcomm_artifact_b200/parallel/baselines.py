@@ -124,6 +124,7 @@ def thc_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tenso
         return _done(buf)
     levels = spec.quantization_levels or 31
     step, index = int(state["batch_idx"]), bucket.index()
+    rank = dist.get_rank(group)
     flat = buf.reshape(-1)
     pos, part = 0, 0
     while pos < flat.numel():
@@ -136,30 +137,97 @@ def thc_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tenso
         if s is None:  # fixed per (bucket, partition): kept as int8
             s = cache[(index, part, d)] = _signs(d, cfg.seed + 7919 * part, buf.device).to(torch.int8)
         y = _rotate(x * s)
-        norm = x.norm().reshape(1)
-        dist.all_reduce(norm, op=dist.ReduceOp.MAX, group=group)
-        first = y[:1].clone()
-        dist.all_reduce(first, group=group)
-        rng = (THC_T * norm / math.sqrt(d)).clamp_min(1e-30)
-        if buf.is_cuda:  # rounding offsets are private to a rank: the device generator is enough
-            u = torch.rand(d, device=buf.device)
+        # rounding offsets are private to a rank (independent errors average out) and a pure function of
+        # (seed, step, bucket, partition, rank) on both devices
+        tag = ((index & 0xFFF) << 20) | ((part & 0xFF) << 12) | (rank & 0xFFF)
+        if buf.is_cuda:
+            total = _thc_partition_cuda(state, y, x, d, levels, world, rank, tag, step, index, part)
+            mean = total  # dequantised in place
         else:
-            u = (uniform_bytes(d, ((index & 0xFFFF) << 16) | part, step, cfg.seed, buf.device).float() + 0.5) / 256.0
-        t = (y.clamp(-rng, rng) + rng) / (2 * rng) * (levels - 1)
-        bins = torch.floor(t + u).clamp_(0, levels - 1)
-        if bins.is_cuda:
-            # integer bins over this package's point-to-point kernel: bf16 carries sums up to 256 exactly
-            wire = 16 if world * (levels - 1) <= 256 else 32
-            total = _p2p_mean(state, bins, wire, spec, step, ((index & 0xFFF) << 4) | (part & 0xF)) * world
-        else:
+            norm = x.norm().reshape(1)
+            dist.all_reduce(norm, op=dist.ReduceOp.MAX, group=group)
+            first = y[:1].clone()
+            dist.all_reduce(first, group=group)
+            rng = (THC_T * norm / math.sqrt(d)).clamp_min(1e-30)
+            u = (uniform_bytes(d, tag, step, cfg.seed, buf.device).float() + 0.5) / 256.0
+            t = (y.clamp(-rng, rng) + rng) / (2 * rng) * (levels - 1)
+            bins = torch.floor(t + u).clamp_(0, levels - 1)
             total = allreduce_torch(bins, IntBinsCodec(), spec.topology, group, transmit=not spec.compute_only) * world
-        mean = (total / (levels - 1) * (2 * rng) - world * rng) / world
-        mean[0] = first[0] / world
+            mean = (total / (levels - 1) * (2 * rng) - world * rng) / world
+            mean[0] = first[0] / world
         out = _rotate(mean) * s
         flat[pos: pos + m] = out[:m].to(buf.dtype)
         pos += m
         part += 1
     return _done(buf)
+
+
+def _thc_partition_cuda(state, y: torch.Tensor, x: torch.Tensor, d: int, levels: int, world: int, rank: int, tag: int,
+                        step: int, index: int, part: int) -> torch.Tensor:
+    """CUDA body of one THC partition, without a library collective: one small sum all-reduce of
+    [||g_0||, .., ||g_{W-1}||, first coordinate] over this package's fp32 point-to-point kernel, the quantise
+    kernel, the bins over the identity wire (bf16 carries sums up to 256 exactly), the dequantise kernel."""
+    from .. import ops as _ops
+    from ..hooks import _engine
+    from ..utils import counters
+
+    dq = _ops.require()
+    spec, cfg = state["spec"], state["config"]
+    eng = _engine(state)
+    stats = torch.zeros(world + 1, dtype=torch.float32, device=y.device)
+    stats[rank] = x.norm()
+    stats[world] = y[0]
+    bid = ((index & 0xFFF) << 4) | (part & 0xF)
+    eng.allreduce_(stats, 32, "direct", cfg.seed, step, bid ^ 0x8000, codec="cast", post_scale=1.0)
+    scale = THC_T / math.sqrt(d)
+    dq.thc_quantize_(y, stats, world, scale, levels, tag, step, cfg.seed)
+    counters.add("thc_quantize")
+    wire = 16 if world * (levels - 1) <= 256 else 32
+    eng.allreduce_(y, wire, spec.topology, cfg.seed, step, bid, no_transmit=spec.compute_only, codec="cast",
+                   post_scale=1.0)
+    dq.thc_dequantize_(y, stats, world, scale, levels)
+    counters.add("thc_dequantize")
+    return y
+
+
+def _omni_union_cuda(state, rows: torch.Tensor, bitmap: torch.Tensor, k: int, world: int, index: int, params: dict):
+    """CUDA body of OmniReduce without a library collective and without a device-to-host read on the step's
+    path.  The bitmap is summed over this package's fp32 point-to-point kernel; the union of the ranks' rows
+    (at most world * k rows) is compacted into a buffer of exactly that capacity with a prefix sum, reduced on
+    the bf16 identity wire, and scattered back; rows of `rows` outside the union are zeroed in place.  The
+    union's density, which steers the next steps' k, is read one step late through pinned memory.  Returns
+    the density observed at an EARLIER step of this bucket (None until one has arrived)."""
+    from ..hooks import _engine
+
+    spec, cfg = state["spec"], state["config"]
+    step = int(state["batch_idx"])
+    eng = _engine(state)
+    nrows = rows.shape[0]
+    eng.allreduce_(bitmap, 32, "direct", cfg.seed, step, ((index & 0xFFF) << 4) | 1, codec="cast", post_scale=1.0)
+    mask = bitmap > 0
+    cap = min(nrows, world * k)
+    pos = torch.cumsum(mask, 0) - 1
+    slot = torch.where(mask & (pos < cap), pos, torch.full_like(pos, cap))  # row `cap` collects what is dropped
+    dense = torch.zeros(cap + 1, 256, dtype=torch.float32, device=rows.device)
+    dense.index_copy_(0, slot, rows)
+    eng.allreduce_(dense[:cap].reshape(-1), 16, spec.topology, cfg.seed, step, (index & 0xFFF) << 4,
+                   no_transmit=spec.compute_only, codec="cast")
+    dense[cap].zero_()
+    rows.copy_(dense.index_select(0, slot))
+    # density feedback, one step late and without blocking
+    pend = params.setdefault("omni_pending", {})
+    seen = None
+    old = pend.get(index)
+    if old is not None and old[1].query():
+        seen = float(old[0][0]) / nrows
+        pend.pop(index)
+    if index not in pend:
+        host = torch.zeros(1, dtype=torch.float32).pin_memory()
+        host.copy_(mask.sum().float().reshape(1), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        pend[index] = (host, ev)
+    return seen
 
 
 def omnireduce_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
@@ -188,20 +256,22 @@ def omnireduce_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torc
     top = torch.topk(rows.pow(2).sum(dim=1), k).indices
     bitmap = torch.zeros(nrows, dtype=torch.float32, device=buf.device)
     bitmap[top] = 1.0
-    dist.all_reduce(bitmap, group=group)
-    union = torch.nonzero(bitmap > 0, as_tuple=False).reshape(-1)
-    out = torch.zeros_like(rows)
-    if union.numel():
-        dense = rows.index_select(0, union).reshape(-1)
-        if dense.is_cuda:
-            red = _p2p_mean(state, dense, 16, spec, int(state["batch_idx"]), index)
-        else:
+    if buf.is_cuda:
+        real = _omni_union_cuda(state, rows, bitmap, k, world, index, params)
+        out = rows  # reduced in place: rows outside the union are zero
+    else:
+        dist.all_reduce(bitmap, group=group)
+        union = torch.nonzero(bitmap > 0, as_tuple=False).reshape(-1)
+        out = torch.zeros_like(rows)
+        if union.numel():
+            dense = rows.index_select(0, union).reshape(-1)
             red = allreduce_torch(dense, CastCodec(torch.bfloat16), spec.topology, group,
                                   transmit=not spec.compute_only)
-        out.index_copy_(0, union, red.view(-1, 256))
-    real = union.numel() / nrows
-    ratio = min(max(real / target, 0.6), 1 / 0.6)
-    topks[index] = 0.75 * local + 0.25 * local / ratio
-    params["last_density"] = real
+            out.index_copy_(0, union, red.view(-1, 256))
+        real = union.numel() / nrows
+    if real is not None:
+        ratio = min(max(real / target, 0.6), 1 / 0.6)
+        topks[index] = 0.75 * local + 0.25 * local / ratio
+        params["last_density"] = real
     buf.copy_(out.reshape(-1)[:n].to(buf.dtype))
     return _done(buf)

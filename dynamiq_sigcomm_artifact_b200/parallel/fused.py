@@ -32,6 +32,14 @@ class CollectiveTimeout(RuntimeError):
     """A device-side wait ran out of budget; the kernel returned instead of hanging."""
 
 
+class MailboxOverrun(RuntimeError):
+    """A guard zone around the mailbox or flag region of the symmetric buffer was overwritten."""
+
+
+CANARY_BYTES = 256
+CANARY_VALUE = 0xC5
+
+
 def _align(x: int, a: int) -> int:
     return (x + a - 1) // a * a
 
@@ -167,7 +175,7 @@ class FusedAllreduce:
 
     def __init__(self, group=None, max_numel: int = 32 << 20, ctas: int = 64, threads: int = 256,
                  timeout_ms: int = 2000, validate: bool = True, rotation: str = "simt", max_ctas: Optional[int] = None,
-                 prefetch: bool = True, widest: Tuple[int, str] = (32, "cast")):
+                 prefetch: bool = True, widest: Tuple[int, str] = (32, "cast"), debug: bool = False):
         """`ctas` is the default grid of a collective; a call may ask for any grid up to `max_ctas`
         (every rank must ask for the same one): a bucket that runs under backward wants a small grid,
         the last bucket of a step has the GPU to itself.
@@ -175,7 +183,13 @@ class FusedAllreduce:
         The mailbox is sized for `max_numel` elements on the `widest` wire (bits, codec) the caller will use
         - (32, "cast"), the fp32 identity wire, unless told otherwise; a 5-bit rotation codec needs a sixth
         of that.  A call that needs more grows the buffers (a collective re-allocation), so callers that know
-        their largest bucket and codec pass them here and never re-allocate inside a training step."""
+        their largest bucket and codec pass them here and never re-allocate inside a training step.
+
+        `debug`: every region of the symmetric buffer that peers write into (the two slot sets, the flag
+        array) is fenced by 256-byte guard zones filled with a pattern; ``check()`` reads them back and
+        raises :class:`MailboxOverrun` if a store landed outside its region.  With compute-sanitizer not
+        available on every machine, this and the byte-exact oracle comparisons are the overrun net."""
+        self.debug = bool(debug)
         self.ops = _ops.require()
         self.group = group
         self.world = dist.get_world_size(group)
@@ -203,14 +217,25 @@ class FusedAllreduce:
         self.allocations += 1
         self.max_numel = int(max_numel)
         self.slot_bytes = _align(int(slot_bytes), 256)
-        self.set_bytes = _align(self.nslots * self.slot_bytes, 4096)
+        # layout: [set 0][guard][set 1][guard][flags][guard][status][tail scratch]; a set is slots plus one guard
+        self.set_bytes = _align(self.nslots * self.slot_bytes, 4096) + 4096  # the last 4 KiB of a set are its guard
         self.flag_words_per_set = self.nslots * self.max_ctas
         self.off_flags = 2 * self.set_bytes
-        self.off_status = self.off_flags + _align(2 * self.flag_words_per_set * 4, 4096)
+        flag_bytes = _align(2 * self.flag_words_per_set * 4, 4096)
+        self.off_status = self.off_flags + flag_bytes + 4096  # guard after the flags
         self.off_tail = self.off_status + 256
         total = self.off_tail + BLOCK * 4
         self.buf = SymmetricBuffer(total, group=self.group, device=self.device, validate=self.validate)
-        self._status_view = self.buf.local()[self.off_status: self.off_status + 16].view(torch.int32)
+        local = self.buf.local()
+        self._status_view = local[self.off_status: self.off_status + 16].view(torch.int32)
+        self._guards = [local[self.set_bytes - 4096: self.set_bytes - 4096 + CANARY_BYTES],
+                        local[2 * self.set_bytes - 4096: 2 * self.set_bytes - 4096 + CANARY_BYTES],
+                        local[self.off_flags + flag_bytes: self.off_flags + flag_bytes + CANARY_BYTES]]
+        for g in self._guards:
+            g.fill_(CANARY_VALUE)
+        if self.world > 1:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)  # nobody writes into a peer before its guards are in place
 
     def ensure_capacity(self, numel: int, bits: int = 32, codec: str = "cast") -> None:
         """Grow the symmetric buffers if a message of `numel` elements on the (bits, codec) wire does not fit a
@@ -233,8 +258,9 @@ class FusedAllreduce:
     def allreduce_(self, bucket: torch.Tensor, bits: int, topology: str = "ring", seed: int = 0, step: int = 0,
                    bucket_id: int = 0, no_transmit: bool = False, correlated: bool = False,
                    codec: Optional[str] = None, ctas: Optional[int] = None,
-                   plan: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """In-place mean all-reduce of a flat fp32/bf16 CUDA tensor on the current stream.
+                   plan: Optional[torch.Tensor] = None, post_scale: Optional[float] = None) -> torch.Tensor:
+        """In-place mean all-reduce of a flat fp32/bf16 CUDA tensor on the current stream (`post_scale`: the
+        factor applied to the sum instead of 1 / world; 1.0 gives the plain sum).
 
         `codec`: None (the engine's rotation codec), "sc_aee" / "sc_mee" (the hierarchical superchunk
         codec with 2 / 4 / 8-bit codes), "scmix_aee" / "scmix_mee" (the same with a width per superchunk,
@@ -252,10 +278,11 @@ class FusedAllreduce:
         mail = [p + parity * self.set_bytes for p in self.buf.ptrs]
         flags = [p + self.off_flags for p in self.buf.ptrs]
         self.ops.fused_allreduce(
-            bucket, self.program(topology, correlated), mail, flags, self.set_bytes, 2 * self.flag_words_per_set, self.nslots,
+            bucket, self.program(topology, correlated), mail, flags, self.set_bytes - 4096, 2 * self.flag_words_per_set, self.nslots,
             self.buf.local_ptr + self.off_status, self.buf.local_ptr + self.off_tail, self.rank, self.world, bits,
             grid, self.threads, lay.blocks_per_shard, lay.slot_stride, lay.scales_off,
-            parity * self.flag_words_per_set, self.epoch, seed, step, bucket_id, 1.0 / self.world, self.timeout_ns,
+            parity * self.flag_words_per_set, self.epoch, seed, step, bucket_id,
+            (1.0 / self.world) if post_scale is None else float(post_scale), self.timeout_ns,
             no_transmit, *codec_args(codec, bits, bucket.device), plan, self.prefetch)
         counters.add("fused_allreduce")
         return bucket
@@ -284,6 +311,16 @@ class FusedAllreduce:
         if msg is not None:
             self._status_view.zero_()
             raise CollectiveTimeout(f"rank {self.rank}: {msg}")
+        if self.debug:
+            self.check_guards()
+
+    def check_guards(self) -> None:
+        """Raise :class:`MailboxOverrun` if a guard zone no longer holds its pattern (synchronises)."""
+        names = ("after slot set 0", "after slot set 1", "after the flag array")
+        for name, g in zip(names, self._guards):
+            if not bool((g == CANARY_VALUE).all()):
+                bad = int((g != CANARY_VALUE).nonzero()[0])
+                raise MailboxOverrun(f"rank {self.rank}: guard zone {name} overwritten at byte {bad}")
 
     def state_dict(self) -> dict:
         return {"epoch": self.epoch}

@@ -154,7 +154,9 @@ def _native_mixed(state, bucket) -> torch.futures.Future:
     with torch.cuda.stream(stream):
         flat, stats = dq.superchunk_center(buf.reshape(-1), world)
         counters.add("superchunk_center")
-        dist.all_reduce(stats, group=group)
+        # (mean, energy) per superchunk, summed over the ranks by this package's own point-to-point kernel on
+        # the fp32 identity wire: no library collective on the hook's path
+        eng.allreduce_(stats.view(-1), 32, "direct", cfg.seed, step, (index << 2) | 2, codec="cast", post_scale=1.0)
         if spec.dynamic_bitrate:
             ctl = params.get("bitrate")
             if ctl is None:

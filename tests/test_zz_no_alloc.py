@@ -30,7 +30,10 @@ def test_noalloc_rmsnorm_backward_matches_operator(dtype):
     dq = ops.require()
     lib = _lib()
     torch.manual_seed(0)
-    for rows, hidden in [(4096, 2048), (77, 136)]:  # second call: smaller, reuses the dirty scratch
+    side = torch.cuda.Stream()
+    # every chunk-count branch of the dispatcher (hidden / 256 rounded up: 8, 1, 2, 3, 5 -> 6, 7 -> 8, 4); each
+    # call after the first reuses the scratch the previous one left dirty; one call runs on a side stream
+    for rows, hidden in [(4096, 2048), (77, 136), (33, 512), (50, 768), (19, 1280), (41, 1792), (600, 1024)]:
         x = torch.randn(rows, hidden, device="cuda").to(dtype)
         dy = torch.randn(rows, hidden, device="cuda").to(dtype)
         w = torch.randn(hidden, device="cuda")
@@ -39,7 +42,7 @@ def test_noalloc_rmsnorm_backward_matches_operator(dtype):
         dx = torch.empty_like(x)
         dw = torch.empty(hidden, device="cuda")
         torch.cuda.synchronize()
-        stream = torch.cuda.current_stream().cuda_stream
+        stream = side.cuda_stream if hidden == 768 else torch.cuda.current_stream().cuda_stream
         rc = lib.dq_rmsnorm_bwd_noalloc(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
                                         dw.data_ptr(), rows, hidden, int(dtype == torch.bfloat16), stream)
         assert rc == 0, lib.dq_noalloc_strerror(rc)
@@ -47,6 +50,14 @@ def test_noalloc_rmsnorm_backward_matches_operator(dtype):
         assert torch.equal(dx, dx_ref)  # same kernel, same arithmetic
         tol = 2e-3
         assert torch.allclose(dw, dw_ref, atol=tol * max(1.0, float(dw_ref.abs().max())), rtol=tol)
+        # and against plain PyTorch in fp32, so that this test stands without the other operator
+        xf, dyf = x.float().requires_grad_(True), dy.float()
+        wf = w.clone().requires_grad_(True)
+        y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * wf
+        y.backward(dyf)
+        t16 = 3e-2 if dtype == torch.bfloat16 else 2e-4
+        assert torch.allclose(dx.float(), xf.grad, atol=t16 * float(xf.grad.abs().max()), rtol=t16)
+        assert torch.allclose(dw, wf.grad, atol=t16 * max(1.0, float(wf.grad.abs().max())), rtol=t16)
 
 
 def test_noalloc_rejects_oversize_and_bad_arguments():
