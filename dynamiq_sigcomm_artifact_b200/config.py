@@ -37,7 +37,7 @@ class MethodSpec:
 
     name: str
     hook: str  # one of HOOK_KINDS
-    family: str = "rht"  # "rht" | "superchunk" (dynamiq hooks only)
+    family: str = "rht"  # "rht" | "superchunk" | "sim" (dynamiq hooks only)
     lattice: str = "aee"  # "aee" linear | "mee" logarithmic lattice (superchunk family)
     bits: int = 5  # nominal average code width
     fixed: bool = False  # superchunk: only the 4-bit group is communicated
@@ -49,6 +49,7 @@ class MethodSpec:
     no_compress: bool = False  # run the selection logic but skip the collective (debug)
     compute_only: bool = False  # "coov": kernels run, nothing is transmitted (debug)
     fpx_format: Optional[str] = None  # "fp4" | "fp6" | "zero" for the fpx hook
+    shared_scale: bool = False  # fpx / fp8: block maxima MAX-reduced over the ranks, adaptive gain (simulation hook)
     quantization_levels: Optional[int] = None  # thc
     thresholds: Dict[int, float] = field(default_factory=dict)
 
@@ -93,6 +94,8 @@ def parse_method(name: str, topology: Optional[str] = None) -> MethodSpec:
                                   or "momentum" in low) else "rht"
         if "rht" in low or "mixed" in low:
             family = "rht"
+        if low.endswith("_sim") or "_sim_" in low:  # the simulation stack's hierarchical compressor (any width)
+            family = "sim"
         mixed = family == "rht" and ("mixed" in low or "bitrate" in low)
         lattice = "aee" if "aee" in low else "mee"
         fixed = "fixed" in low
@@ -103,11 +106,14 @@ def parse_method(name: str, topology: Optional[str] = None) -> MethodSpec:
                           correlated="correlated" in low, no_compress="no_compress" in low,
                           momentum="momentum" in low, mixed=mixed,
                           thresholds=thresholds, **common)
+    shared = "shared" in low or "adaptive" in low
     if "fp8" in low:
+        if shared:
+            return MethodSpec(hook="fpx", bits=8, fpx_format="fp8", shared_scale=True, **common)
         return MethodSpec(hook="mxfp8", bits=8, **common)
     for fmt, b in (("fp4", 4), ("fp6", 6), ("zero", 0)):
         if fmt in low:
-            return MethodSpec(hook="fpx", bits=b, fpx_format=fmt, **common)
+            return MethodSpec(hook="fpx", bits=b, fpx_format=fmt, shared_scale=shared and fmt != "zero", **common)
     if "fp16" in low:
         return MethodSpec(hook="fp16", bits=16, **common)
     if "fp32" in low or low in ("none", "nccl", "allreduce"):

@@ -283,7 +283,32 @@ def dynamiq_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.T
         from .parallel.superchunk import superchunk_allreduce
 
         return superchunk_allreduce(state, bucket)
+    if state["spec"].family == "sim":
+        return _sim_allreduce(state, bucket)
     return _rht_allreduce(state, bucket)
+
+
+def _sim_allreduce(state: HookState, bucket) -> torch.futures.Future:
+    """``dynamiQ_{aee,mee}_{b}bit_sim``: the simulation stack's hierarchical compressor over the step programs,
+    executed with tensor operators on whatever device the bucket lives on (numerics study, not a fast path)."""
+    from .parallel.codecs import SimHierarchicalCodec
+    from .parallel.torch_backend import allreduce_torch
+
+    spec, cfg = state["spec"], state["config"]
+    buf = bucket.buffer()
+    world = _world(state)
+    if world == 1 or buf.numel() == 0:
+        return _done(buf)
+    codec = SimHierarchicalCodec(spec.bits, spec.lattice, seed=cfg.seed, step=int(state["batch_idx"]),
+                                 bucket=bucket.index())
+    n = buf.numel()
+    pad = (-n) % (codec.align * world)
+    x = torch.zeros(n + pad, dtype=torch.float32, device=buf.device)
+    x[:n] = buf.reshape(-1).float()
+    out = allreduce_torch(x, codec, spec.topology, state["group"], transmit=not spec.compute_only)
+    buf.copy_(out[:n].to(buf.dtype).view_as(buf))
+    state["stats"]["collectives"] += 1
+    return _done(buf)
 
 
 def _cast_hook(dtype: Optional[torch.dtype]) -> Callable:

@@ -69,7 +69,62 @@ def _block_float_hook(fmt_of):
 
 
 mxfp8_hook = _block_float_hook(lambda spec: "fp8")
-fpx_hook = _block_float_hook(lambda spec: spec.fpx_format)
+_local_scale_fpx_hook = _block_float_hook(lambda spec: spec.fpx_format)
+
+SHARED_CHUNK = 32  # values that share one power-of-two scale in the shared-scale variant
+SHARED_PROPORTION = 0.01  # saturated share of a bucket above which the gain backs off
+
+
+def fpx_shared_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
+    """``fp4_shared`` / ``fp6_shared`` / ``fp8_shared``: the simulation stack's block-float hook
+    (simulations_llm/new_comm_hooks/comm_hooks.py:990-1060).  Every 32-value chunk is divided by a
+    power-of-two bound of its magnitude that is MAX-reduced over the ranks first, so all ranks share the
+    scales and the hops add bare minifloats; the values are then multiplied by a gain ``mu`` per bucket
+    that a feedback rule keeps just below saturation: if more than 1 % of the reduced values sit at the
+    format's largest magnitude, mu shrinks by 5 % (not below vmax / (2 W)); otherwise it grows by 2^0.02
+    (not above vmax).  FP6 and FP8 keep mu fixed, as in the reference.  The MAX reduction is a library
+    collective: this variant reproduces the simulation's numerics, not a fused fast path."""
+    from .codecs import _FORMATS, MinifloatCodec
+
+    state = _begin(state, bucket)
+    buf = bucket.buffer()
+    if state["batch_idx"] < state["config"].warmup_steps:
+        return _warmup(state, buf)
+    group, spec = state["group"], state["spec"]
+    world = dist.get_world_size(group)
+    if world == 1:
+        return _done(buf)
+    fmt = spec.fpx_format
+    vmax = _FORMATS[fmt][2]
+    index, n = bucket.index(), buf.numel()
+    mus = state["params"].setdefault("fpx_mu", {})
+    mu = mus.get(index, vmax / world)
+    nchunk = (n + SHARED_CHUNK - 1) // SHARED_CHUNK
+    x = torch.zeros(nchunk * SHARED_CHUNK, dtype=torch.float32, device=buf.device)
+    x[:n] = buf.reshape(-1).float() / world
+    x = x.view(nchunk, SHARED_CHUNK)
+    bound = x.abs().amax(dim=1, keepdim=True).clamp_min(1e-30)
+    bound = torch.exp2(torch.ceil(torch.log2(bound)))  # round up to a power of two
+    dist.all_reduce(bound, op=dist.ReduceOp.MAX, group=group)
+    eps = 5e-7 if fmt == "fp4" else 1e-23
+    scaled = (x / (bound + eps) * mu).reshape(-1)
+    total = allreduce_torch(scaled, MinifloatCodec(fmt), spec.topology, group, transmit=not spec.compute_only) * world
+    if fmt == "fp4":  # saturation feedback, decided from the reduced values every rank holds identically
+        saturated = int((total.abs() >= vmax - 5e-8).sum())
+        if saturated > total.numel() * SHARED_PROPORTION:
+            mus[index] = max(mu * 0.95, vmax / world / 2)
+        else:
+            mus[index] = min(vmax, mu * 2 ** 0.02)
+    else:
+        mus[index] = mu
+    out = (total.view(nchunk, SHARED_CHUNK) / mu * (bound + eps)).reshape(-1)[:n]
+    buf.copy_(out.to(buf.dtype).view_as(buf))
+    return _done(buf)
+
+
+def fpx_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
+    st = state[0] if isinstance(state, (list, tuple)) else state
+    return (fpx_shared_hook if st["spec"].shared_scale else _local_scale_fpx_hook)(state, bucket)
 
 
 def fwht_(x: torch.Tensor) -> torch.Tensor:

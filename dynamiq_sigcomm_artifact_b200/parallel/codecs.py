@@ -110,6 +110,78 @@ class SuperchunkCodec(TorchCodec):
         return (level * dec.unsqueeze(2)).reshape(-1)
 
 
+SIM_EPS = {2: 0.27, 4: 0.20, 5: 0.18, 7: 0.10, 8: 0.08}  # simulations_llm/new_comm_hooks/utils_aggregation.py:8
+
+
+class SimHierarchicalCodec(TorchCodec):
+    """The simulation stack's hierarchical compressor (``Mee_Dynamic_Range_Hierarchical``,
+    simulations_llm/new_comm_hooks/utils_aggregation.py:176-357), which differs from the testbed's superchunk
+    format in three ways that this class keeps:
+
+    * any code width in 2..8 with the simulation's own epsilon table (``SIM_EPS``); codes are the lattice
+      indices -2^(b-1) .. 2^(b-1), rounded stochastically between the two neighbouring lattice values in
+      proportion to the position between them (unbiased also on the logarithmic lattice);
+    * the scale of a chunk, max|chunk| / lattice(2^(b-1)), is itself quantised to 8 bits relative to the
+      largest scale of its supergroup with stochastic rounding, floor(s / s_max * 255 + u);
+    * no mean-centring and no superchunk byte format: the message carries the codes, one byte per
+      chunk scale and one fp32 per supergroup (the simulation keeps them as bf16 numbers in one tensor).
+
+    Rounding offsets come from the counter-based generator (the reference slides an LCG window over a
+    pre-generated pool), so runs are reproducible from the seed."""
+
+    def __init__(self, bits: int, lattice: str = "mee", chunk: int = 16, supergroup: int = 16, seed: int = 0,
+                 step: int = 0, bucket: int = 0):
+        if bits not in SIM_EPS:
+            raise ValueError(f"the simulation compressor has widths {sorted(SIM_EPS)}")
+        self.bits, self.lattice, self.chunk, self.supergroup = bits, lattice, chunk, supergroup
+        self.seed, self.step, self.bucket = seed, step, bucket
+        self.eps = SIM_EPS[bits]
+        self.half = 1 << (bits - 1)
+        self.align = chunk * supergroup
+        levels = torch.arange(-(1 << bits), (1 << bits) + 1, dtype=torch.float32)
+        self.table = mee_lattice(levels, self.eps) if lattice == "mee" else levels
+        self.top = float(self.table[(1 << bits) + self.half])  # lattice value of the largest code
+
+    def message_bytes(self, numel: int) -> int:
+        nchunk = numel // self.chunk
+        return 2 * numel + nchunk + 4 * (nchunk // self.supergroup)
+
+    def _u(self, n: int, tag: int, device) -> torch.Tensor:
+        stream = ((self.bucket & 0xFFFF) << 16) | (tag & 0xFFFF)
+        return (uniform_bytes(n, stream, self.step, self.seed, device).float() + 0.5) / 256.0
+
+    def encode(self, v, first, tag):
+        assert v.numel() % self.align == 0
+        x = torch.nan_to_num(v.float(), nan=0.0, posinf=0.0, neginf=0.0).view(-1, self.chunk)
+        tab = self.table.to(x.device)
+        scale = x.abs().amax(dim=1, keepdim=True) / self.top + 1e-23
+        y = x / scale
+        idx = torch.searchsorted(tab, y.contiguous(), right=True).clamp(1, tab.numel() - 1)
+        left, right = tab[idx - 1], tab[idx]
+        prob = (y - left) / (right - left)
+        u = self._u(x.numel(), tag, x.device).view_as(x)
+        code = torch.where(u < prob, idx, idx - 1) - (1 << self.bits)
+        code = code.clamp(-self.half, self.half)
+        sg = scale.view(-1, self.supergroup)
+        sg_max = sg.amax(dim=1, keepdim=True) + 1e-23
+        q = sg / sg_max * 255.0
+        qf = torch.floor(q)
+        u2 = self._u(sg.numel(), tag ^ 0x5A5A, x.device).view_as(sg)
+        qf = (qf + (u2 < (q - qf)).float()).clamp_(0, 255)
+        return torch.cat([code.to(torch.int16).reshape(-1).contiguous().view(torch.uint8),
+                          qf.to(torch.uint8).reshape(-1), sg_max.reshape(-1).contiguous().view(torch.uint8)])
+
+    def decode(self, msg, numel):
+        nchunk = numel // self.chunk
+        nsg = nchunk // self.supergroup
+        code = msg[: 2 * numel].contiguous().view(torch.int16).long().view(nchunk, self.chunk)
+        q = msg[2 * numel: 2 * numel + nchunk].float().view(nsg, self.supergroup)
+        sg_max = msg[2 * numel + nchunk: 2 * numel + nchunk + 4 * nsg].contiguous().view(torch.float32).view(nsg, 1)
+        scale = (q * sg_max / 255.0).view(nchunk, 1)
+        tab = self.table.to(msg.device)
+        return (tab[code + (1 << self.bits)] * scale).reshape(-1)
+
+
 class CastCodec(TorchCodec):
     """Values travel as bf16 / fp16 / fp32; partial sums are rounded to the wire type per hop."""
 
@@ -217,6 +289,31 @@ class BlockFloatCodec(TorchCodec):
         mag = self._table(msg.device)[(code & ((1 << (w - 1)) - 1)).clamp_max(self.table.numel() - 1)]
         y = torch.ldexp(sign * mag, e.unsqueeze(2))
         return y.reshape(-1)[:numel]
+
+
+class MinifloatCodec(TorchCodec):
+    """Values already normalised by the caller travel as bare FP8 / FP6 / FP4 numbers: every hop rounds its
+    partial sum to the format's grid and saturates at its largest magnitude, with no scale of its own - the
+    arithmetic of the reference's simulated ``Fpx_arithmetics`` under the shared-scale hook
+    (simulations_llm/new_comm_hooks/comm_hooks.py:1026-1046).  One byte per value on this executor's wire."""
+
+    align = 16
+
+    def __init__(self, fmt: str):
+        self.fmt = fmt
+        self.ebits, self.mbits, self.vmax = _FORMATS[fmt]
+        self.width = 1 + self.ebits + self.mbits
+
+    def message_bytes(self, numel: int) -> int:
+        return numel * 4
+
+    def encode(self, v, first, tag):
+        y = _round_to_minifloat(torch.nan_to_num(v.float(), nan=0.0, posinf=self.vmax, neginf=-self.vmax), self.ebits,
+                                self.mbits, self.vmax)
+        return y.contiguous().view(torch.uint8).reshape(-1)
+
+    def decode(self, msg, numel):
+        return msg.view(torch.float32)[:numel].clone()
 
 
 class IntBinsCodec(TorchCodec):

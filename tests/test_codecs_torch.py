@@ -120,3 +120,43 @@ def test_round_plan_covers_program(topology):
         flat = [st for rnd in rounds for st in rnd[r]]
         assert flat == sch.build_program(r, 4, topology)
     assert len(rounds) <= 6
+
+
+def test_minifloat_codec_rounds_to_the_grid_and_saturates():
+    from dynamiq_sigcomm_artifact_b200.parallel.codecs import MinifloatCodec
+
+    c = MinifloatCodec("fp4")
+    v = torch.tensor([0.0, 0.2, 0.26, 0.8, 1.2, 2.4, 3.4, 5.1, 7.0, -9.0, 0.74])
+    back = c.decode(c.encode(v, 0, 0), v.numel())
+    assert back.tolist() == [0.0, 0.0, 0.5, 1.0, 1.0, 2.0, 3.0, 6.0, 6.0, -6.0, 0.5]
+    from dynamiq_sigcomm_artifact_b200.config import parse_method
+
+    s = parse_method("fp4_shared")
+    assert s.hook == "fpx" and s.shared_scale and s.fpx_format == "fp4" and not parse_method("fp4").shared_scale
+
+
+@pytest.mark.parametrize("bits,lattice", [(4, "mee"), (5, "mee"), (8, "aee"), (2, "mee")])
+def test_simulation_hierarchical_codec_is_unbiased_and_bounded(bits, lattice):
+    from dynamiq_sigcomm_artifact_b200.parallel.codecs import SIM_EPS, SimHierarchicalCodec
+
+    torch.manual_seed(bits)
+    n = 16 * 16 * 8
+    x = torch.randn(n) * torch.exp(torch.randn(n // 16)).repeat_interleave(16)
+    acc = torch.zeros(n)
+    reps = 200
+    for rep in range(reps):
+        c = SimHierarchicalCodec(bits, lattice, seed=3, step=rep, bucket=1)
+        msg = c.encode(x, 0, 0x100)
+        assert msg.numel() == c.message_bytes(n)
+        y = c.decode(msg, n)
+        acc += y
+    mean = acc / reps
+    # unbiased: the error of the mean of many independent roundings (codes and chunk scales both round
+    # stochastically) falls like 1 / reps; one rounding stays within the width's error level
+    nm = lambda a: float((a - x).pow(2).sum() / x.pow(2).sum())
+    single, averaged = nm(y), nm(mean)
+    assert single < {2: 0.5, 4: 0.05, 5: 0.02, 8: 3e-4}[bits], single
+    assert averaged < single / (reps / 4), (single, averaged)
+    assert SIM_EPS[5] == 0.18
+    with pytest.raises(ValueError):
+        SimHierarchicalCodec(3)

@@ -91,7 +91,8 @@ def test_every_method_family_world2():
         "dynamiQ_mee_5bit": 4e-2, "dynamiQ_aee_5bit_superchunk": 4e-2, "dynamiQ_aee_4bit_fixed": 5e-2,
         "dynamiQ_mee_5bit_dynamic_bitrate": 4e-2, "dynamiQ_mee_4bit_butterfly": 0.1,
         "dynamiQ_aee_8bit_direct": 5e-4, "MXfp8": 5e-3, "fp6": 1e-2, "fp4": 5e-2, "thc": 5e-2,
-        "omnireduce": 1.0, "fp16": 1e-6,
+        "omnireduce": 1.0, "fp16": 1e-6, "fp4_shared": 0.2, "fp8_shared": 5e-3, "dynamiQ_aee_5bit_mixed": 3e-2,
+        "dynamiQ_mee_5bit_sim": 5e-2,
     }
     res = _run(list(bounds), numel=1 << 16, steps=4, world=2)
     for r in res:
