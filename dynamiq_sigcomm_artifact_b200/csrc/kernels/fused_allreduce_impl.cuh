@@ -207,9 +207,16 @@ __device__ __forceinline__ void fused_simt_body(const ARParams& p) {
           else if constexpr (MX) mx_decode_block<MXB, false>(v, rec_tile, lane);
           else sc_decode_block<SCB, MEE, false>(v, rec_tile, scp, lane);
           __syncwarp();
-          const float wf = static_cast<float>(p.world);
+          // the mean divides by the world size, as the tensor-operator codecs do; any other post-scale
+          // (1 for a plain sum) multiplies
+          const float wf = static_cast<float>(p.world), ps = p.finish_scale * 1024.0f;
+          if (ps == __fdiv_rn(1.0f, wf)) {
 #pragma unroll
-          for (int k = 0; k < 32; ++k) v[k] = __fdiv_rn(v[k], wf);
+            for (int k = 0; k < 32; ++k) v[k] = __fdiv_rn(v[k], wf);
+          } else {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) v[k] = __fmul_rn(v[k], ps);
+          }
           sc_store_block<T>(bucket + e0, valid, vec_ok, lane, v);
         }
       } else {
