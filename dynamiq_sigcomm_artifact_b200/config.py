@@ -152,7 +152,11 @@ class DynamiqConfig:
     wait_timeout_ms: int = 2000  # budget of every device-side wait before it gives up with an error status
     max_bucket_mb: int = 128  # symmetric-buffer capacity (grown on demand between steps)
     overlap: bool = True  # run the collective on a side stream under backward
-    use_nvls: bool = True  # multimem for the uncompressed baseline where the box exposes it
+    use_nvls: bool = False  # uncompressed wires (bf16 method) reduce inside the NVSwitch (multimem) when the box
+    #                         exposes a multicast object and there are more than two ranks.  Off by default: on four
+    #                         B200s the point-to-point cast wire was faster at every size from 1 MB to 1 GB
+    #                         (256 MB fp32 bucket, bf16 wire: 0.47 ms against 0.54 ms), its casts ride in the same
+    #                         pass as the transfer while the in-switch path stages through a symmetric buffer
     measure_comm_error: bool = False  # exact all-reduce of a clone + vNMSE accounting
     nvtx: bool = False
     debug: bool = False  # guard zones around the mailbox / flag regions, checked by every status check

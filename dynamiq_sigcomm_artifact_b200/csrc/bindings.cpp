@@ -49,6 +49,9 @@ void fwht_levels_(at::Tensor x, int64_t first, int64_t nlevels, double scale);
 void superchunk_widths(at::Tensor stats, at::Tensor state, at::Tensor s_out, at::Tensor widths);
 at::Tensor superchunk_plan(at::Tensor widths);
 void superchunk_bitrate_update(at::Tensor sorted_s, at::Tensor state, double target);
+void nvls_allreduce(at::Tensor bucket, int64_t stage_ptr, int64_t mc_ptr, std::vector<int64_t> flag_ptrs,
+                    int64_t stage_bytes, int64_t status_ptr, int64_t rank, int64_t world, int64_t wire_bits, int64_t epoch,
+                    double post_scale, int64_t timeout_ns, int64_t ctas);
 void thc_quantize_(at::Tensor y, at::Tensor stats, int64_t world, double t_over_sqrt_d, int64_t levels, int64_t stream,
                    int64_t step, int64_t seed);
 void thc_dequantize_(at::Tensor total, at::Tensor stats, int64_t world, double t_over_sqrt_d, int64_t levels);
@@ -80,6 +83,9 @@ TORCH_LIBRARY(dq, m) {
   m.def("superchunk_bitrate_update(Tensor sorted_s, Tensor(a!) state, float target) -> ()", &dq::superchunk_bitrate_update);
   m.def("rht_widths_update(Tensor mailbox, Tensor(a!) plan, int nblocks, int blocks_per_shard, int slot_stride, "
         "int scales_off, int first_ag_slot, int budget) -> ()", &dq::rht_widths_update);
+  m.def("nvls_allreduce(Tensor(a!) bucket, int stage_ptr, int mc_ptr, int[] flag_ptrs, int stage_bytes, int status_ptr, "
+        "int rank, int world, int wire_bits, int epoch, float post_scale, int timeout_ns, int ctas) -> ()",
+        &dq::nvls_allreduce);
   m.def("thc_quantize_(Tensor(a!) y, Tensor stats, int world, float t_over_sqrt_d, int levels, int stream, int step, "
         "int seed) -> ()", &dq::thc_quantize_);
   m.def("thc_dequantize_(Tensor(a!) total, Tensor stats, int world, float t_over_sqrt_d, int levels) -> ()",

@@ -86,6 +86,9 @@ class HookState(dict):
         if self["engine"] is not None:
             self["engine"].close()
             self["engine"] = None
+        if self.get("nvls") is not None:
+            self["nvls"].close()
+            self["nvls"] = None
 
 
 def _unwrap(state) -> HookState:
@@ -162,6 +165,25 @@ def _engine(state: HookState):
                                          debug=cfg.debug)
         state["comm_stream"] = torch.cuda.Stream(priority=-1)
     return state["engine"]
+
+
+def _nvls(state: HookState, numel: int, wire_bits: int):
+    """The in-switch (NVLS) all-reduce engine for the uncompressed wires, or None: off by configuration
+    (``use_nvls``), no multicast support on this box, two ranks only (nothing to reduce inside the switch), or a
+    bucket larger than its staging buffer.  Created once, sized for the largest bucket seen."""
+    cfg: DynamiqConfig = state["config"]
+    if not cfg.use_nvls or _world(state) <= 2:
+        return None
+    eng = state.get("nvls")
+    if eng is None:
+        from .parallel.nvls import NvlsAllreduce
+
+        cap = max(int(state.get("max_bucket_numel", 0)), numel)
+        eng = state["nvls"] = NvlsAllreduce(group=state["group"], max_numel=cap, wire_bits=32,
+                                            timeout_ms=cfg.wait_timeout_ms)
+        if not eng.available and dist.get_rank(state["group"]) == 0:
+            print(f"[dynamiq] NVLS all-reduce not used: {eng.reason}", flush=True)
+    return eng if eng.fits(numel, wire_bits) else None
 
 
 def _grid(state: HookState, bucket) -> Optional[int]:
@@ -338,13 +360,17 @@ def bf16_hook(state, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tens
     if not use_p2p:
         return _library_mean(state, buf, torch.bfloat16)
     spec, cfg = state["spec"], state["config"]
-    eng = _engine(state)
+    eng = _engine(state)  # also owns the side stream
+    nvls = _nvls(state, buf.numel(), 16) if not spec.compute_only else None
     stream = state["comm_stream"]
     stream.wait_stream(torch.cuda.current_stream())
     fut = torch.futures.Future(devices=[buf.device])
     with torch.cuda.stream(stream), tracing.nvtx_range(f"bucket{bucket.index()}.p2p_bf16_{spec.topology}"):
-        eng.allreduce_(buf.reshape(-1), 16, spec.topology, cfg.seed, int(state["batch_idx"]), bucket.index(),
-                       no_transmit=spec.compute_only, codec="cast", ctas=_grid(state, bucket))
+        if nvls is not None:  # in-switch reduction on the bf16 wire
+            nvls.allreduce_(buf.reshape(-1), 16, ctas=_grid(state, bucket) or cfg.comm_ctas)
+        else:
+            eng.allreduce_(buf.reshape(-1), 16, spec.topology, cfg.seed, int(state["batch_idx"]), bucket.index(),
+                           no_transmit=spec.compute_only, codec="cast", ctas=_grid(state, bucket))
         buf.record_stream(stream)
         fut.set_result(buf)
     return fut

@@ -29,8 +29,34 @@ import torch.distributed as dist
 from ..parallel import schedules as sch
 from ..parallel.fused import BLOCK, FusedAllreduce, Layout, LocalCluster
 
-NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction per GPU on this pool
+NVLINK_NOMINAL_GBS = 900.0  # NVLink 5, per direction per GPU; replaced by --peer-copy's measurement
 HBM_GBS_FALLBACK = 6650.0
+
+
+def measure_peer_copy(eng: FusedAllreduce, nbytes: int = 256 << 20, iters: int = 10) -> float:
+    """GB/s of a device-to-device copy out of the NEXT rank's symmetric buffer into local memory, all ranks
+    copying at once (every link direction loaded): the link bandwidth a kernel's peer traffic can hope for.
+    MAX time over the ranks, CUDA events."""
+    from .. import ops as _ops
+
+    dq = _ops.require()
+    world, rank = eng.world, eng.rank
+    nbytes = min(nbytes, eng.buf.nbytes // 4096 * 4096)
+    peer = dq.wrap_ptr(eng.buf.ptrs[(rank + 1) % world], nbytes, eng.device)
+    dst = torch.empty(nbytes, dtype=torch.uint8, device=peer.device)
+    for _ in range(3):
+        dst.copy_(peer)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        dst.copy_(peer)
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return nbytes / float(t[0]) / 1e6
 
 
 def measured_peaks() -> dict:
@@ -58,7 +84,7 @@ def time_op(fn, prepare, iters: int, warmup: int, reps: int = 1) -> float:
     for _ in range(warmup):
         prepare()
         fn()
-    total = 0.0
+    samples = []
     for _ in range(iters):
         prepare()
         if dist.is_initialized():
@@ -70,13 +96,18 @@ def time_op(fn, prepare, iters: int, warmup: int, reps: int = 1) -> float:
             fn()
         e1.record()
         torch.cuda.synchronize()
-        total += e0.elapsed_time(e1) / reps
-    ms = total / iters
-    if dist.is_initialized():
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        samples.append(e0.elapsed_time(e1) / reps)
+    t = torch.tensor(samples, dtype=torch.float64)
+    if dist.is_initialized():  # every sample is the slowest rank's
+        t = t.cuda()
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t[0])
-    return ms
+        t = t.cpu()
+    global LAST_SPREAD
+    LAST_SPREAD = {"median_ms": float(t.median()), "min_ms": float(t.min()), "max_ms": float(t.max()), "iters": iters}
+    return float(t.mean())
+
+
+LAST_SPREAD: dict = {}
 
 
 def nmse_vs(exact: torch.Tensor, got: torch.Tensor) -> float:
@@ -93,6 +124,20 @@ def run_collectives(args) -> None:
     topologies = args.topologies.split(",")
     eng = FusedAllreduce(max_numel=max(sizes), ctas=args.ctas, threads=args.threads, timeout_ms=5000,
                          rotation=args.rotation)
+    link_gbs, link_kind = NVLINK_NOMINAL_GBS, "nominal"
+    if args.peer_copy:
+        link_gbs, link_kind = measure_peer_copy(eng), "measured"
+        if rank == 0:
+            print(json.dumps({"peer_copy_gbs_per_direction": link_gbs, "world": world,
+                              "how": "device-to-device copy of 256 MB out of the next rank's buffer, all ranks at once"}),
+                  flush=True)
+    nvls = None
+    if not args.no_nvls and world > 1:
+        from ..parallel.nvls import NvlsAllreduce
+
+        nvls = NvlsAllreduce(max_numel=max(sizes), wire_bits=32, ctas=148, timeout_ms=5000)
+        if rank == 0 and not nvls.available:
+            print(json.dumps({"nvls": "unavailable", "reason": nvls.reason}), flush=True)
     rows = []
     for numel in sizes:
         base = make_input(numel, rank, args.seed, dev)
@@ -106,7 +151,7 @@ def run_collectives(args) -> None:
             row = {"method": name, "world": world, "numel": numel, "input_mb": in_bytes / 2 ** 20, "ms": ms,
                    "algbw_gbs": 2 * (world - 1) / world * in_bytes / ms / 1e6,
                    "input_gbs": in_bytes / ms / 1e6, "wire_gbs": wire_bytes / ms / 1e6,
-                   "link_fraction_of_measured": wire_bytes / ms / 1e6 / NVLINK_GBS, "nmse": err}
+                   f"link_fraction_of_{link_kind}": wire_bytes / ms / 1e6 / link_gbs, "nmse": err, **LAST_SPREAD}
             row.update(extra or {})
             rows.append(row)
             if rank == 0:
@@ -141,6 +186,12 @@ def run_collectives(args) -> None:
             eng.check()
             lay = Layout(numel, world, cbits, "cast")
             record(f"{label}_direct", ms, 2 * (world - 1) * lay.blocks_per_shard * 128 * cbits, nmse_vs(exact, work))
+        # in-switch reduction (NVLS) on the same wires, when the box exposes a multicast object
+        if nvls is not None and nvls.available:
+            for cbits, label in ((16, "nvls_bf16"), (32, "nvls_fp32")):
+                ms = time_op(lambda: nvls.allreduce_(work, cbits), lambda: work.copy_(base), args.iters, args.warmup)
+                nvls.check()
+                record(label, ms, 2 * numel * cbits // 8, nmse_vs(exact, work))
         for topo in topologies:
             if topo == "butterfly" and world & (world - 1):
                 continue
@@ -157,11 +208,11 @@ def run_collectives(args) -> None:
                 ms = time_op(fused, lambda: work.copy_(base), args.iters, args.warmup)
                 eng.check()
                 hbm = measured_peaks().get("hbm_gbs", HBM_GBS_FALLBACK)
-                t_link = wire / (NVLINK_GBS * 1e6)
+                t_link = wire / (link_gbs * 1e6)
                 t_hbm = (2 * in_bytes + 3 * wire) / (hbm * 1e6)
                 record(f"fused_{topo}_{bits}bit" + ("_tc" if args.rotation == "tc" else ""), ms, wire, nmse_vs(exact, work),
                        {"roofline_ms": max(t_link, t_hbm), "roofline_fraction": max(t_link, t_hbm) / ms,
-                        "bound": "nvlink" if t_link > t_hbm else "hbm"})
+                        "bound": "nvlink" if t_link > t_hbm else "hbm", "link_gbs": link_gbs, "link": link_kind})
     if rank == 0 and args.out:
         with open(args.out, "w") as f:
             json.dump(rows, f, indent=1)
@@ -267,6 +318,9 @@ def main(argv=None) -> None:
     ap.add_argument("--rht-only", action="store_true", help="--kernels: only the rotation codec's stages")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-nvls", action="store_true", help="skip the in-switch (NVLS) rows")
+    ap.add_argument("--peer-copy", action="store_true",
+                    help="measure the peer-copy bandwidth first and use it as the link figure of the roofline fractions")
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--out", default=None)
     args = ap.parse_args(argv)

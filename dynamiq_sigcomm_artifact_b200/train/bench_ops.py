@@ -23,7 +23,11 @@ def main(argv=None) -> None:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--rows", type=int, default=8192)
+    ap.add_argument("--only", default="", help="comma list of substrings: time only the kernels whose name has one "
+                    "(a profiler capture of one kernel then runs a small program)")
+    ap.add_argument("--adamw-params", type=int, default=124_000_000)
     args = ap.parse_args(argv)
+    only = [t for t in args.only.split(",") if t]
     dq = _ops.require()
     dev = torch.device("cuda", 0)
     hbm = measured_peaks().get("hbm_gbs", HBM_GBS_FALLBACK)
@@ -32,6 +36,8 @@ def main(argv=None) -> None:
     rows = args.rows
 
     def timed(name, fn, nbytes):
+        if only and not any(t in name for t in only):
+            return
         for _ in range(args.warmup):
             fn()
         total = 0.0
@@ -76,11 +82,13 @@ def main(argv=None) -> None:
     timed("cross_entropy_fwd_50304", lambda: dq.ce_fwd(logits, labels, V, -100), rows * Vp * 2)
     work = logits.clone()
     timed("cross_entropy_bwd_50304", lambda: dq.ce_bwd(work, labels, lse, one, nv, V, -100), 2 * rows * Vp * 2)
-    p = torch.randn(124_000_000, device=dev).requires_grad_(True)
-    p.grad = torch.randn_like(p)
-    opt = FusedAdamW([p], lr=1e-4)
-    opt.step()
-    timed("adamw_124M_fp32", lambda: opt.step(), p.numel() * 28)
+    if not only or any(t in "adamw_124M_fp32" for t in only):
+        p = torch.randn(args.adamw_params, device=dev).requires_grad_(True)
+        p.grad = torch.randn_like(p)
+        opt = FusedAdamW([p], lr=1e-4)
+        opt.step()
+        timed("adamw_124M_fp32", lambda: opt.step(), p.numel() * 28)
+        del p, opt
     xs = torch.randn(64 << 20, device=dev)
     timed("superchunk_center_64Mi", lambda: dq.superchunk_center(xs, 8), xs.numel() * 8 + xs.numel() // 32)
     bins = torch.randint(0, 16, (64 << 20,), dtype=torch.uint8, device=dev)

@@ -34,3 +34,20 @@ def test_collective_over_peer_mappings_matches_the_simulator(rotation, tmp_path)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     summary = json.loads(out.read_text())
     assert summary["ok"] and summary["collectives_checked"] >= 60
+
+
+def test_in_switch_allreduce_matches_the_exact_mean():
+    ngpu = torch.cuda.device_count()
+    if ngpu < 2:
+        pytest.skip("needs at least two GPUs")
+    n = 4 if ngpu >= 4 else 2
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+           os.path.join(ROOT, "tests", "multigpu", "check_nvls.py")]
+    res = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    line = [ln for ln in res.stdout.splitlines() if ln.startswith("{")][-1]
+    summary = json.loads(line)
+    if not summary["available"]:
+        pytest.skip("no NVLink multicast on this machine: " + summary["reason"])
+    assert summary["cases"] == 36
