@@ -303,9 +303,34 @@ def run_kernels(args) -> None:
             json.dump(rows, f, indent=1)
 
 
+def run_reference(args) -> None:
+    """The reference arm lives beside the checkout's baseline/ folder, outside the package, and imports
+    nothing of it; it prints its own rows (or one ``unavailable`` line)."""
+    import importlib.util
+
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    path = os.path.join(root, "baseline", "reference_allreduce.py")
+    if not os.path.isfile(path):
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "baseline/reference_allreduce.py not found beside the package"}))
+        return
+    spec = importlib.util.spec_from_file_location("reference_allreduce", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    argv = ["--sizes-mb", args.sizes_mb, "--methods", args.methods, "--iters", str(args.iters), "--warmup",
+            str(args.warmup), "--seed", str(args.seed)]
+    if args.out:
+        argv += ["--out", args.out]
+    mod.main(argv)
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--kernels", action="store_true", help="single-GPU codec kernel throughput")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"],
+                    help="reference: the unmodified reference hook (its eden_utils kernels and NCCL point-to-point "
+                         "butterfly) on the same tensors, through baseline/reference_allreduce.py")
+    ap.add_argument("--methods", default="dynamiQ_aee_5bit", help="--impl reference: comma list of its method names")
     ap.add_argument("--numel", type=int, default=1 << 26)
     ap.add_argument("--sizes-mb", default="1,4,16,64,256")
     ap.add_argument("--bits", default="4,5,8")
@@ -324,7 +349,9 @@ def main(argv=None) -> None:
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--out", default=None)
     args = ap.parse_args(argv)
-    if args.kernels:
+    if args.impl == "reference":
+        run_reference(args)
+    elif args.kernels:
         run_kernels(args)
     else:
         run_collectives(args)

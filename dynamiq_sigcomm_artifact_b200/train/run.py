@@ -94,7 +94,22 @@ def build_parser(task: str, default_model: str, default_seq: int, default_batch:
 
 
 def main(task: str, argv=None, default_model: str = "gpt2-small", default_seq: int = 1024, default_batch: int = 8):
+    """Parse, train, and leave ``rank_<r>.exitcode`` (0, or 1 after an exception, which is re-raised) in the
+    output directory: the launcher collects one per rank, since the process launcher reports a single code."""
     args = build_parser(task, default_model, default_seq, default_batch).parse_args(argv)
+    code = 1
+    try:
+        loss = _run(task, args)
+        code = 0
+        return loss
+    finally:
+        if args.output_dir:
+            os.makedirs(args.output_dir, exist_ok=True)
+            with open(os.path.join(args.output_dir, f"rank_{os.environ.get('RANK', '0')}.exitcode"), "w") as f:
+                f.write(f"{code}\n")
+
+
+def _run(task: str, args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     use_cuda = torch.cuda.is_available()
     if world > 1:

@@ -21,6 +21,37 @@ def test_launcher_dry_run_expands_matrix(capsys):
     assert run_matrix.DEFAULT_METHODS.split(",")[5] == "dynamiQ_aee_5bit"
 
 
+def test_launcher_runs_a_combination_and_leaves_its_logs(tmp_path):
+    """Two gloo ranks, three steps of the tiny model, under a stand-in for the system profiler that records
+    its arguments and runs the command it was given."""
+    fake = tmp_path / "nsys"
+    fake.write_text("#!/bin/bash\necho \"$@\" > %s\nwhile [ \"$1\" != \"%s\" ]; do shift; done\nexec \"$@\"\n"
+                    % (tmp_path / "nsys_args.txt", os.sys.executable))
+    fake.chmod(0o755)
+    root = tmp_path / "matrix"
+    env_before = os.environ.get("CUDA_VISIBLE_DEVICES")
+    os.environ["CUDA_VISIBLE_DEVICES"] = ""
+    try:
+        rc = run_matrix.main(["--gpus", "2", "--tasks", "causal:gpt2-tiny", "--aggregation-methods", "dynamiQ_aee_5bit",
+                              "--max-train-steps", "3", "--output-root", str(root), "--nsys-profile-step", "1",
+                              "--nsys-bin", str(fake), "--base-port", "23450"])
+    finally:
+        if env_before is None:
+            os.environ.pop("CUDA_VISIBLE_DEVICES")
+        else:
+            os.environ["CUDA_VISIBLE_DEVICES"] = env_before
+    out = root / "causal_gpt2-tiny" / "dynamiQ_aee_5bit_direct"
+    assert rc == 0, (out / "launcher.err").read_text()[-2000:]
+    meta = (root / "metadata.log").read_text()
+    assert "host=" in meta and "torch=" in meta and "methods=dynamiQ_aee_5bit_direct" in meta and f"nsys_binary={fake}" in meta
+    assert (out / "status").read_text().splitlines() == ["exitcode 0", "rank 0 0", "rank 1 0"]
+    assert "aggregation_method=dynamiQ_aee_5bit_direct" in (out / "command.log").read_text()
+    nsys_args = (tmp_path / "nsys_args.txt").read_text()
+    assert "--capture-range=cudaProfilerApi" in nsys_args and "--capture-range-end=stop" in nsys_args
+    assert "--trace=cuda,nvtx,osrt" in nsys_args and "--nsys_profile_step 1" in nsys_args
+    assert (out / "ranks").is_dir() and any((out / "ranks").rglob("stdout.log"))
+
+
 def test_lr_rule_and_bandwidth_definitions():
     assert abs(train_run.default_lr("causal", 8) - 1e-5 * 2.0) < 1e-12
     assert abs(train_run.default_lr("causal", 2) - 1e-5 * (4 ** 0.4)) < 1e-12
