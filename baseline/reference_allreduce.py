@@ -109,14 +109,16 @@ def main(argv=None) -> None:
             dist._DEFAULT_FIRST_BUCKET_BYTES = 8000 * 1024 * 1024
             net = DDP(OneTensor(n), device_ids=[local], bucket_cap_mb=8000)
             net.register_comm_hook([state], hook)
-            x = synth(n, rank, args.seed, dev).bfloat16()
-            exact = x.double()
+            x0 = synth(n, rank, args.seed, dev).bfloat16()
+            exact = x0.double()
             dist.all_reduce(exact)
             exact /= world
+            x = torch.empty_like(x0)
             times = []
             for it in range(args.warmup + args.iters):
                 state["batch_idx"] = it
                 net.module.w.grad = None
+                x.copy_(x0)  # autograd may adopt the handed-over tensor as .grad, which the hook then overwrites
                 dist.barrier()
                 torch.cuda.synchronize()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

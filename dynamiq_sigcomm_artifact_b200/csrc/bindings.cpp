@@ -14,6 +14,7 @@ void symm_close(int64_t ptr);
 void symm_free(int64_t ptr);
 at::Tensor wrap_ptr(int64_t ptr, int64_t bytes, int64_t device);
 
+void set_debug(bool on);
 void fused_allreduce(at::Tensor bucket, at::Tensor steps, std::vector<int64_t> mail_ptrs,
                      std::vector<int64_t> flag_ptrs, int64_t mailbox_bytes, int64_t flag_words, int64_t nslots,
                      int64_t status_ptr, int64_t tail_ws_ptr, int64_t rank, int64_t world, int64_t bits, int64_t ctas,
@@ -99,6 +100,7 @@ TORCH_LIBRARY(dq, m) {
   m.def("symm_close(int ptr) -> ()", &dq::symm_close);
   m.def("symm_free(int ptr) -> ()", &dq::symm_free);
   m.def("wrap_ptr(int ptr, int bytes, int device) -> Tensor", &dq::wrap_ptr);
+  m.def("set_debug(bool on) -> ()", &dq::set_debug);
   m.def(
       "fused_allreduce(Tensor(a!) bucket, Tensor steps, int[] mail_ptrs, int[] flag_ptrs, int mailbox_bytes, "
       "int flag_words, int nslots, int status_ptr, int tail_ws_ptr, int rank, int world, int bits, int ctas, "

@@ -1,3 +1,4 @@
+#include <atomic>
 // Persistent compressed all-reduce over peer-mapped NVLink memory (sm_100a).
 //
 // One cooperative launch per bucket performs the whole collective: rotation, scaling,
@@ -142,6 +143,10 @@ static void fill_sc(ARParams& p, int64_t codec, int64_t bits, double lattice_max
   }
 }
 
+// Process-wide switch of the kernels' debug mode (ARParams::debug), set from Python (`set_debug`).
+static std::atomic<int> g_debug{0};
+void set_debug(bool on) { g_debug.store(on ? 1 : 0); }
+
 static void fill_common(ARParams& p, const at::Tensor& bucket, const at::Tensor& steps, int64_t rank, int64_t world,
                         int64_t blocks_per_shard, int64_t slot_stride, int64_t scales_off, int64_t flag_base,
                         int64_t epoch, int64_t seed, int64_t step, int64_t bucket_id, double post_scale,
@@ -175,14 +180,17 @@ static void fill_common(ARParams& p, const at::Tensor& bucket, const at::Tensor&
   p.status = reinterpret_cast<uint32_t*>(status_ptr);
   p.tail_ws = reinterpret_cast<float*>(tail_ws_ptr);
   p.no_transmit = no_transmit ? 1 : 0;
+  p.debug = g_debug.load();
   const int* sp = steps.data_ptr<int>();
   for (int s = 0; s < p.nsteps; ++s)
     for (int k = 0; k < kStepInts; ++k) p.steps[s][k] = sp[s * kStepInts + k];
 }
 
-static void check_layout(const ARParams& p, int bits, int64_t mailbox_bytes, int64_t nslots, int64_t flag_words,
+static void check_layout(ARParams& p, int bits, int64_t mailbox_bytes, int64_t nslots, int64_t flag_words,
                          int ctas) {
   (void)bits;
+  p.nslots = static_cast<int>(nslots);
+  p.set_bytes = static_cast<unsigned long long>(mailbox_bytes);
   const unsigned long long need = static_cast<unsigned long long>(p.blocks_per_shard) * p.block_bytes;
   const bool has_scales = p.codec == kCodecRht || p.codec == kCodecRhtTc || p.codec == kCodecRhtMix;  // fp32 scales after the codes
   TORCH_CHECK(p.scales_off >= need && (p.scales_off % 16) == 0, "scales overlap the codes of a slot");

@@ -19,7 +19,10 @@ enum : int {
 };
 
 // error codes left in status[0]; status[1] = (step << 16) | cta, status[2] = slot
-enum : uint32_t { kOk = 0, kErrWaitTimeout = 1, kErrBadProgram = 2, kErrCopyTimeout = 3, kErrMmaTimeout = 4 };
+enum : uint32_t {
+  kOk = 0, kErrWaitTimeout = 1, kErrBadProgram = 2, kErrCopyTimeout = 3, kErrMmaTimeout = 4,
+  kErrBounds = 5  // debug mode: a slot index or a block's offset inside a slot left its region; the step is not run
+};
 
 struct ARParams {
   void* bucket;        // this rank's gradient bucket: input, scratch for partial sums, and output
@@ -51,6 +54,9 @@ struct ARParams {
   const uint32_t* sc_plan;         // mixed widths: [nblocks + 1] message offsets of the blocks in 8-byte units (a prefix
                                    // sum), then [nblocks] packed widths (byte j = width of superchunk j of the block);
                                    // kCodecRhtMix: offsets in 128-byte units, then one width (2..8) per block
+  int debug;                       // 1 (DQ_DEBUG=1 / debug=True): before a step touches a mailbox every CTA checks the
+  int nslots;                      // step's slot indices against nslots, and the offset and length of every block of
+  unsigned long long set_bytes;    // its range against the slot (plan-driven codecs: offsets come from device memory)
   int steps[kMaxSteps][kStepInts];
 };
 

@@ -113,6 +113,17 @@ __device__ __forceinline__ void fused_simt_body(const ARParams& p) {
     step_range(p, s, cta, per_cta, shard_lo, lo, hi);
     if (hi <= lo) continue;  // producer and consumer agree on empty ranges: no flag traffic
 
+    if (p.debug) {  // CTA-uniform: a step with an access outside its slots is not run at all
+      int bad_slot;
+      constexpr int kPlanUnit = (CODEC == kCodecScMixAee || CODEC == kCodecScMixMee) ? 8 : (CODEC == kCodecRhtMix ? 128 : 0);
+      const bool bad = debug_step_out_of_bounds<kPlanUnit, !SC>(p, s, shard_lo, lo, hi, bad_slot);
+      if (__syncthreads_or(bad)) {
+        if (bad) fail(kErrBounds, s, bad_slot);
+        aborted = true;
+        break;
+      }
+    }
+
     if (nrecv > 0) {
       bool timed_out = false;
       int bad_slot = 0;

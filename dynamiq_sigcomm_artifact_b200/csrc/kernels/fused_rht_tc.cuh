@@ -381,6 +381,16 @@ __device__ __forceinline__ void rht_tc_body(const ARParams& p) {
     const int lo = range.x, hi = range.y, shard_lo = range.z;
     if (hi <= lo) continue;  // producer and consumer agree on empty ranges: no flag traffic
 
+    if (p.debug) {  // CTA-uniform: a step with an access outside its slots is not run at all
+      int bad_slot;
+      const bool bad = debug_step_out_of_bounds<0, true>(p, s, shard_lo, lo, hi, bad_slot);
+      if (__syncthreads_or(bad)) {
+        if (bad) report_failure(p, kErrBounds, s, bad_slot);
+        aborted = true;
+        break;
+      }
+    }
+
     if (nrecv > 0) {
       bool timed_out = false;
       int bad_slot = 0;

@@ -69,4 +69,39 @@ __device__ __forceinline__ void report_failure(const ARParams& p, uint32_t code,
   }
 }
 
+// Debug mode: true if this thread found a slot index of step s outside the set, or a block of the CTA's range
+// [lo, hi) whose encoded bytes would leave its slot.  Fixed-width codecs: block i of the shard sits at
+// i * block_bytes.  Plan-driven codecs (PLAN_UNIT = 8: superchunk records of mixed width, 128: rotation codes
+// of mixed width) read offsets from device memory, which no host-side check sees.  Threads stride the range.
+template <int PLAN_UNIT, bool HAS_SCALES>
+__device__ __forceinline__ bool debug_step_out_of_bounds(const ARParams& p, int s, int shard_lo, int lo, int hi,
+                                                         int& bad_slot) {
+  const int recv_slot = p.steps[s][2], nrecv = p.steps[s][3], out = p.steps[s][4], send_slot = p.steps[s][6];
+  bool bad = false;
+  bad_slot = -1;
+  if (nrecv > 0 && (recv_slot < 0 || recv_slot + nrecv > p.nslots)) bad = true, bad_slot = recv_slot;
+  if ((out == kOutSend || out == kOutFinal) && (send_slot < 0 || send_slot >= p.nslots)) bad = true, bad_slot = send_slot;
+  if (static_cast<unsigned long long>(p.nslots) * p.slot_stride > p.set_bytes) bad = true;
+  const unsigned long long payload_end = HAS_SCALES ? p.scales_off : p.slot_stride;
+  for (int blk = lo + static_cast<int>(threadIdx.x); blk < hi && !bad; blk += static_cast<int>(blockDim.x)) {
+    unsigned long long off, bytes;
+    if constexpr (PLAN_UNIT > 0) {
+      const uint32_t base = __ldg(p.sc_plan + shard_lo), o0 = __ldg(p.sc_plan + blk), o1 = __ldg(p.sc_plan + blk + 1);
+      if (o0 < base || o1 < o0) bad = true;
+      off = static_cast<unsigned long long>(o0 - base) * PLAN_UNIT;
+      bytes = static_cast<unsigned long long>(o1 - o0) * PLAN_UNIT;
+      if constexpr (PLAN_UNIT == 128) {  // one width (2..8) per block, 128 bytes per bit of width
+        const uint32_t wb = __ldg(p.sc_plan + p.nblocks + 1 + blk);
+        if (wb < 2u || wb > 8u || o1 - o0 != wb) bad = true;
+      }
+    } else {
+      off = static_cast<unsigned long long>(blk - shard_lo) * p.block_bytes;
+      bytes = p.block_bytes;
+    }
+    if (off + bytes > payload_end) bad = true;
+    if (HAS_SCALES && p.scales_off + 4ull * static_cast<unsigned long long>(blk - shard_lo + 1) > p.slot_stride) bad = true;
+  }
+  return bad;
+}
+
 }  // namespace dq

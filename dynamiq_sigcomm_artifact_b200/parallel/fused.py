@@ -159,7 +159,8 @@ def mix_table(lattice: str, device) -> torch.Tensor:
 
 STATUS_MESSAGES = {1: "timed out waiting for a peer's flag", 2: "malformed step program",
                    3: "a bulk copy into shared memory did not complete",
-                   4: "a tensor-core pass did not signal completion"}
+                   4: "a tensor-core pass did not signal completion",
+                   5: "debug mode: a slot index or a block's offset left its slot; the step was not run"}
 
 
 def decode_status(words: Sequence[int]) -> Optional[str]:
@@ -187,9 +188,15 @@ class FusedAllreduce:
 
         `debug`: every region of the symmetric buffer that peers write into (the two slot sets, the flag
         array) is fenced by 256-byte guard zones filled with a pattern; ``check()`` reads them back and
-        raises :class:`MailboxOverrun` if a store landed outside its region.  With compute-sanitizer not
+        raises :class:`MailboxOverrun` if a store landed outside its region; and the kernels run in debug
+        mode (process-wide switch): before a step touches a mailbox, every CTA checks the step's slot indices
+        and the offset and length of every block of its range against the slot - for the plan-driven codecs
+        those come from device memory, where no host-side check sees them - and a violation ends the
+        collective with a status (``CollectiveTimeout`` names it) instead of a stray store.  With compute-sanitizer not
         available on every machine, this and the byte-exact oracle comparisons are the overrun net."""
         self.debug = bool(debug)
+        if self.debug:
+            _ops.require().set_debug(True)
         self.ops = _ops.require()
         self.group = group
         self.world = dist.get_world_size(group)
@@ -329,14 +336,21 @@ class FusedAllreduce:
         if self.buf is not None:
             self.buf.close()
             self.buf = None
+        if self.debug:
+            self.ops.set_debug(False)
+            self.debug = False
 
 
 class LocalCluster:
     """All ranks of a collective on one GPU, one cooperative launch (blockIdx.y = rank)."""
 
     def __init__(self, world: int, max_numel: int, ctas: int = 8, threads: int = 256, device="cuda",
-                 timeout_ms: int = 1000, rotation: str = "simt", prefetch: bool = True):
+                 timeout_ms: int = 1000, rotation: str = "simt", prefetch: bool = True, debug: Optional[bool] = None):
+        """`debug`: True / False switches the kernels' bounds-checking mode on / off for the whole process
+        (None leaves it as it is)."""
         self.ops = _ops.require()
+        if debug is not None:
+            self.ops.set_debug(bool(debug))
         self.prefetch = bool(prefetch)
         self.tensor_rotation = _rotation_flag(rotation)
         self.world, self.ctas, self.threads = world, ctas, threads

@@ -305,10 +305,22 @@ def run_kernels(args) -> None:
 
 def run_reference(args) -> None:
     """The reference arm lives beside the checkout's baseline/ folder, outside the package, and imports
-    nothing of it; it prints its own rows (or one ``unavailable`` line)."""
+    nothing of it; it prints its own rows (or one ``unavailable`` line).  With ``--kernels`` it is the reference's
+    own kernel benchmark, run unmodified (cuda_kernels/tests/benchmark_scaling_quantization.py: 2^28 bf16
+    elements, compress / decompress / decompress+compress of its hierarchical codec at 2, 4 and 8 bits)."""
     import importlib.util
 
     root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    if args.kernels:
+        import runpy
+
+        path = os.path.join(root, "baseline", "_ref", "tests", "benchmark_scaling_quantization.py")
+        if not os.path.isfile(path):
+            print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/tests/benchmark_scaling_quantization.py "
+                              "is missing: run baseline/install_reference.sh <path of the reference checkout>"}))
+            return
+        runpy.run_path(path, run_name="__main__")
+        return
     path = os.path.join(root, "baseline", "reference_allreduce.py")
     if not os.path.isfile(path):
         if int(os.environ.get("RANK", "0")) == 0:

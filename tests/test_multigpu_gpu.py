@@ -1,5 +1,6 @@
-"""Launches the multi-process oracle check (tests/multigpu/check_collective.py) when the machine has
-at least two GPUs; skipped on a single-GPU machine."""
+"""Launches the multi-process checks under tests/multigpu/ (collective against the simulator, in-switch
+all-reduce, the two reducers of the trainer) when the machine has at least two GPUs; skipped on a
+single-GPU machine."""
 import json
 import os
 import socket
@@ -51,3 +52,16 @@ def test_in_switch_allreduce_matches_the_exact_mean():
     if not summary["available"]:
         pytest.skip("no NVLink multicast on this machine: " + summary["reason"])
     assert summary["cases"] == 36
+
+
+def test_flat_and_ddp_reducers_train_alike():
+    ngpu = torch.cuda.device_count()
+    if ngpu < 2:
+        pytest.skip("needs at least two GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+           os.path.join(ROOT, "tests", "multigpu", "check_trainers.py")]
+    res = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    line = [ln for ln in res.stdout.splitlines() if ln.startswith("{")][-1]
+    assert json.loads(line)["cases"] == 2

@@ -119,3 +119,24 @@ def test_flat_reducer_over_gloo_keeps_ranks_identical(method):
     assert all(r[2] for r in res), "parameters diverged between ranks"
     assert all(r[3] > 1 for r in res)
     assert all(all(l == l and l < 12 for l in r[1]) for r in res)
+
+
+def test_flat_and_ddp_reducers_train_alike_on_gloo_ranks():
+    """The multi-process comparison of the two reducers (tests/multigpu/check_trainers.py) on two CPU ranks."""
+    import json
+    import os
+    import socket
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(root, "tests", "multigpu", "check_trainers.py")]
+    res = subprocess.run(cmd, cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    line = [ln for ln in res.stdout.splitlines() if ln.startswith("{")][-1]
+    assert json.loads(line)["cases"] == 2

@@ -84,3 +84,40 @@ def test_flat_bucket_quacks_like_a_grad_bucket():
     assert torch.equal(buf, torch.ones(6))
     b.set_buffer(buf)  # the same storage: nothing to copy
     assert torch.equal(p.grad, torch.ones(6))
+
+
+def test_level_solver_reproduces_the_published_optima():
+    """Errors and positions of the reference's result files (simulations_llm/compression/
+    optimal_INCA_2_X_bits_invp_1024.txt and optimal_INCA_5_X_bits_invp_1024_n16.txt), read as text."""
+    golden2 = {3: (0.8130913915224226, [1, 3]), 4: (0.6293661377218382, [1, 4]), 9: (0.6267778470922883, [2, 9])}
+    for g, (err, pos) in golden2.items():
+        e, p = thc_tables.solve_levels(2, g)
+        assert abs(e - err) < 1e-12 and p == pos, (g, e, p)
+    e, p = thc_tables.solve_levels(5, 16)
+    assert abs(e - 0.0071314959952194935) < 1e-12 and p == list(range(15)) + [16]
+    e, p = thc_tables.solve_levels(5, 2)
+    assert abs(e - 0.45248911821625015) < 1e-12 and p[-2:] == [1, 2] and set(p[:-2]) == {0}
+    assert abs(thc_tables.solve_levels(2, 1)[0] - 1.6317562270095627) < 1e-12
+    # a finer grid never hurts, and the optimum beats the uniform grid of the same size
+    errs = [thc_tables.solve_levels(4, g)[0] for g in (8, 12, 21, 40)]
+    assert all(a >= b - 1e-15 for a, b in zip(errs, errs[1:]))
+    uniform = sum(thc_tables.interval_cost(-thc_tables.THC_T + i * 2 * thc_tables.THC_T / 15,
+                                           -thc_tables.THC_T + (i + 1) * 2 * thc_tables.THC_T / 15) for i in range(15))
+    assert errs[-1] < uniform
+
+
+def test_sender_and_receiver_tables_are_unbiased_and_summable():
+    g, bits = 21, 4
+    _, pos = thc_tables.solve_levels(bits, g)
+    recv = thc_tables.receiver_table(pos, g)
+    levels = thc_tables.level_values(pos, g)
+    assert recv[0] == 0 and recv[-1] == 2 * g and recv == sorted(recv) and len(recv) == 1 << bits
+    lower, prob = thc_tables.sender_table(pos, g, 1001)
+    T = thc_tables.THC_T
+    for q in (0, 137, 500, 730, 1000):  # E[decoded] equals the fine-grid input
+        x = -T + 2 * T * q / 1000
+        k, p = lower[q], prob[q]
+        assert abs((1 - p) * levels[k] + p * levels[k + 1] - x) < 1e-12
+    # integer sums decode linearly: two senders' table values
+    a, b = recv[3], recv[12]
+    assert abs(((a + b) - 2 * g) * T / g - (levels[3] + levels[12])) < 1e-12
