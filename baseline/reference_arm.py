@@ -157,8 +157,15 @@ def run_reference(args, models) -> None:
         torch.cuda.synchronize()
 
     warm = max(args.warmup, 3)
-    for i in range(warm):
-        float(step(host[i % 4].to(dev, non_blocking=True)).item())
+    try:
+        for i in range(warm):
+            float(step(host[i % 4].to(dev, non_blocking=True)).item())
+    except RuntimeError as e:
+        # an exception raised by the reference's own code on this configuration (every rank raises the same one,
+        # on the host, inside the hook): reported instead of a number
+        why = str(e).strip().splitlines()
+        _unavailable(f"the reference's {method} hook raised on {args.model} at {world} GPUs: " + " | ".join(why[:2])[:300])
+        return
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()

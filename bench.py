@@ -51,7 +51,9 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--reducer", default="flat", choices=["flat", "ddp"])
     ap.add_argument("--comm-prefetch", type=int, default=1, help="0: collective kernel without its staging buffer")
     ap.add_argument("--sparse-embedding", type=int, default=-1, help="-1: automatic, 0 / 1: force off / on")
-    ap.add_argument("--bucket-cap-mb", type=int, default=0, help="0: 25 MB (GPT-2, BERT) or 100 MB (Llama 1.2B)")
+    ap.add_argument("--bucket-cap-mb", type=int, default=0,
+                    help="0: one bucket for the whole model (4000 MB cap, the reference's setting for DynamiQ); the "
+                         "fp32 library arm always uses 25 MB buckets")
     ap.add_argument("--rotation", default="simt", choices=["simt", "tc"])
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the collective self-check and the same-engine fp32 comparison after the timed regions")
@@ -114,6 +116,7 @@ def same_engine_fp32(args, cfg_kwargs: dict, steps: int, warmup: int):
 
     kw = dict(cfg_kwargs)
     kw["method"] = "fp32"
+    kw["bucket_cap_mb"] = 0  # automatic: 25 MB buckets, under which the library all-reduce overlaps backward best
     tr = Trainer(TrainConfig(**kw))
     batches = [tr.synthetic_batch(pinned=True).to(tr.device) for _ in range(4)]
     for i in range(max(warmup, 3)):
@@ -132,7 +135,7 @@ def same_engine_fp32(args, cfg_kwargs: dict, steps: int, warmup: int):
     tokens = tr.tokens_per_step() * steps
     tr.close()
     return {"value": tokens / (float(t[0]) / 1e3), "unit": "tokens/s", "ms_per_step": float(t[0]) / steps,
-            "method": "fp32 (library all-reduce through the same reducer and optimizer)"}
+            "method": "fp32 (library all-reduce through the same reducer and optimizer, 25 MB buckets)"}
 
 
 def main() -> None:
@@ -163,7 +166,9 @@ def main() -> None:
 
     mb, seq, task, desc = MODELS[args.model]
     if args.bucket_cap_mb <= 0:
-        args.bucket_cap_mb = 100 if args.model == "llama-1.2b" else 25
+        from dynamiq_sigcomm_artifact_b200.train.engine import default_bucket_cap_mb
+
+        args.bucket_cap_mb = default_bucket_cap_mb(args.method, world, args.model)
     os.environ.setdefault("DQ_ROTATION", args.rotation)
     cfg_kwargs = dict(model=args.model, method=args.method, micro_batch=mb, seq_len=seq, task=task,
                       bucket_cap_mb=args.bucket_cap_mb, topology=args.topology, comm_ctas=args.comm_ctas,

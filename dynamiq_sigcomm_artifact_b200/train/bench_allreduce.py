@@ -213,6 +213,33 @@ def run_collectives(args) -> None:
                 record(f"fused_{topo}_{bits}bit" + ("_tc" if args.rotation == "tc" else ""), ms, wire, nmse_vs(exact, work),
                        {"roofline_ms": max(t_link, t_hbm), "roofline_fraction": max(t_link, t_hbm) / ms,
                         "bound": "nvlink" if t_link > t_hbm else "hbm", "link_gbs": link_gbs, "link": link_kind})
+        # whole communication hooks by method name on the same tensor (the counterpart of the reference arm's rows):
+        # what a training step pays per bucket, statistics passes and width policies included
+        for method in [m for m in args.hook_methods.split(",") if m]:
+            from .. import hooks as _hooks
+            from ..config import DynamiqConfig
+            from ..parallel.reducer import FlatBucket
+
+            dcfg = DynamiqConfig.from_env(method=method, seed=args.seed, comm_ctas=args.ctas, comm_threads=args.threads,
+                                          tail_ctas=args.ctas)
+            state = _hooks.build_comm_state(dcfg)[0]
+            hook = _hooks.select_comm_hook(method, dcfg.topology)
+            _hooks.note_bucket(state, work)
+            bucket = FlatBucket(0, work, [], True)
+            step = [dcfg.warmup_steps]
+
+            def run_hook():
+                state.begin_step(step[0])  # past the library-served warm-up steps from the first call on
+                step[0] += 1
+                hook([state], bucket).wait()
+
+            ms = time_op(run_hook, lambda: work.copy_(base), args.iters, max(args.warmup, 3))
+            if state["engine"] is not None:
+                state["engine"].check()
+            spec = state["spec"]
+            record(f"hook_{method}", ms, float(state["stats"].get("wire_bytes", 0)) / max(state["stats"].get("collectives", 1), 1),
+                   nmse_vs(exact, work), {"family": spec.family, "hook": spec.hook, "topology": spec.topology})
+            state.close()
     if rank == 0 and args.out:
         with open(args.out, "w") as f:
             json.dump(rows, f, indent=1)
@@ -358,6 +385,9 @@ def main(argv=None) -> None:
     ap.add_argument("--no-nvls", action="store_true", help="skip the in-switch (NVLS) rows")
     ap.add_argument("--peer-copy", action="store_true",
                     help="measure the peer-copy bandwidth first and use it as the link figure of the roofline fractions")
+    ap.add_argument("--hook-methods", default="",
+                    help="comma list of aggregation_method names: also time the whole communication hook of each on the "
+                         "same tensors (rows hook_<method>)")
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--out", default=None)
     args = ap.parse_args(argv)

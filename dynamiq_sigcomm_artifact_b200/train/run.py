@@ -78,7 +78,7 @@ def build_parser(task: str, default_model: str, default_seq: int, default_batch:
     ap.add_argument("--max_train_steps", type=int, default=MEASURE_END_STEP + 1)
     ap.add_argument("--measure_start_step", type=int, default=MEASURE_START_STEP)
     ap.add_argument("--measure_end_step", type=int, default=MEASURE_END_STEP)
-    ap.add_argument("--bucket_cap_mb", type=int, default=25)
+    ap.add_argument("--bucket_cap_mb", type=int, default=0, help="0: one bucket for the package's own collectives, 25 MB for the library all-reduce")
     ap.add_argument("--comm_ctas", type=int, default=64)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--output_dir", default=None)
