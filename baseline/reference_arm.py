@@ -160,25 +160,25 @@ def run_reference(args, models) -> None:
     try:
         for i in range(warm):
             float(step(host[i % 4].to(dev, non_blocking=True)).item())
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            step(devb[i % 4])
+        e1.record()
+        barrier()
+        ms_dev = e0.elapsed_time(e1)
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            last = float(step(host[i % 4].to(dev, non_blocking=True)).item())
+        barrier()
+        ms_e2e = (time.perf_counter() - t0) * 1e3
     except RuntimeError as e:
         # an exception raised by the reference's own code on this configuration (every rank raises the same one,
         # on the host, inside the hook): reported instead of a number
-        why = str(e).strip().splitlines()
+        why = [ln.strip() for ln in str(e).strip().splitlines() if ln.strip()]
         _unavailable(f"the reference's {method} hook raised on {args.model} at {world} GPUs: " + " | ".join(why[:2])[:300])
         return
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        step(devb[i % 4])
-    e1.record()
-    barrier()
-    ms_dev = e0.elapsed_time(e1)
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        last = float(step(host[i % 4].to(dev, non_blocking=True)).item())
-    barrier()
-    ms_e2e = (time.perf_counter() - t0) * 1e3
     t = torch.tensor([ms_dev, ms_e2e], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -207,25 +207,36 @@ __device__ long long block_sum(long long v, long long* scratch) {
   return t;
 }
 
-__global__ void __launch_bounds__(1024, 1) rht_widths_update_kernel(const uint8_t* __restrict__ mail, int* __restrict__ plan,
-                                                                   int nblocks, int blocks_per_shard,
-                                                                   long long slot_stride, long long scales_off,
-                                                                   int first_ag_slot, long long budget) {
-  __shared__ int hist[kLogBins];
-  __shared__ long long scratch[32];
-  __shared__ int prefix[1024];
-  const int tid = threadIdx.x, nt = blockDim.x;
-  int* widths = plan + nblocks + 1;
-  auto log_of = [&](int k) {
+// The update runs as four small launches so that every pass over the blocks is spread over the whole GPU (a bucket
+// of 1.2 G elements has 1.2 M blocks): (1) quantised log2 of every block's absmax + histogram, (2) bisection on the
+// histogram for the offset c (one CTA), (3) new widths and their prefix sum inside tiles of 1024 blocks, (4) tile
+// bases added.  Scratch (int32): [kLogBins histogram][1 offset][ntiles tile totals][nblocks logs].
+
+__global__ void __launch_bounds__(256) rht_log_hist_kernel(const uint8_t* __restrict__ mail, const int* __restrict__ plan,
+                                                           int nblocks, int blocks_per_shard, long long slot_stride,
+                                                           long long scales_off, int first_ag_slot,
+                                                           int* __restrict__ hist, int* __restrict__ logs) {
+  __shared__ int local[kLogBins];
+  const int* widths = plan + nblocks + 1;
+  for (int i = threadIdx.x; i < kLogBins; i += blockDim.x) local[i] = 0;
+  __syncthreads();
+  for (int k = blockIdx.x * blockDim.x + threadIdx.x; k < nblocks; k += gridDim.x * blockDim.x) {
     const int shard = k / blocks_per_shard, bs = k - shard * blocks_per_shard;
     const float scale = *reinterpret_cast<const float*>(mail + (first_ag_slot + shard) * slot_stride + scales_off + 4ll * bs);
     const int wprev = max(2, min(8, widths[k]));
-    return quantised_log2(__fmul_rn(scale, static_cast<float>((1 << (wprev - 1)) - 1)));
-  };
-  for (int i = tid; i < kLogBins; i += nt) hist[i] = 0;
+    const int lq = quantised_log2(__fmul_rn(scale, static_cast<float>((1 << (wprev - 1)) - 1)));
+    logs[k] = lq;
+    atomicAdd(&local[lq + kLogBias], 1);
+  }
   __syncthreads();
-  for (int k = tid; k < nblocks; k += nt) atomicAdd(&hist[log_of(k) + kLogBias], 1);
-  __syncthreads();
+  for (int i = threadIdx.x; i < kLogBins; i += blockDim.x)
+    if (local[i] != 0) atomicAdd(&hist[i], local[i]);
+}
+
+__global__ void __launch_bounds__(1024, 1) rht_offset_kernel(const int* __restrict__ hist, long long budget,
+                                                             int* __restrict__ offset) {
+  __shared__ long long scratch[32];
+  const int tid = threadIdx.x, nt = blockDim.x;
   auto total_at = [&](int c8) {
     long long v = 0;
     for (int b = tid; b < kLogBins; b += nt) v += static_cast<long long>(hist[b]) * rht_width_at(b - kLogBias, c8);
@@ -240,27 +251,53 @@ __global__ void __launch_bounds__(1024, 1) rht_widths_update_kernel(const uint8_
       if (total_at(m) <= budget) lo = m; else hi = m;
     }
   }
-  // widths and their exclusive prefix sum: thread t owns a contiguous run of blocks
-  const int chunk = (nblocks + nt - 1) / nt;
-  const int k0 = min(tid * chunk, nblocks), k1 = min(k0 + chunk, nblocks);
-  int mine = 0;
-  for (int k = k0; k < k1; ++k) mine += rht_width_at(log_of(k), lo);
-  prefix[tid] = mine;
+  if (tid == 0) *offset = lo;
+}
+
+// tile = 1024 consecutive blocks, one per thread: new width, exclusive prefix inside the tile, tile total
+__global__ void __launch_bounds__(1024, 1) rht_widths_tiles_kernel(const int* __restrict__ logs, const int* __restrict__ offset,
+                                                                   int nblocks, int* __restrict__ plan,
+                                                                   int* __restrict__ tile_totals) {
+  __shared__ int warp_sums[32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int k = blockIdx.x * 1024 + tid;
+  int* widths = plan + nblocks + 1;
+  const int w = k < nblocks ? rht_width_at(logs[k], *offset) : 0;
+  int incl = w;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+    if (lane >= o) incl += up;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
   __syncthreads();
-  for (int o = 1; o < nt; o <<= 1) {  // Hillis-Steele inclusive scan
-    const int add = tid >= o ? prefix[tid - o] : 0;
-    __syncthreads();
-    prefix[tid] += add;
-    __syncthreads();
+  if (warp == 0) {
+    int v = warp_sums[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xFFFFFFFFu, v, o);
+      if (lane >= o) v += up;
+    }
+    warp_sums[lane] = v;  // inclusive over warps
   }
-  int run = prefix[tid] - mine;
-  for (int k = k0; k < k1; ++k) {
-    const int wnew = rht_width_at(log_of(k), lo);  // reads the previous width of block k, then replaces it
-    plan[k] = run;
-    run += wnew;
-    widths[k] = wnew;
+  __syncthreads();
+  const int before = (warp > 0 ? warp_sums[warp - 1] : 0) + incl - w;
+  if (k < nblocks) {
+    plan[k] = before;  // offset inside the tile; the tile's base is added by the next launch
+    widths[k] = w;
   }
-  if (tid == nt - 1) plan[nblocks] = prefix[nt - 1];
+  if (tid == 1023) tile_totals[blockIdx.x] = warp_sums[31];
+}
+
+__global__ void __launch_bounds__(1024, 1) rht_add_tile_base_kernel(const int* __restrict__ tile_totals, int nblocks,
+                                                                    int* __restrict__ plan) {
+  __shared__ long long scratch[32];
+  long long mine = 0;
+  for (int t = threadIdx.x; t < static_cast<int>(blockIdx.x); t += blockDim.x) mine += tile_totals[t];
+  const int base = static_cast<int>(block_sum(mine, scratch));
+  const int k = blockIdx.x * 1024 + threadIdx.x;
+  if (k < nblocks) plan[k] += base;
+  if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) plan[nblocks] = base + tile_totals[blockIdx.x];
 }
 
 }  // namespace
@@ -279,9 +316,23 @@ void rht_widths_update(at::Tensor mailbox, at::Tensor plan, int64_t nblocks, int
               "the all-gather slots lie outside the mailbox");
   TORCH_CHECK(scales_off % 4 == 0 && slot_stride % 4 == 0, "misaligned scales");
   c10::cuda::CUDAGuard guard(plan.device());
-  rht_widths_update_kernel<<<1, 1024, 0, at::cuda::getCurrentCUDAStream()>>>(
-      mailbox.data_ptr<uint8_t>(), plan.data_ptr<int>(), static_cast<int>(nblocks), static_cast<int>(blocks_per_shard),
-      slot_stride, scales_off, static_cast<int>(first_ag_slot), budget);
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+  const int nb = static_cast<int>(nblocks), ntiles = (nb + 1023) / 1024;
+  at::Tensor scratch = at::zeros({kLogBins + 1 + ntiles + nblocks}, plan.options());
+  int* hist = scratch.data_ptr<int>();
+  int* offset = hist + kLogBins;
+  int* tile_totals = offset + 1;
+  int* logs = tile_totals + ntiles;
+  const int grid = std::min((nb + 255) / 256, 148 * 4);
+  rht_log_hist_kernel<<<grid, 256, 0, stream>>>(mailbox.data_ptr<uint8_t>(), plan.data_ptr<int>(), nb,
+                                                static_cast<int>(blocks_per_shard), slot_stride, scales_off,
+                                                static_cast<int>(first_ag_slot), hist, logs);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  rht_offset_kernel<<<1, 1024, 0, stream>>>(hist, budget, offset);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  rht_widths_tiles_kernel<<<ntiles, 1024, 0, stream>>>(logs, offset, nb, plan.data_ptr<int>(), tile_totals);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  rht_add_tile_base_kernel<<<ntiles, 1024, 0, stream>>>(tile_totals, nb, plan.data_ptr<int>());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 

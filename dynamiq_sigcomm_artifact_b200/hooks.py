@@ -163,6 +163,7 @@ def _engine(state: HookState):
                                          rotation=cfg.rotation, max_ctas=max(cfg.comm_ctas, cfg.tail_ctas),
                                          prefetch=cfg.comm_prefetch, widest=widest_wire(state["spec"]),
                                          debug=cfg.debug)
+        state["engine"].stats_sink = state["stats"]  # every collective adds the bytes it puts on the wire
         state["comm_stream"] = torch.cuda.Stream(priority=-1)
     return state["engine"]
 
@@ -224,10 +225,6 @@ def _rht_allreduce(state: HookState, bucket) -> torch.futures.Future:
     st = state["stats"]
     st["collectives"] += 1
     st["buckets"][index] = {"numel": buf.numel(), "bits": bits, "mixed": spec.mixed}
-    if buf.is_cuda:
-        from .parallel.fused import wire_bytes_per_rank
-
-        st["wire_bytes"] += wire_bytes_per_rank(buf.numel(), world, bits, "rht")  # mixed: the average meets `bits`
     exact = None
     if cfg.measure_comm_error:
         exact = buf.detach().clone().float()
@@ -242,7 +239,8 @@ def _rht_allreduce(state: HookState, bucket) -> torch.futures.Future:
             if spec.mixed:  # one collective with a width per block, then the next step's widths from its scales
                 plan = _mixed_plan(state, index, buf.numel(), buf.device)
                 eng.allreduce_(buf, 8, spec.topology, cfg.seed, step, index, no_transmit=spec.compute_only,
-                               correlated=spec.correlated, codec="rht_mix", plan=plan, ctas=grid)
+                               correlated=spec.correlated, codec="rht_mix", plan=plan, ctas=grid,
+                               wire_bits=float(bits))  # the width policy meets `bits` on average
                 if not spec.compute_only:
                     eng.update_widths_(plan, buf.numel(), float(bits))
             else:

@@ -89,14 +89,20 @@ class Layout:
         return _align(self.scales_off + scales, 256)
 
 
-def wire_bytes_per_rank(numel: int, world: int, bits: int, codec: str = "rht") -> int:
+def wire_bytes_per_rank(numel: int, world: int, bits: float, codec: str = "rht") -> int:
     """Bytes one rank puts on NVLink in one collective of `numel` elements (each direction): W - 1
-    reduce-scatter messages and its own shard to W - 1 peers, whatever the topology."""
+    reduce-scatter messages and its own shard to W - 1 peers, whatever the topology.  For the codecs whose
+    width varies per block or superchunk, `bits` is the average width the plan was built for."""
     if world <= 1:
         return 0
-    lay = Layout(numel, world, bits, codec)
-    per_block = (128 * bits if codec in RHT_CODECS else block_bytes(bits, codec)) + (4 if codec in RHT_CODECS else 0)
-    return 2 * (world - 1) * lay.blocks_per_shard * per_block
+    lay = Layout(numel, world, 8 if codec in ("rht_mix",) or codec.startswith("scmix_") else int(bits), codec)
+    if codec in RHT_CODECS:
+        per_block = 128.0 * bits + 4
+    elif codec.startswith("scmix_"):
+        per_block = 4 * (32.0 * bits + 18)  # four 256-element superchunk records: codes + 16 scales + header
+    else:
+        per_block = block_bytes(int(bits), codec)
+    return int(2 * (world - 1) * lay.blocks_per_shard * per_block)
 
 
 def uniform_plan(numel: int, bits: int, device) -> torch.Tensor:
@@ -195,6 +201,7 @@ class FusedAllreduce:
         collective with a status (``CollectiveTimeout`` names it) instead of a stray store.  With compute-sanitizer not
         available on every machine, this and the byte-exact oracle comparisons are the overrun net."""
         self.debug = bool(debug)
+        self.stats_sink: Optional[dict] = None  # a hook state's "stats": gets the bytes every collective puts on the wire
         if self.debug:
             _ops.require().set_debug(True)
         self.ops = _ops.require()
@@ -265,9 +272,11 @@ class FusedAllreduce:
     def allreduce_(self, bucket: torch.Tensor, bits: int, topology: str = "ring", seed: int = 0, step: int = 0,
                    bucket_id: int = 0, no_transmit: bool = False, correlated: bool = False,
                    codec: Optional[str] = None, ctas: Optional[int] = None,
-                   plan: Optional[torch.Tensor] = None, post_scale: Optional[float] = None) -> torch.Tensor:
+                   plan: Optional[torch.Tensor] = None, post_scale: Optional[float] = None,
+                   wire_bits: Optional[float] = None) -> torch.Tensor:
         """In-place mean all-reduce of a flat fp32/bf16 CUDA tensor on the current stream (`post_scale`: the
-        factor applied to the sum instead of 1 / world; 1.0 gives the plain sum).
+        factor applied to the sum instead of 1 / world; 1.0 gives the plain sum).  `wire_bits` only feeds the
+        byte accounting (`stats_sink["wire_bytes"]`): the average width of a plan-driven codec.
 
         `codec`: None (the engine's rotation codec), "sc_aee" / "sc_mee" (the hierarchical superchunk
         codec with 2 / 4 / 8-bit codes), "scmix_aee" / "scmix_mee" (the same with a width per superchunk,
@@ -292,6 +301,9 @@ class FusedAllreduce:
             (1.0 / self.world) if post_scale is None else float(post_scale), self.timeout_ns,
             no_transmit, *codec_args(codec, bits, bucket.device), plan, self.prefetch)
         counters.add("fused_allreduce")
+        if self.stats_sink is not None and not no_transmit:
+            self.stats_sink["wire_bytes"] += wire_bytes_per_rank(bucket.numel(), self.world,
+                                                                 bits if wire_bits is None else wire_bits, codec)
         return bucket
 
     # -- a code width per block (codec "rht_mix") ------------------------------------------

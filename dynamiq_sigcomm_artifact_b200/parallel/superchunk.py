@@ -175,7 +175,8 @@ def _native_mixed(state, bucket) -> torch.futures.Future:
         plan = dq.superchunk_plan(widths)
         counters.add("superchunk_plan")
         eng.allreduce_(flat, 8, spec.topology, cfg.seed, step, (index << 2) | 3, no_transmit=spec.compute_only,
-                       codec=f"scmix_{spec.lattice}", plan=plan, ctas=_grid(state, bucket))
+                       codec=f"scmix_{spec.lattice}", plan=plan, ctas=_grid(state, bucket),
+                       wire_bits=float(spec.bits))  # nominal: the realised mixture depends on the data
         dq.superchunk_add_mean(flat, stats[:, 0].contiguous(), buf.reshape(-1))
         counters.add("superchunk_add_mean")
         st = state["stats"]
