@@ -236,9 +236,17 @@ def run_collectives(args) -> None:
             ms = time_op(run_hook, lambda: work.copy_(base), args.iters, max(args.warmup, 3))
             if state["engine"] is not None:
                 state["engine"].check()
+            spread = dict(LAST_SPREAD)
+            err = nmse_vs(exact, work)
+            sent = state["stats"]["wire_bytes"]  # bytes of ONE more call (statistics collectives included)
+            work.copy_(base)
+            run_hook()
+            torch.cuda.synchronize()
+            sent = state["stats"]["wire_bytes"] - sent
+            LAST_SPREAD.update(spread)
             spec = state["spec"]
-            record(f"hook_{method}", ms, float(state["stats"].get("wire_bytes", 0)) / max(state["stats"].get("collectives", 1), 1),
-                   nmse_vs(exact, work), {"family": spec.family, "hook": spec.hook, "topology": spec.topology})
+            record(f"hook_{method}", ms, float(sent), err,
+                   {"family": spec.family, "hook": spec.hook, "topology": spec.topology})
             state.close()
     if rank == 0 and args.out:
         with open(args.out, "w") as f:
