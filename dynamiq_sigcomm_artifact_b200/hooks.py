@@ -275,6 +275,9 @@ def _rht_allreduce(state: HookState, bucket) -> torch.futures.Future:
 
         out = cb.allreduce_gloo(buf.detach().float().numpy(), bits, spec.topology, cfg.seed, step, index,
                                 group=state["group"], correlated=spec.correlated, codec_factory=factory)
+        from .parallel.fused import wire_bytes_per_rank
+
+        st["wire_bytes"] += wire_bytes_per_rank(buf.numel(), world, float(bits), "rht_mix" if spec.mixed else "rht")
         if spec.mixed:
             from . import bitalloc
 

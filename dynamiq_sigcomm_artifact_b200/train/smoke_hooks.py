@@ -85,7 +85,8 @@ def run(args) -> dict:
     if state["engine"] is not None:
         state["engine"].check()
     out = {"method": args.aggregation_method, "world": world, "numel": args.numel, "nmse": errs,
-           "checksum_delta": deltas, "grad_sum": digest,
+           "checksum_delta": deltas, "grad_sum": digest, "wire_bytes": int(state["stats"]["wire_bytes"]),
+           "collectives": int(state["stats"]["collectives"]),
            "mean_step_s": float(np.mean(times[3:])) if len(times) > 3 else None}
     state.close()
     return out

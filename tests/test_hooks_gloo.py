@@ -72,6 +72,8 @@ def test_dynamiq_aee_5bit_ring_world2():
     assert max(a["nmse"][:2]) < 1e-12
     assert all(1e-4 < e < 3e-2 for e in a["nmse"][2:]), a["nmse"]
     assert max(a["checksum_delta"]) == 0.0
+    # two compressed steps of 2^20 elements on 2 ranks: 2 (W - 1) shards of 512 blocks x (640 code + 4 scale bytes)
+    assert a["wire_bytes"] == 2 * 2 * 512 * 644 and a["collectives"] == 2
     b = _run("dynamiQ_aee_5bit")
     assert a["grad_sum"] == b["grad_sum"], "not bit-reproducible from the seed"
 
