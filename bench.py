@@ -70,8 +70,6 @@ def collective_self_check(tr, world: int, rank: int):
 
     from dynamiq_sigcomm_artifact_b200 import codec_ref as cr
     from dynamiq_sigcomm_artifact_b200.parallel import cpu_backend as cb
-    from dynamiq_sigcomm_artifact_b200.parallel.fused import wire_bytes_per_rank
-
     state = tr.state
     if world == 1 or state is None or state["spec"].hook not in ("dynamiq", "dynamiq_bitrate") \
             or state["spec"].family != "rht":
@@ -104,7 +102,7 @@ def collective_self_check(tr, world: int, rank: int):
     return {"bit_exact": bool(flag.item()) and not tc, "within_tf32_tolerance": bool(flag.item()),
             "rotation": "tc" if tc else "simt", "numel": n, "bits": bits, "topology": topo,
             "nmse_vs_exact_mean": cr.nmse(got, exact), "collectives": int(state["stats"]["collectives"]) + 1,
-            "wire_bytes": int(state["stats"]["wire_bytes"]) + wire_bytes_per_rank(n, world, bits, "rht")}
+            "wire_bytes": int(state["stats"]["wire_bytes"])}  # the engine accounts every collective, this one included
 
 
 def same_engine_fp32(args, cfg_kwargs: dict, steps: int, warmup: int):
