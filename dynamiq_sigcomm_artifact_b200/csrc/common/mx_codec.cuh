@@ -153,6 +153,58 @@ __device__ __forceinline__ void cast_decode_block(float (&v)[32], const uint8_t*
   }
 }
 
+// ---- identity wire without staging ---------------------------------------------------------------------
+// The message of the identity codec is the block's values in element order, so a warp can move them straight
+// between global memory and registers in the coalesced load layout (element j * 128 + lane * 4 + k in
+// v[4 j + k], the layout of load_block / store_block): every access is a full 512-byte (fp32) or 256-byte
+// (bf16) line run per instruction, and nothing passes through shared memory.
+
+// what the wire keeps of each value (non-finite -> 0, bf16 rounding for the 16-bit wire)
+template <int B>
+__device__ __forceinline__ void cast_round(float (&v)[32]) {
+#pragma unroll
+  for (int k = 0; k < 32; k += 2) {
+    const float a = sanitize(v[k]), b = sanitize(v[k + 1]);
+    if (B == 16) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+      const uint32_t q = *reinterpret_cast<const uint32_t*>(&h);
+      v[k] = __uint_as_float(q << 16), v[k + 1] = __uint_as_float(q & 0xFFFF0000u);
+    } else {
+      v[k] = a, v[k + 1] = b;
+    }
+  }
+}
+
+// values already rounded by cast_round -> message
+template <int B>
+__device__ __forceinline__ void cast_msg_store(uint8_t* dst, const float (&v)[32], int lane) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float o[4] = {v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]};
+    if (B == 16) Elem<__nv_bfloat16>::store4(reinterpret_cast<__nv_bfloat16*>(dst) + j * 128 + lane * 4, o);
+    else Elem<float>::store4(reinterpret_cast<float*>(dst) + j * 128 + lane * 4, o);
+  }
+}
+
+// message -> v (ADD: accumulate); the message was written by a peer: read past L1
+template <int B, bool ADD>
+__device__ __forceinline__ void cast_msg_load(float (&v)[32], const uint8_t* src, int lane) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float o[4];
+    if (B == 16) {
+      const uint2 q = __ldcg(reinterpret_cast<const uint2*>(src) + j * 32 + lane);
+      o[0] = __uint_as_float(q.x << 16), o[1] = __uint_as_float(q.x & 0xFFFF0000u);
+      o[2] = __uint_as_float(q.y << 16), o[3] = __uint_as_float(q.y & 0xFFFF0000u);
+    } else {
+      const float4 q = __ldcg(reinterpret_cast<const float4*>(src) + j * 32 + lane);
+      o[0] = q.x, o[1] = q.y, o[2] = q.z, o[3] = q.w;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[4 * j + k] = ADD ? __fadd_rn(v[4 * j + k], o[k]) : o[k];
+  }
+}
+
 template <int NBYTES>
 __device__ __forceinline__ void bytes_copy_out(uint8_t* dst, const uint8_t* tile, int lane) {
   for (int i = lane; i < NBYTES / 16; i += 32) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(tile)[i];

@@ -74,6 +74,41 @@ __device__ __forceinline__ void sc_store_block(T* base, int valid, bool vec_ok, 
   }
 }
 
+// The same two moves for whole fp32 blocks with fully coalesced global accesses: the warp reads or writes 512
+// contiguous bytes per instruction and the lane-contiguous runs are formed through a warp-private 4 KiB shared
+// buffer.  16-byte chunk c (= element / 4) of the block lives at chunk c ^ ((c >> 3) & 7) of the buffer, which
+// makes both the linear side (chunk j * 32 + lane) and the per-lane side (chunk lane * 8 + i) free of bank
+// conflicts while every register index stays a compile-time constant.
+__device__ __forceinline__ void sc_load_block_coalesced(const float* base, float* buf, int lane, float (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int c = j * 32 + lane;
+    const float4 q = *reinterpret_cast<const float4*>(base + 4 * c);
+    *reinterpret_cast<float4*>(buf + 4 * (c ^ ((c >> 3) & 7))) = q;
+  }
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float4 q = *reinterpret_cast<const float4*>(buf + 4 * ((lane * 8 + i) ^ (lane & 7)));
+    v[4 * i] = q.x, v[4 * i + 1] = q.y, v[4 * i + 2] = q.z, v[4 * i + 3] = q.w;
+  }
+  __syncwarp();
+}
+
+__device__ __forceinline__ void sc_store_block_coalesced(float* base, float* buf, int lane, const float (&v)[32]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    *reinterpret_cast<float4*>(buf + 4 * ((lane * 8 + i) ^ (lane & 7))) =
+        make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int c = j * 32 + lane;
+    *reinterpret_cast<float4*>(base + 4 * c) = *reinterpret_cast<const float4*>(buf + 4 * (c ^ ((c >> 3) & 7)));
+  }
+  __syncwarp();
+}
+
 // Encode the block held in v into four records in `tile` (shared memory, >= kBlockBytes).
 template <int B, bool MEE>
 __device__ __forceinline__ void sc_encode_block(const float (&v)[32], uint8_t* tile, const ScParams& sp,

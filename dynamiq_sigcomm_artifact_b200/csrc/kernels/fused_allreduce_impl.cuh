@@ -90,7 +90,9 @@ __device__ __forceinline__ void fused_simt_body(const ARParams& p) {
   // prefetch state (warp-uniform): the item whose data is in flight or resident in `stage`
   RawItem pf = RawItem{-1, -1};
   uint32_t pf_parity = 0;
-  bool prefetch_ok = !SC && use_stage;  // the record codecs read lane-contiguous runs straight from global memory
+  // the rotation codec and the identity wire read raw blocks in the coalesced load layout, which a bulk copy into
+  // the warp's staging buffer can prefetch; the other record codecs use that buffer to form lane-contiguous runs
+  bool prefetch_ok = (!SC || CAST) && use_stage;
   const ScParams scp{p.sc_lattice_max, p.sc_c1, p.sc_c2, p.sc_lut};
   uint8_t* rec_tile = reinterpret_cast<uint8_t*>(tile);  // superchunk codec: the warp's record staging area
   auto issue_prefetch = [&](RawItem it) {
@@ -180,55 +182,122 @@ __device__ __forceinline__ void fused_simt_body(const ARParams& p) {
           else sc_encode_block<SCB, MEE>(v, rec_tile, scp, first_call, tag, p.step, p.seed_lo, p.seed_hi, lane);
           __syncwarp();
         };
-        if (out != kOutDecode) {
-          if (local == kLocalRaw) sc_load_block<T>(bucket + e0, valid, vec_ok, lane, v);
-          else if (blk == tail_block) sc_load_block<float>(p.tail_ws, kBlock, true, lane, v);
-          else sc_load_block<T>(bucket + e0, kBlock, vec_ok, lane, v);
-          for (int r = 0; r < nrecv; ++r) {
-            const uint8_t* slot = my_mail + static_cast<unsigned long long>(recv_slot + r) * p.slot_stride;
-            rec_in(slot + boff);
-            if constexpr (MIX) sc_decode_block_mix<MEE, true>(v, rec_tile, p.sc_lut, wpack, lane);
-            else if constexpr (CAST) cast_decode_block<CB, true>(v, rec_tile, lane);
-            else if constexpr (MX) mx_decode_block<MXB, true>(v, rec_tile, lane);
-            else sc_decode_block<SCB, MEE, true>(v, rec_tile, scp, lane);
-            __syncwarp();
-          }
-        }
-        if (out == kOutStore) {
-          if (blk == tail_block) sc_store_block<float>(p.tail_ws, kBlock, true, lane, v);
-          else sc_store_block<T>(bucket + e0, kBlock, vec_ok, lane, v);
-        } else if (out == kOutSend) {
-          rec_encode();
-          if (!p.no_transmit) rec_out(p.mail[dst] + static_cast<unsigned long long>(send_slot) * p.slot_stride + boff);
-          __syncwarp();
-        } else {
-          if (out == kOutFinal) {
-            rec_encode();
-            if (!p.no_transmit) {
-              for (int peer = 0; peer < p.world; ++peer) {
-                if (peer == p.rank) continue;
-                rec_out(p.mail[peer] + static_cast<unsigned long long>(send_slot) * p.slot_stride + boff);
+        if constexpr (CAST) {
+          // identity wire: values move between global memory and registers in the coalesced load layout,
+          // nothing is staged (csrc/common/mx_codec.cuh, cast_msg_*)
+          if (out != kOutDecode) {
+            if (local == kLocalRaw) {
+              if (pf.s == s && pf.blk == blk && mbar_wait(bar, pf_parity)) {
+                pf_parity ^= 1u;
+                load_block<T>(reinterpret_cast<const T*>(stage), kBlock, true, lane, v);
+                __syncwarp();
+              } else {
+                if (pf.s == s && pf.blk == blk) {  // the copy never completed: report it, read directly,
+                  fail(kErrCopyTimeout, s, -1);    // and stop prefetching (the warp stays in step with its CTA)
+                  prefetch_ok = false;
+                }
+                load_block<T>(bucket + e0, valid, vec_ok, lane, v);
               }
+              issue_prefetch(next_raw_item(p, s, blk, cta, per_cta, warp, nwarps));
             }
-          } else {
-            rec_in(my_mail + static_cast<unsigned long long>(recv_slot) * p.slot_stride + boff);
+            else if (blk == tail_block) load_block<float>(p.tail_ws, kBlock, true, lane, v);
+            else load_block<T>(bucket + e0, kBlock, vec_ok, lane, v);
+            for (int r = 0; r < nrecv; ++r)
+              cast_msg_load<CB, true>(v, my_mail + static_cast<unsigned long long>(recv_slot + r) * p.slot_stride + boff, lane);
           }
-          if constexpr (MIX) sc_decode_block_mix<MEE, false>(v, rec_tile, p.sc_lut, wpack, lane);
-          else if constexpr (CAST) cast_decode_block<CB, false>(v, rec_tile, lane);
-          else if constexpr (MX) mx_decode_block<MXB, false>(v, rec_tile, lane);
-          else sc_decode_block<SCB, MEE, false>(v, rec_tile, scp, lane);
-          __syncwarp();
-          // the mean divides by the world size, as the tensor-operator codecs do; any other post-scale
-          // (1 for a plain sum) multiplies
-          const float wf = static_cast<float>(p.world), ps = p.finish_scale * 1024.0f;
-          if (ps == __fdiv_rn(1.0f, wf)) {
-#pragma unroll
-            for (int k = 0; k < 32; ++k) v[k] = __fdiv_rn(v[k], wf);
+          if (out == kOutStore) {
+            if (blk == tail_block) store_block<float>(p.tail_ws, kBlock, true, lane, v);
+            else store_block<T>(bucket + e0, kBlock, vec_ok, lane, v);
+          } else if (out == kOutSend) {
+            cast_round<CB>(v);
+            if (!p.no_transmit)
+              cast_msg_store<CB>(p.mail[dst] + static_cast<unsigned long long>(send_slot) * p.slot_stride + boff, v, lane);
           } else {
+            if (out == kOutFinal) {
+              cast_round<CB>(v);  // this rank keeps what its peers will decode
+              if (!p.no_transmit) {
+                for (int peer = 0; peer < p.world; ++peer) {
+                  if (peer == p.rank) continue;
+                  cast_msg_store<CB>(p.mail[peer] + static_cast<unsigned long long>(send_slot) * p.slot_stride + boff, v, lane);
+                }
+              }
+            } else {
+              cast_msg_load<CB, false>(v, my_mail + static_cast<unsigned long long>(recv_slot) * p.slot_stride + boff, lane);
+            }
+            const float wf = static_cast<float>(p.world), ps = p.finish_scale * 1024.0f;
+            if (ps == __fdiv_rn(1.0f, wf)) {
 #pragma unroll
-            for (int k = 0; k < 32; ++k) v[k] = __fmul_rn(v[k], ps);
+              for (int k = 0; k < 32; ++k) v[k] = __fdiv_rn(v[k], wf);
+            } else {
+#pragma unroll
+              for (int k = 0; k < 32; ++k) v[k] = __fmul_rn(v[k], ps);
+            }
+            store_block<T>(bucket + e0, valid, vec_ok, lane, v);
           }
-          sc_store_block<T>(bucket + e0, valid, vec_ok, lane, v);
+        } else {
+        // whole fp32 blocks go through the warp's (otherwise unused) staging buffer with coalesced accesses
+        auto raw_in = [&](const T* src, int nvalid) {
+          if constexpr (std::is_same<T, float>::value) {
+            if (use_stage && vec_ok && nvalid == kBlock) return sc_load_block_coalesced(src, stage, lane, v);
+          }
+          sc_load_block<T>(src, nvalid, vec_ok, lane, v);
+        };
+        auto raw_out = [&](T* dstp, int nvalid) {
+          if constexpr (std::is_same<T, float>::value) {
+            if (use_stage && vec_ok && nvalid == kBlock) return sc_store_block_coalesced(dstp, stage, lane, v);
+          }
+          sc_store_block<T>(dstp, nvalid, vec_ok, lane, v);
+        };
+        if (out != kOutDecode) {
+            if (local == kLocalRaw) raw_in(bucket + e0, valid);
+            else if (blk == tail_block) sc_load_block<float>(p.tail_ws, kBlock, true, lane, v);
+            else raw_in(bucket + e0, kBlock);
+            for (int r = 0; r < nrecv; ++r) {
+              const uint8_t* slot = my_mail + static_cast<unsigned long long>(recv_slot + r) * p.slot_stride;
+              rec_in(slot + boff);
+              if constexpr (MIX) sc_decode_block_mix<MEE, true>(v, rec_tile, p.sc_lut, wpack, lane);
+              else if constexpr (CAST) cast_decode_block<CB, true>(v, rec_tile, lane);
+              else if constexpr (MX) mx_decode_block<MXB, true>(v, rec_tile, lane);
+              else sc_decode_block<SCB, MEE, true>(v, rec_tile, scp, lane);
+              __syncwarp();
+            }
+          }
+          if (out == kOutStore) {
+            if (blk == tail_block) sc_store_block<float>(p.tail_ws, kBlock, true, lane, v);
+            else raw_out(bucket + e0, kBlock);
+          } else if (out == kOutSend) {
+            rec_encode();
+            if (!p.no_transmit) rec_out(p.mail[dst] + static_cast<unsigned long long>(send_slot) * p.slot_stride + boff);
+            __syncwarp();
+          } else {
+            if (out == kOutFinal) {
+              rec_encode();
+              if (!p.no_transmit) {
+                for (int peer = 0; peer < p.world; ++peer) {
+                  if (peer == p.rank) continue;
+                  rec_out(p.mail[peer] + static_cast<unsigned long long>(send_slot) * p.slot_stride + boff);
+                }
+              }
+            } else {
+              rec_in(my_mail + static_cast<unsigned long long>(recv_slot) * p.slot_stride + boff);
+            }
+            if constexpr (MIX) sc_decode_block_mix<MEE, false>(v, rec_tile, p.sc_lut, wpack, lane);
+            else if constexpr (CAST) cast_decode_block<CB, false>(v, rec_tile, lane);
+            else if constexpr (MX) mx_decode_block<MXB, false>(v, rec_tile, lane);
+            else sc_decode_block<SCB, MEE, false>(v, rec_tile, scp, lane);
+            __syncwarp();
+            // the mean divides by the world size, as the tensor-operator codecs do; any other post-scale
+            // (1 for a plain sum) multiplies
+            const float wf = static_cast<float>(p.world), ps = p.finish_scale * 1024.0f;
+            if (ps == __fdiv_rn(1.0f, wf)) {
+  #pragma unroll
+              for (int k = 0; k < 32; ++k) v[k] = __fdiv_rn(v[k], wf);
+            } else {
+  #pragma unroll
+              for (int k = 0; k < 32; ++k) v[k] = __fmul_rn(v[k], ps);
+            }
+            raw_out(bucket + e0, valid);
+          }
         }
       } else {
       // ---- rotation codec ----
