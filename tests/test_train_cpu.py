@@ -132,3 +132,22 @@ def test_eval_reports_perplexity(tmp_path, capsys):
     masked_lm.main(["--model_name", "bert-tiny", "--per_device_train_batch_size", "2", "--block_size", "32",
                     "--max_train_steps", "3", "--eval_batches", "2", "--output_dir", str(tmp_path / "b")])
     assert "perplexity=" in capsys.readouterr().out
+
+
+def test_bucket_policy_and_wire_accounting():
+    from dynamiq_sigcomm_artifact_b200.parallel.fused import wire_bytes_per_rank
+    from dynamiq_sigcomm_artifact_b200.train.engine import default_bucket_cap_mb
+
+    # one bucket per model for the package's own collectives on several GPUs, small buckets otherwise
+    assert default_bucket_cap_mb("dynamiQ_aee_5bit", 8, "gpt2-small") == 4000
+    assert default_bucket_cap_mb("bf16", 4, "bert-base") == 4000
+    assert default_bucket_cap_mb("fp32", 8, "gpt2-small") == 25 and default_bucket_cap_mb("none", 2, "x") == 25
+    assert default_bucket_cap_mb("dynamiQ_aee_5bit", 1, "gpt2-small") == 25
+    assert default_bucket_cap_mb("dynamiQ_aee_5bit", 1, "llama-1.2b") == 100
+    # bytes per rank and direction: 2 (W - 1) shards; rotation codec 128 b + 4 per block, bf16 wire 2 KiB per block
+    n, w = 8 * 1024 * 16, 4
+    assert wire_bytes_per_rank(n, w, 5, "rht") == 2 * 3 * 32 * 644
+    assert wire_bytes_per_rank(n, w, 4.5, "rht_mix") == 2 * 3 * 32 * 580
+    assert wire_bytes_per_rank(n, w, 16, "cast") == 2 * 3 * 32 * 2048
+    assert wire_bytes_per_rank(n, w, 4, "scmix_mee") == 2 * 3 * 32 * 4 * 146
+    assert wire_bytes_per_rank(n, 1, 5, "rht") == 0
