@@ -54,6 +54,9 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--bucket-cap-mb", type=int, default=0,
                     help="0: one bucket for the whole model (4000 MB cap, the reference's setting for DynamiQ); the "
                          "fp32 library arm always uses 25 MB buckets")
+    ap.add_argument("--tail-pipeline-mb", type=int, default=0,
+                    help="> 0: buckets of this size sent after backward, optimizer step of bucket k under the "
+                         "collective of bucket k + 1")
     ap.add_argument("--rotation", default="simt", choices=["simt", "tc"])
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the collective self-check and the same-engine fp32 comparison after the timed regions")
@@ -171,7 +174,7 @@ def main() -> None:
     cfg_kwargs = dict(model=args.model, method=args.method, micro_batch=mb, seq_len=seq, task=task,
                       bucket_cap_mb=args.bucket_cap_mb, topology=args.topology, comm_ctas=args.comm_ctas,
                       comm_threads=args.comm_threads, tail_ctas=args.tail_ctas, reducer=args.reducer,
-                      comm_prefetch=bool(args.comm_prefetch),
+                      comm_prefetch=bool(args.comm_prefetch), tail_pipeline_mb=args.tail_pipeline_mb,
                       sparse_embedding=None if args.sparse_embedding < 0 else bool(args.sparse_embedding))
     cfg = TrainConfig(**cfg_kwargs)
     tr = Trainer(cfg)
@@ -240,7 +243,7 @@ def main() -> None:
             "data": "synthetic uniform token ids, random-init weights", "impl": "ours",
             "config": {"model": args.model, "arch": desc, "global_batch": mb * world, "seq_len": seq,
                        "parallelism": f"dp{world}", "method": args.method if world > 1 else "none (1 GPU)",
-                       "bucket_cap_mb": args.bucket_cap_mb, "reducer": args.reducer, "optimizer": "fused AdamW, fp32 master weights",
+                       "bucket_cap_mb": args.bucket_cap_mb, "tail_pipeline_mb": args.tail_pipeline_mb, "reducer": args.reducer, "optimizer": "fused AdamW, fp32 master weights",
                        "l2": "per-step working set (weights+grads+optimizer state+activations) is several GB, >> 126 MB L2"},
             "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"),
                        "reasons": clocks.get("reasons", []), "samples": clocks.get("samples", 0)},

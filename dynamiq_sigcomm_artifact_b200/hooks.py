@@ -190,7 +190,7 @@ def _nvls(state: HookState, numel: int, wire_bits: int):
 def _grid(state: HookState, bucket) -> Optional[int]:
     """The step's last bucket has no backward pass left to share the GPU with: give it the wide grid."""
     cfg: DynamiqConfig = state["config"]
-    if cfg.tail_ctas > 0 and bucket.is_last():
+    if cfg.tail_ctas > 0 and (bucket.is_last() or getattr(bucket, "exposed", False)):
         return cfg.tail_ctas
     return None
 

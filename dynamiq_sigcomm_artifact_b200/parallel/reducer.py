@@ -50,6 +50,7 @@ class FlatBucket:
 
     def __init__(self, index: int, buffer: torch.Tensor, params: List[nn.Parameter], last: bool):
         self._index, self._buffer, self._params, self._last = index, buffer, params, last
+        self.exposed = last  # True when nothing of backward runs beside this bucket's collective (wide grid)
 
     def index(self) -> int:
         return self._index
@@ -109,8 +110,12 @@ class BucketReducer:
     def __init__(self, model: nn.Module, bucket_cap_mb: float = 25.0, hook: Optional[Callable] = None,
                  hook_state=None, on_reduced: Optional[Callable[[int, List[nn.Parameter]], None]] = None,
                  direct: bool = True, side_stream: bool = True, group=None, install: bool = True,
-                 sparse_embedding: Optional[bool] = None):
+                 sparse_embedding: Optional[bool] = None, defer: bool = False):
+        """`defer`: no bucket is sent while backward runs; after it, the buckets go out back to back on the side
+        stream and every bucket's consumer (`on_reduced`, the optimizer step) runs on a second stream as soon as
+        its bucket is reduced - bucket k's optimizer step overlaps bucket k+1's collective instead of backward."""
         self.model, self.hook, self.hook_state, self.on_reduced = model, hook, hook_state, on_reduced
+        self.defer = bool(defer)
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self._sparse_wanted = sparse_embedding
@@ -133,6 +138,11 @@ class BucketReducer:
         self.groups = self._make_groups(params)
         self._layout(bucket_cap_mb)
         self.side = torch.cuda.Stream(self.device) if (self.cuda and side_stream) else None
+        self.consumer_stream = torch.cuda.Stream(self.device) if (self.side is not None and self.defer) else None
+        self._pending: List[int] = []
+        if self.defer:
+            for b in self.buckets:
+                b.exposed = True
         self._ready_upto = -1  # groups [0, _ready_upto] have been reported
         self._next_bucket = 0
         self._handles = []
@@ -270,6 +280,7 @@ class BucketReducer:
     def begin_step(self) -> None:
         self._ready_upto = -1
         self._next_bucket = 0
+        self._pending = []
 
     def group_ready(self, gi: int) -> None:
         """Groups are reported in order; reporting group g implies every group before it."""
@@ -281,6 +292,9 @@ class BucketReducer:
             self._next_bucket += 1
 
     def _launch(self, bi: int) -> None:
+        if self.defer and self.consumer_stream is not None:
+            self._pending.append(bi)  # sent by finish(), after backward
+            return
         bucket = self.buckets[bi]
         self.launched += 1
         if self.side is not None:
@@ -306,10 +320,39 @@ class BucketReducer:
     def finish(self) -> None:
         """After ``loss.backward()``: flush what no marker reported and join the side stream."""
         self.group_ready(len(self.groups) - 1)
+        if self._pending:
+            self._run_deferred()
         if self.sparse_params:
             self._finish_sparse()
         if self.side is not None:
             torch.cuda.current_stream(self.device).wait_stream(self.side)
+
+    def _run_deferred(self) -> None:
+        """Every bucket's hook on the side stream, back to back; its consumer on a second stream behind an event."""
+        cur = torch.cuda.current_stream(self.device)
+        self.side.wait_stream(cur)
+        self.consumer_stream.wait_stream(cur)
+        for bi in self._pending:
+            bucket = self.buckets[bi]
+            self.launched += 1
+            with torch.cuda.stream(self.side), torch.no_grad():
+                if self.hook is not None:
+                    fut = self.hook(self.hook_state, bucket)
+                    fut.wait()
+                    bucket.set_buffer(fut.value())
+                if self._gap_index is not None and bucket.is_last():
+                    self.arena.index_fill_(0, self._gap_index, 0.0)
+                reduced = torch.cuda.Event()
+                reduced.record(self.side)
+            if self.on_reduced is not None:
+                with torch.cuda.stream(self.consumer_stream), torch.no_grad():
+                    self.consumer_stream.wait_event(reduced)
+                    ready = [p for p in self.bucket_params[bi] if id(p) not in self._sparse_ids]
+                    self.on_reduced(bi, ready)
+                    for p in self.bucket_accum[bi]:
+                        p.grad.zero_()
+        self._pending = []
+        self.side.wait_stream(self.consumer_stream)  # finish() joins the side stream
 
     def _finish_sparse(self) -> None:
         """Exchange the lookup rows of the tied embeddings, add every rank's rows (same order everywhere), then

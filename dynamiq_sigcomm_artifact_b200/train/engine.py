@@ -62,6 +62,8 @@ class TrainConfig:
     weight_decay: float = 0.0
     total_steps: int = 10_000
     bucket_cap_mb: int = 0  # 0: automatic (see the module docstring)
+    tail_pipeline_mb: int = 0  # > 0 ("flat" reducer on CUDA): buckets of this size, all sent AFTER backward, each
+    #                            bucket's optimizer step on a second stream under the next bucket's collective
     seed: int = 0
     dtype: str = "bf16"  # autocast dtype; parameters, gradients and optimizer state are fp32
     task: str = "causal"  # causal | mlm
@@ -116,7 +118,9 @@ class Trainer:
                 hook = hooks.select_comm_hook(cfg.method, dcfg.topology)
                 self.state = state_list[0]
             # the arena has to exist before the blocks are captured: the graphs keep its addresses
-            self.reducer = BucketReducer(self.model, cfg.bucket_cap_mb, hook, state_list,
+            defer = cfg.tail_pipeline_mb > 0 and device.type == "cuda"
+            self.reducer = BucketReducer(self.model, cfg.tail_pipeline_mb if defer else cfg.bucket_cap_mb, hook, state_list,
+                                         defer=defer,
                                          on_reduced=lambda bi, ps: self.opt.step_params(bi, ps),
                                          direct=(device.type == "cuda" and cfg.dtype == "bf16"), install=False,
                                          sparse_embedding=cfg.sparse_embedding)

@@ -48,10 +48,13 @@ def test_in_place_gradients_equal_autograd(name):
     r.detach()
 
 
-@pytest.mark.parametrize("name,graphs", [("gpt2-tiny", True), ("llama-tiny", True), ("gpt2-tiny", False)])
-def test_pipelined_trainer_matches_plain_trainer(name, graphs):
+@pytest.mark.parametrize("name,graphs,tail", [("gpt2-tiny", True, 0), ("llama-tiny", True, 0), ("gpt2-tiny", False, 0),
+                                              ("gpt2-tiny", True, 1)])
+def test_pipelined_trainer_matches_plain_trainer(name, graphs, tail):
+    """`tail` > 0: every bucket goes out after backward and the optimizer steps run on a second stream."""
     cfg = dict(model=name, micro_batch=2, seq_len=128, lr=1e-3, weight_decay=0.01, cuda_graphs=graphs)
-    a = Trainer(TrainConfig(reducer="flat", **cfg))
+    a = Trainer(TrainConfig(reducer="flat", tail_pipeline_mb=tail, bucket_cap_mb=1, **cfg))
+    assert (a.reducer.consumer_stream is not None) == (tail > 0) and len(a.reducer.buckets) > 1
     b = Trainer(TrainConfig(reducer="ddp", **cfg))
     b.model.load_state_dict(a.model.state_dict())
     enable_shadows(b.model)
