@@ -238,26 +238,31 @@ __device__ __forceinline__ uint32_t unpack_code(const uint32_t (&w)[B], int k) {
   return x & ((1u << B) - 1u);
 }
 
-// max(m, |a|, |b|) in one instruction (three-input max of sm_100); a NaN operand makes the result NaN
-__device__ __forceinline__ float max3_abs(float m, float a, float b) {
-  float d;
-  asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(m), "f"(fabsf(a)), "f"(fabsf(b)));
-  return d;
-}
-__device__ __forceinline__ float max_nan(float a, float b) {
-  float d;
-  asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
-  return d;
-}
-
-// largest magnitude of the block; NaN if any coefficient is NaN
+// Largest magnitude of the block (fmaxf ignores NaN operands; the absolute values fold into the max
+// instruction as operand modifiers).  A NaN among the inputs of a rotation reaches EVERY coefficient of the
+// block, so a block with a NaN arrives here with all 32 x 32 values NaN and the result stays 0; an infinite
+// input gives coefficients that are infinite or NaN, and the result is infinite or 0.  Both fail the
+// caller's range check, which is all that is asked of them.
 __device__ __forceinline__ float warp_absmax(const float (&y)[32]) {
   float m = 0.0f;
 #pragma unroll
-  for (int k = 0; k < 32; k += 2) m = max3_abs(m, y[k], y[k + 1]);
+  for (int k = 0; k < 32; k += 2) m = fmaxf(m, fmaxf(fabsf(y[k]), fabsf(y[k + 1])));
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) m = max_nan(m, __shfl_xor_sync(kFullMask, m, o));
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(kFullMask, m, o));
   return m;
+}
+
+// The packed words of a block whose every code is R (the zero level), word j of B.
+template <int B>
+__device__ __forceinline__ constexpr uint32_t zero_block_word(int j) {
+  constexpr uint32_t R = (1u << (B - 1)) - 1u;
+  uint32_t w = 0;
+  for (int k = 0; k < 32; ++k) {
+    const int off = k * B, wi = off >> 5, sh = off & 31;
+    if (wi == j) w |= R << sh;
+    if (sh + B > 32 && wi + 1 == j) w |= R >> (32 - sh);
+  }
+  return w;
 }
 
 // Stochastic b-bit quantisation of a block in the coefficient layout.  Returns the block scale.
@@ -269,7 +274,8 @@ __device__ __forceinline__ float warp_absmax(const float (&y)[32]) {
 //                                          pattern are floor((t - 2^15) / 256) + R = the code
 // No conversion, subtraction or clamp is issued.  No clamp is needed because |y| <= absmax holds exactly:
 // |y * (R / absmax)| <= R (1 + 2^-24), so t - 2^15 lies strictly inside (-256 R, 256 (R + 1)).
-// A block whose absmax is NaN, infinite or below 1e-30 is sent as zeros (scale 0, every code = R).
+// A block whose absmax is infinite or below 1e-30 (which includes the all-NaN block, see warp_absmax) is sent as
+// zeros (scale 0, every code = R); the codes computed from its values are discarded, y itself is left as it is.
 //
 // Stratified ("correlated") rounding, strat_world > 1: all ranks draw the same byte per value and
 // rank r uses u = (((r + shift) mod W) * 256 + byte + 0.5) / (256 W), shift = the byte of the
@@ -293,10 +299,6 @@ __device__ __forceinline__ float quantize_block_rw(float (&y)[32], uint32_t (&w)
   const bool ok = (m >= 1e-30f) && (m <= 3.402823466e38f);
   const float scale = ok ? __fdiv_rn(m, static_cast<float>(R)) : 0.0f;
   const float inv = ok ? __fdiv_rn(static_cast<float>(R), m) : 0.0f;
-  if (!ok) {  // warp-uniform and rare
-#pragma unroll
-    for (int k = 0; k < 32; ++k) y[k] = 0.0f;
-  }
   uint32_t f[32];
   if (strat_world > 1) {
     const float2 half_off = make_float2(-8388607.5f, -8388607.5f);
@@ -336,6 +338,10 @@ __device__ __forceinline__ float quantize_block_rw(float (&y)[32], uint32_t (&w)
     }
   }
   pack_codes<B>(f, w, strat_world > 1 ? 0x4B400000u : 0x4F400000u);
+  if (!ok) {  // warp-uniform and rare: whatever the non-finite values produced above is replaced by the zero block
+#pragma unroll
+    for (int j = 0; j < B; ++j) w[j] = zero_block_word<B>(j);
+  }
   return scale;
 }
 
