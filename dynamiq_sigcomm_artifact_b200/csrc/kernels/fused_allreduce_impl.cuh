@@ -198,7 +198,8 @@ __device__ __forceinline__ void fused_simt_body(const ARParams& p) {
                 }
                 load_block<T>(bucket + e0, valid, vec_ok, lane, v);
               }
-              issue_prefetch(next_raw_item(p, s, blk, cta, per_cta, warp, nwarps));
+              issue_prefetch(blk + nwarps < hi ? RawItem{s, blk + nwarps}  // the common case needs no search
+                                              : next_raw_item(p, s + 1, -1, cta, per_cta, warp, nwarps));
             }
             else if (blk == tail_block) load_block<float>(p.tail_ws, kBlock, true, lane, v);
             else load_block<T>(bucket + e0, kBlock, vec_ok, lane, v);
@@ -357,7 +358,8 @@ __device__ __forceinline__ void fused_simt_body(const ARParams& p) {
             }
             load_block<T>(bucket + e0, valid, vec_ok, lane, v);
           }
-          issue_prefetch(next_raw_item(p, s, blk, cta, per_cta, warp, nwarps));
+          issue_prefetch(blk + nwarps < hi ? RawItem{s, blk + nwarps}  // the common case needs no search
+                                              : next_raw_item(p, s + 1, -1, cta, per_cta, warp, nwarps));
         } else if (blk == tail_block) {
           load_block<float>(p.tail_ws, kBlock, true, lane, v);
         } else {
