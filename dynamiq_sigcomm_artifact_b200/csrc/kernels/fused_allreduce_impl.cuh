@@ -35,13 +35,13 @@ __device__ __forceinline__ RawItem next_raw_item(const ARParams& p, int s, int b
 
 // Shared-memory layout of a CTA of the SIMT bodies (nwarps warps):
 //   [tile: nwarps x 4 KiB][stage: nwarps x 4 KiB (optional)][sign table fwd][sign table inv][sign words]
-//   [prefetch barriers]
+//   [prefetch barriers][pending flags: 2 x kMaxWorld ints]
 // The tensor-core rotation has its own layout (fused_rht_tc.cuh).
 template <bool TC>
 __host__ __device__ constexpr size_t fused_smem_bytes(int threads, bool stage = true) {
   if (TC) return rht_tc_smem_bytes(threads, stage);
   const size_t nwarps = threads / 32;
-  return nwarps * kBlock * 4 + (stage ? nwarps * kBlock * 4 : 0) + 2 * 4096 + 32 * 4 + nwarps * 8 + 128;
+  return nwarps * kBlock * 4 + (stage ? nwarps * kBlock * 4 : 0) + 2 * 4096 + 32 * 4 + nwarps * 8 + 64 + 128;
 }
 
 template <int BITS, typename T, int CODEC>
@@ -105,10 +105,27 @@ __device__ __forceinline__ void fused_simt_body(const ARParams& p) {
 
   auto fail = [&](uint32_t code, int s, int slot) { report_failure(p, code, s, slot); };
 
+  // Flags of consecutive sending steps that receive nothing (the scatter of the direct topology: W - 1 of them)
+  // are published together: one block barrier and one system-scope fence for the run instead of one per step.
+  // A consumer needs all of its incoming shards before it can start anyway, so nothing is delayed.
+  int* pend = reinterpret_cast<int*>(reinterpret_cast<uint64_t*>(cursor) + nwarps);  // 2 * kMaxWorld ints behind the barriers
+  int npend = 0;  // CTA-uniform
+  auto flush_flags = [&]() {
+    if (npend == 0) return;
+    __syncthreads();  // every warp's payload stores of the pending steps precede their flags
+    if (tid < npend) {
+      __threadfence_system();
+      st_release_sys(p.flags[pend[2 * tid]] + p.flag_base + static_cast<uint32_t>(pend[2 * tid + 1]) * G + cta, p.epoch);
+    }
+    npend = 0;
+    __syncthreads();  // `pend` may be rewritten from here on
+  };
+
   bool aborted = false;
   for (int s = 0; s < p.nsteps && !aborted; ++s) {
     const int local = p.steps[s][1], recv_slot = p.steps[s][2], nrecv = p.steps[s][3];
     const int out = p.steps[s][4], dst = p.steps[s][5], send_slot = p.steps[s][6];
+    if (!(nrecv == 0 && out == kOutSend)) flush_flags();  // before this step waits for anybody
     const uint32_t tag = stream_tag(p.bucket_id, static_cast<uint32_t>(p.steps[s][7]) & ~kTagStratified);
     const int strat_world = (static_cast<uint32_t>(p.steps[s][7]) & kTagStratified) ? p.world : 1;
     int shard_lo, lo, hi;
@@ -419,19 +436,20 @@ __device__ __forceinline__ void fused_simt_body(const ARParams& p) {
       }  // rotation codec
     }
 
-    if (out == kOutSend || out == kOutFinal) {
-      __syncthreads();  // every warp's payload stores precede the flag
-      if (out == kOutSend) {
-        if (tid == 0) {
-          __threadfence_system();
-          st_release_sys(p.flags[dst] + p.flag_base + static_cast<uint32_t>(send_slot) * G + cta, p.epoch);
-        }
-      } else if (tid < p.world && tid != p.rank) {
+    if (out == kOutSend) {
+      if (tid == 0) pend[2 * npend] = dst, pend[2 * npend + 1] = send_slot;
+      ++npend;
+      const bool next_is_pure_send = s + 1 < p.nsteps && p.steps[s + 1][3] == 0 && p.steps[s + 1][4] == kOutSend;
+      if (!next_is_pure_send || npend == kMaxWorld) flush_flags();
+    } else if (out == kOutFinal) {
+      __syncthreads();  // every warp's payload stores precede the flags
+      if (tid < p.world && tid != p.rank) {
         __threadfence_system();
         st_release_sys(p.flags[tid] + p.flag_base + static_cast<uint32_t>(send_slot) * G + cta, p.epoch);
       }
     }
   }
+  flush_flags();  // a run of sends that ends the program, or an abort
 
   if (aborted && pf.s >= 0) mbar_wait(bar, pf_parity);  // let this warp's copy in flight land before leaving
 }
